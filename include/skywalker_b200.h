@@ -1,0 +1,217 @@
+/*
+ * skywalker_b200 -- C ABI of the B200-native alias-method sampling / random-walk engine.
+ *
+ * The reference (wpybtw/Skywalker) is a single CUDA executable with no FFI layer; its
+ * "operator interface" is a set of host entry functions called by src/main.cu, each taking a
+ * C++ owner object (Sampler / Walker) and returning kernel seconds.  This header is the plain-C
+ * boundary a maintainer binds instead: every entry point below names the reference function or
+ * type (file:line, paths relative to the reference tree) whose job it takes over.
+ *
+ * Conventions
+ *   - every function returns SKW_OK (0) or a negative skw_status; it never calls exit();
+ *     skw_last_error(ctx) gives the text of the last failure on that context.
+ *   - one skw_ctx per GPU, used by one host thread at a time (the reference runs one OpenMP
+ *     thread per GPU, src/main.cu:252-270).
+ *   - pointers named h_* are host memory (pageable or pinned), d_* are device memory of the
+ *     context's GPU.  The library never keeps a caller pointer after the call returns, except
+ *     the CSR arrays handed over with skw_graph_adopt_device().
+ *   - vertex ids, edge offsets and degrees are uint32_t (reference: vtx_t/edge_t,
+ *     include/graph.cuh:40-45); weights are float.
+ *   - all randomness is Philox4x32-10, counter = (unit id low, unit id high, step, trial),
+ *     key = 64-bit seed xor a per-purpose tag.  Results therefore do not depend on launch
+ *     shape, on the number of GPUs, or on how units are split between calls.
+ *   - there is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     SKW_ERR_CUDA.
+ */
+#ifndef SKYWALKER_B200_H
+#define SKYWALKER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct skw_ctx skw_ctx;
+
+typedef enum skw_status {
+  SKW_OK = 0,
+  SKW_ERR_ARG = -1,      /* bad argument (null pointer, size out of range, wrong state) */
+  SKW_ERR_CUDA = -2,     /* a CUDA runtime call failed; text in skw_last_error           */
+  SKW_ERR_STATE = -3,    /* call order wrong (no graph, no table ...)                    */
+  SKW_ERR_DEVICE = -4,   /* a kernel reported an internal error word (bounded wait ran  *
+                          * out, index out of range, capacity exceeded)                  */
+  SKW_ERR_IO = -5,       /* file could not be read / malformed .gr                       */
+  SKW_ERR_NOMEM = -6
+} skw_status;
+
+/* walk applications (reference presets: src/main.cu:156-175) */
+typedef enum skw_app {
+  SKW_APP_DEEPWALK = 0,  /* fixed length, no termination                                   */
+  SKW_APP_PPR = 1,       /* before every step stop with probability tp                      *
+                          * (reference rule: src/online_walk.cu:109-125, unbiased_walk.cu:82) */
+  SKW_APP_NODE2VEC = 2   /* 2nd-order walk, rejection against max(1/p,1,1/q)                *
+                          * (reference: src/api/bias_node2vec.cu:14-24, unbiased_walk.cu:14-61) */
+} skw_app;
+
+/* where the alias table of the current vertex comes from (reference flag --ol) */
+typedef enum skw_mode {
+  SKW_MODE_OFFLINE = 0,  /* prebuilt table of all vertices (skw_alias_build_offline)        */
+  SKW_MODE_ONLINE = 1    /* table built on the fly for the vertex being left, then dropped  */
+} skw_mode;
+
+/* k-hop flags */
+#define SKW_KHOP_TAKE_ALL 1u /* reference behaviour (src/offline_sample.cu:120-128): when the  *
+                              * fan-out is >= degree copy every neighbour instead of drawing  */
+
+#define SKW_INVALID_VERTEX 0xFFFFFFFFu /* written into k-hop cells that hold no sample */
+
+/* ---------------------------------------------------------------- context ---------------- */
+
+/* Replaces the per-thread cudaSetDevice/cudaFree(0) set-up of src/main.cu:268-270. */
+int skw_ctx_create(int device, skw_ctx** out);
+void skw_ctx_destroy(skw_ctx* ctx);
+const char* skw_last_error(const skw_ctx* ctx);
+/* Library-wide text of the last failure of a call that had no context (skw_ctx_create). */
+const char* skw_last_global_error(void);
+/* All later work of ctx is issued on `cuda_stream` (a cudaStream_t; NULL = the context's own
+ * stream).  Lets a caller time the kernels with its own events. */
+int skw_ctx_set_stream(skw_ctx* ctx, void* cuda_stream);
+int skw_ctx_synchronize(skw_ctx* ctx);
+/* Number of kernels of this library launched by ctx since creation. */
+uint64_t skw_ctx_kernel_launches(const skw_ctx* ctx);
+
+/* ---------------------------------------------------------------- graph ------------------ */
+
+/* Copy a host CSR to the GPU.  Replaces gpu_graph::gpu_graph (include/gpu_graph.cuh:68-117)
+ * in its --gmgraph placement.  xadj has V+1 entries (xadj[0] == 0, xadj[V] == E); adjwgt may
+ * be NULL (all weights 1).  Adjacency lists must be sorted ascending for node2vec. */
+int skw_graph_upload(skw_ctx* ctx, uint32_t V, uint64_t E, const uint32_t* h_xadj,
+                     const uint32_t* h_adjncy, const float* h_adjwgt);
+/* Use CSR arrays that already live on the GPU (borrowed until the context is destroyed or
+ * another graph is set). */
+int skw_graph_adopt_device(skw_ctx* ctx, uint32_t V, uint64_t E, const uint32_t* d_xadj,
+                           const uint32_t* d_adjncy, const float* d_adjwgt);
+/* Read a Galois .gr (version 1) file and upload it.  Replaces Graph::ReadGraphGR
+ * (include/graph.cuh:164-327): header 4 x u64 {1, sizeEdgeTy, numNode, numEdge}, numNode x u64
+ * end offsets, numEdge x u32 destinations, 4-byte pad when numEdge is odd, numEdge x u32 edge
+ * data converted to float by value.  weight_mode: 0 = from file (--weight), 1 = all ones,
+ * 2 = out-degree of the source (--dw), 3 = seeded uniform in [0, weightrange)
+ * (--randomweight). */
+int skw_graph_load_gr(skw_ctx* ctx, const char* path, int weight_mode, uint32_t weightrange,
+                      uint64_t weight_seed);
+int skw_graph_info(const skw_ctx* ctx, uint32_t* V, uint64_t* E, uint32_t* max_degree);
+/* Copy the resident CSR back to the host (any pointer may be NULL). */
+int skw_graph_download(skw_ctx* ctx, uint32_t* h_xadj, uint32_t* h_adjncy, float* h_adjwgt);
+/* Device addresses of the resident CSR (for callers that keep everything on the GPU). */
+int skw_graph_device_ptrs(const skw_ctx* ctx, const uint32_t** d_xadj,
+                          const uint32_t** d_adjncy, const float** d_adjwgt);
+/* Release the weights after an offline build, as src/createTable.cu:175-177 does. */
+int skw_graph_free_weights(skw_ctx* ctx);
+
+/* Seeded synthetic graphs, generated on the GPU (stand-ins for the datasets of
+ * scripts/fig8_biased.sh:9-24).  R-MAT: 2^scale vertices, raw_edges draws with quadrant
+ * probabilities (a,b,c,1-a-b-c), ids scrambled by a fixed bijection, duplicates and self loops
+ * removed, adjacency sorted; symmetric != 0 adds every reverse edge first.  Weights are
+ * 1 + 9 * k / 2^24 rounded down to a multiple of 2^-20, k a 24-bit Philox draw per edge. */
+int skw_graph_generate_rmat(skw_ctx* ctx, uint32_t scale, uint64_t raw_edges, double a, double b,
+                            double c, int symmetric, uint64_t graph_seed, uint64_t weight_seed);
+/* Power-law graph: vertex v gets target degree min(cap, floor(dmin * u^(-1/(exponent-1)))),
+ * endpoints of raw_edges undirected edges are drawn proportionally to target degree, the edge
+ * set is symmetrised, de-duplicated, self loops dropped, adjacency sorted. */
+int skw_graph_generate_powerlaw(skw_ctx* ctx, uint32_t V, uint64_t raw_edges, double exponent,
+                                double dmin, uint32_t cap, uint64_t graph_seed,
+                                uint64_t weight_seed);
+/* start[i] = mulhi32(philox(seed; id_base + i).x, V): uniformly random start vertices. */
+int skw_generate_starts_device(skw_ctx* ctx, uint64_t n, uint64_t id_base, uint64_t seed,
+                               uint32_t* d_starts);
+
+/* ---------------------------------------------------------------- alias table ------------ */
+
+/* Build the alias table of vertices [v_begin, v_end) from the resident weights.  Replaces
+ * ConstructTable (src/createTable.cu:119-179) and, inside it, loadFromGraph / construct /
+ * constructBC / SaveAliasTable of include/alias_table_new.cuh (1077-1132, 1211-1316, 334-464,
+ * 1105-1115).  The table of a vertex is a pure function of its weight list (see
+ * skw_alias_vertex_spec below), so the result does not depend on scheduling.  *ms receives the
+ * build kernels' time (may be NULL). */
+int skw_alias_build_offline(skw_ctx* ctx, uint32_t v_begin, uint32_t v_end, float* ms);
+/* Copy the table out / in as the reference's two arrays (gpu_graph::prob_array, alias_array,
+ * valid; include/gpu_graph.cuh:40-60): prob[E] float, alias[E] uint32 (index inside the
+ * vertex's list), valid[V] bytes.  Any pointer may be NULL. */
+int skw_alias_export(skw_ctx* ctx, float* h_prob, uint32_t* h_alias, uint8_t* h_valid);
+int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
+                     const uint8_t* h_valid);
+/* Device address of the packed table: E slots of {float prob; uint32 alias} and V valid bytes. */
+int skw_alias_device_ptrs(const skw_ctx* ctx, const void** d_slots, const uint8_t** d_valid);
+
+/* ---------------------------------------------------------------- walks ------------------ */
+
+/* Parameters shared by the walk entry points.  hop_num = walk length + 1 (reference
+ * Jobs_result<RW>::hop_num, include/sampler_result.cuh:459). */
+typedef struct skw_walk_params {
+  uint32_t app;         /* skw_app                                                     */
+  uint32_t mode;        /* skw_mode                                                    */
+  uint32_t hop_num;     /* cells per path row = max steps + 1                          */
+  float tp;             /* PPR termination probability (ignored unless app == PPR)     */
+  float p, q;           /* node2vec hyper-parameters                                   */
+  uint64_t seed;        /* Philox seed                                                 */
+  uint64_t walker_base; /* global id of walker 0 of this call (multi-GPU sharding)     */
+} skw_walk_params;
+
+/* Run n walkers.  Replaces OfflineWalk (src/offline_walk.cu:181-230) for mode OFFLINE and
+ * OnlineWalkShMem / OnlineWalkGMem (src/online_walk.cu:245-327, src/online_walk_gmem.cu) for
+ * mode ONLINE.  Output layout is Jobs_result<RW> (include/sampler_result.cuh:607-612):
+ * paths[w * hop_num + s] = vertex after s steps (s = 0 is the start), lengths[w] = number of
+ * steps taken (= sampled edges of that walker; hop_num - 1 unless the walk met a vertex with
+ * no usable out-edge or PPR stopped it).  Cells after paths[w * hop_num + lengths[w]] are not
+ * written.  *ms = kernel time, *sampled_edges = sum of lengths (both may be NULL). */
+int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_starts,
+                    uint64_t n, uint32_t* d_paths, uint32_t* d_lengths, float* ms,
+                    uint64_t* sampled_edges);
+/* Same with host buffers: copies starts in, runs, copies paths and lengths out. */
+int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+             uint32_t* h_paths, uint32_t* h_lengths, float* ms, uint64_t* sampled_edges);
+
+/* ---------------------------------------------------------------- k-hop sampling --------- */
+
+typedef struct skw_khop_params {
+  uint32_t mode;        /* skw_mode                                                    */
+  uint32_t nhops;       /* number of hops (reference --d), 1..4                         */
+  uint32_t fanout[4];   /* samples per vertex at hop 1..nhops (reference hops[1..])     */
+  uint32_t flags;       /* SKW_KHOP_*                                                  */
+  uint64_t seed;
+  uint64_t instance_base; /* global id of seed vertex 0 of this call                    */
+} skw_khop_params;
+
+/* Cells per seed in `data` (1 + f1 + f1*f2 ...) and in `sample_lengths` (1 + f1 + ... without
+ * the last hop), as Jobs_result<NS>::init computes them (include/sampler_result.cuh:226-260). */
+int skw_khop_layout(const skw_khop_params* prm, uint32_t* cells_per_seed,
+                    uint32_t* lengths_per_seed);
+
+/* Sample the k-hop neighbourhood tree of n seed vertices.  Replaces OfflineSample
+ * (src/offline_sample.cu:443-513) and OnlineGBSampleNew (src/online_sample_new.cu:459-547).
+ * data[s * cells + offset(h) + idx]: the child number j of the vertex at (hop h, idx) is at
+ * (hop h+1, idx * fanout[h+1] + j) (include/sampler_result.cuh:334-352, 421-426);
+ * sample_lengths[s * lens + offset(h) + idx] = children actually sampled from that vertex.
+ * Draws are with replacement.  Cells without a sample hold SKW_INVALID_VERTEX. */
+int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds,
+                           uint64_t n, uint32_t* d_data, uint32_t* d_sample_lengths, float* ms,
+                           uint64_t* sampled_edges);
+int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_seeds, uint64_t n,
+                    uint32_t* h_data, uint32_t* h_sample_lengths, float* ms,
+                    uint64_t* sampled_edges);
+
+/* ---------------------------------------------------------------- host helpers ----------- */
+
+/* Pinned host memory for the h_* buffers (optional; any host pointer is accepted). */
+int skw_host_alloc(size_t bytes, void** out);
+void skw_host_free(void* p);
+
+/* Library version, "major.minor". */
+const char* skw_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SKYWALKER_B200_H */

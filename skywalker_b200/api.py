@@ -1,0 +1,322 @@
+"""Host-side mirror of the reference's operator interface, on top of the C ABI.
+
+The reference drives its kernels through owner objects and free functions that return the kernel
+time in seconds (declarations: include/sampler.cuh:510-529 of the reference):
+
+    Graph, gpu_graph            -> Graph (host CSR) / Context.upload
+    Sampler, Walker             -> Sampler, Walker
+    ConstructTable(sampler)     -> ConstructTable(sampler)
+    OfflineWalk(walker)         -> OfflineWalk(walker)
+    OnlineWalkShMem(walker)     -> OnlineWalkShMem(walker)
+    OfflineSample(sampler)      -> OfflineSample(sampler)
+    OnlineGBSampleNew(sampler)  -> OnlineGBSampleNew(sampler)
+
+Buffers may be numpy arrays (host entry points; copies happen inside the call) or anything with a
+`data_ptr()` method such as a CUDA torch tensor (device entry points; no copies).
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _capi
+from ._capi import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, INVALID_VERTEX, KHOP_TAKE_ALL,
+                    MODE_OFFLINE, MODE_ONLINE, KhopParams, WalkParams)
+
+
+class SkwError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("skywalker_b200 error %d: %s" % (code, msg))
+        self.code = code
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, np.ndarray):
+        if not x.flags["C_CONTIGUOUS"]:
+            raise ValueError("array must be C-contiguous")
+        return C.c_void_p(x.ctypes.data)
+    if hasattr(x, "data_ptr"):
+        return C.c_void_p(x.data_ptr())
+    return C.c_void_p(int(x))
+
+
+def _is_device(x):
+    return hasattr(x, "data_ptr") and getattr(x, "is_cuda", False)
+
+
+class Context:
+    """One GPU.  Owns the resident graph and alias table (reference: gpu_graph + Sampler state)."""
+
+    def __init__(self, device=0):
+        self._lib = _capi.load()
+        h = C.c_void_p()
+        rc = self._lib.skw_ctx_create(device, C.byref(h))
+        if rc:
+            raise SkwError(rc, self._lib.skw_last_global_error().decode())
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.skw_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, rc):
+        if rc:
+            raise SkwError(rc, self._lib.skw_last_error(self._h).decode())
+
+    # -- plumbing
+    def set_stream(self, cuda_stream):
+        self._ck(self._lib.skw_ctx_set_stream(self._h, C.c_void_p(cuda_stream or 0)))
+
+    def synchronize(self):
+        self._ck(self._lib.skw_ctx_synchronize(self._h))
+
+    @property
+    def kernel_launches(self):
+        return int(self._lib.skw_ctx_kernel_launches(self._h))
+
+    # -- graph
+    def upload(self, xadj, adjncy, adjwgt=None):
+        xadj = np.ascontiguousarray(xadj, np.uint32)
+        adjncy = np.ascontiguousarray(adjncy, np.uint32)
+        if adjwgt is not None:
+            adjwgt = np.ascontiguousarray(adjwgt, np.float32)
+        V, E = len(xadj) - 1, len(adjncy)
+        self._ck(self._lib.skw_graph_upload(self._h, V, E, _ptr(xadj), _ptr(adjncy) if E else _ptr(np.zeros(1, np.uint32)),
+                                            _ptr(adjwgt) if adjwgt is not None and E else None))
+
+    def adopt_device(self, V, E, d_xadj, d_adjncy, d_adjwgt=None):
+        self._ck(self._lib.skw_graph_adopt_device(self._h, V, E, _ptr(d_xadj), _ptr(d_adjncy), _ptr(d_adjwgt)))
+
+    def load_gr(self, path, weight_mode=0, weightrange=2, weight_seed=0):
+        self._ck(self._lib.skw_graph_load_gr(self._h, path.encode(), weight_mode, weightrange, weight_seed))
+
+    def generate_rmat(self, scale, raw_edges, a=0.57, b=0.19, c=0.19, symmetric=False, graph_seed=1, weight_seed=7):
+        self._ck(self._lib.skw_graph_generate_rmat(self._h, scale, raw_edges, a, b, c, int(symmetric),
+                                                   graph_seed, weight_seed))
+
+    def generate_powerlaw(self, V, raw_edges, exponent=2.1, dmin=8.0, cap=33000, graph_seed=1, weight_seed=7):
+        self._ck(self._lib.skw_graph_generate_powerlaw(self._h, V, raw_edges, exponent, dmin, cap,
+                                                       graph_seed, weight_seed))
+
+    def graph_info(self):
+        V, E, md = C.c_uint32(), C.c_uint64(), C.c_uint32()
+        self._ck(self._lib.skw_graph_info(self._h, C.byref(V), C.byref(E), C.byref(md)))
+        return V.value, E.value, md.value
+
+    def download(self, weights=True):
+        V, E, _ = self.graph_info()
+        xadj = np.zeros(V + 1, np.uint32)
+        adjncy = np.zeros(max(E, 1), np.uint32)
+        w = np.zeros(max(E, 1), np.float32) if weights else None
+        self._ck(self._lib.skw_graph_download(self._h, _ptr(xadj), _ptr(adjncy), _ptr(w)))
+        return xadj, adjncy[:E], (w[:E] if weights else None)
+
+    def graph_device_ptrs(self):
+        a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        self._ck(self._lib.skw_graph_device_ptrs(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
+
+    def free_weights(self):
+        self._ck(self._lib.skw_graph_free_weights(self._h))
+
+    def generate_starts(self, n, seed, d_out, id_base=0):
+        self._ck(self._lib.skw_generate_starts_device(self._h, n, id_base, seed, _ptr(d_out)))
+
+    # -- alias table
+    def alias_build_offline(self, v_begin=0, v_end=None):
+        """Returns the build kernels' time in milliseconds."""
+        if v_end is None:
+            v_end = self.graph_info()[0]
+        ms = C.c_float()
+        self._ck(self._lib.skw_alias_build_offline(self._h, v_begin, v_end, C.byref(ms)))
+        return ms.value
+
+    def alias_export(self):
+        V, E, _ = self.graph_info()
+        prob = np.zeros(max(E, 1), np.float32)
+        alias = np.zeros(max(E, 1), np.uint32)
+        valid = np.zeros(max(V, 1), np.uint8)
+        self._ck(self._lib.skw_alias_export(self._h, _ptr(prob), _ptr(alias), _ptr(valid)))
+        return prob[:E], alias[:E], valid[:V]
+
+    def alias_import(self, prob, alias, valid):
+        prob = np.ascontiguousarray(prob, np.float32)
+        alias = np.ascontiguousarray(alias, np.uint32)
+        valid = np.ascontiguousarray(valid, np.uint8)
+        pad = lambda a: a if a.size else np.zeros(1, a.dtype)
+        self._ck(self._lib.skw_alias_import(self._h, _ptr(pad(prob)), _ptr(pad(alias)), _ptr(pad(valid))))
+
+    # -- walks
+    def walk(self, starts, hop_num, app=APP_DEEPWALK, mode=MODE_OFFLINE, tp=0.0, p=2.0, q=0.5, seed=42,
+             walker_base=0, paths=None, lengths=None, n=None):
+        """Host arrays (numpy) or device buffers.  Returns (paths, lengths, ms, sampled_edges)."""
+        prm = WalkParams(app, mode, hop_num, tp, p, q, seed, walker_base)
+        ms, edges = C.c_float(), C.c_uint64()
+        if _is_device(starts):
+            n = int(starts.numel()) if n is None else n
+            fn = self._lib.skw_walk_device
+        else:
+            starts = np.ascontiguousarray(starts, np.uint32)
+            n = len(starts) if n is None else n
+            if paths is None:
+                paths = np.full((n, hop_num), INVALID_VERTEX, np.uint32)
+            if lengths is None:
+                lengths = np.zeros(n, np.uint32)
+            fn = self._lib.skw_walk
+        self._ck(fn(self._h, C.byref(prm), _ptr(starts) if n else None, n, _ptr(paths) if n else None,
+                    _ptr(lengths) if n else None, C.byref(ms), C.byref(edges)))
+        return paths, lengths, ms.value, edges.value
+
+    # -- k-hop
+    @staticmethod
+    def khop_layout(fanout):
+        prm = KhopParams(0, len(fanout), (C.c_uint32 * 4)(*(list(fanout) + [0] * (4 - len(fanout)))), 0, 0, 0)
+        cells, lens = C.c_uint32(), C.c_uint32()
+        rc = _capi.load().skw_khop_layout(C.byref(prm), C.byref(cells), C.byref(lens))
+        if rc:
+            raise SkwError(rc, "bad fan-out list %r" % (list(fanout),))
+        return cells.value, lens.value
+
+    def sample_khop(self, seeds, fanout, mode=MODE_OFFLINE, flags=0, seed=42, instance_base=0, data=None,
+                    sample_lengths=None, n=None):
+        """Returns (data[n, cells], sample_lengths[n, lens], ms, sampled_edges)."""
+        cells, lens = self.khop_layout(fanout)
+        prm = KhopParams(mode, len(fanout), (C.c_uint32 * 4)(*(list(fanout) + [0] * (4 - len(fanout)))),
+                         flags, seed, instance_base)
+        ms, edges = C.c_float(), C.c_uint64()
+        if _is_device(seeds):
+            n = int(seeds.numel()) if n is None else n
+            fn = self._lib.skw_sample_khop_device
+        else:
+            seeds = np.ascontiguousarray(seeds, np.uint32)
+            n = len(seeds) if n is None else n
+            if data is None:
+                data = np.zeros((n, cells), np.uint32)
+            if sample_lengths is None:
+                sample_lengths = np.zeros((n, lens), np.uint32)
+            fn = self._lib.skw_sample_khop
+        self._ck(fn(self._h, C.byref(prm), _ptr(seeds) if n else None, n, _ptr(data) if n else None,
+                    _ptr(sample_lengths) if n else None, C.byref(ms), C.byref(edges)))
+        return data, sample_lengths, ms.value, edges.value
+
+
+# ---------------------------------------------------------------------------------------------
+# Reference-shaped surface (names and return values of include/sampler.cuh:510-529).
+
+class Graph:
+    """Host CSR graph (reference: class Graph, include/graph.cuh:47-328)."""
+
+    def __init__(self, xadj, adjncy, adjwgt=None):
+        self.xadj = np.ascontiguousarray(xadj, np.uint32)
+        self.adjncy = np.ascontiguousarray(adjncy, np.uint32)
+        self.adjwgt = None if adjwgt is None else np.ascontiguousarray(adjwgt, np.float32)
+        self.numNode = len(self.xadj) - 1
+        self.numEdge = len(self.adjncy)
+        deg = np.diff(self.xadj.astype(np.int64))
+        self.MaxDegree = int(deg.max()) if len(deg) else 0
+
+
+class Sampler:
+    """Owner of the device graph, the alias table and a k-hop job (reference: Sampler / Sampler_new,
+    include/sampler.cuh:30-400)."""
+
+    def __init__(self, graph, device=0, ctx=None):
+        self.ctx = ctx or Context(device)
+        self.graph = graph
+        if graph is not None:
+            self.ctx.upload(graph.xadj, graph.adjncy, graph.adjwgt)
+        self.sampled_edges = 0
+        self.seeds = None
+        self.hops = None
+        self.result = None
+        self.seed = 42
+        self.flags = KHOP_TAKE_ALL
+
+    def SetSeed(self, seeds, hops, dev_num=1, dev_id=0):
+        """hops = [1, f1, f2, ...] as in the reference (src/main.cu:193-202)."""
+        self.seeds = np.ascontiguousarray(seeds, np.uint32)
+        self.hops = list(hops)
+        self.instance_base = 0
+
+
+class Walker:
+    """Owner of a batch of walks (reference: Walker, include/sampler.cuh:402-508)."""
+
+    def __init__(self, sampler):
+        self.sampler = sampler
+        self.ctx = sampler.ctx
+        self.sampled_edges = 0
+        self.app = APP_DEEPWALK
+        self.tp, self.p, self.q = 0.0, 2.0, 0.5
+        self.seed = 42
+        self.walker_base = 0
+
+    def SetSeed(self, starts, hop_num, dev_num=1, dev_id=0):
+        self.starts = np.ascontiguousarray(starts, np.uint32)
+        self.num_seed = len(self.starts)
+        self.hop_num = hop_num
+        self.result = None
+
+
+class _WalkResult:
+    def __init__(self, data, length):
+        self.data, self.length = data, length
+
+
+class _SampleResult:
+    def __init__(self, data, sample_lengths):
+        self.data, self.sample_lengths = data, sample_lengths
+
+
+def ConstructTable(sampler, ngpu=1, index=0):
+    """Build the alias table of every vertex; returns seconds (src/createTable.cu:119-179)."""
+    return sampler.ctx.alias_build_offline() * 1e-3
+
+
+def _walk(walker, mode):
+    paths, lengths, ms, edges = walker.ctx.walk(walker.starts, walker.hop_num, app=walker.app, mode=mode,
+                                                tp=walker.tp, p=walker.p, q=walker.q, seed=walker.seed,
+                                                walker_base=walker.walker_base)
+    walker.result = _WalkResult(paths, lengths)
+    walker.sampled_edges = edges
+    return ms * 1e-3
+
+
+def OfflineWalk(walker):
+    """src/offline_walk.cu:181-230."""
+    return _walk(walker, MODE_OFFLINE)
+
+
+def OnlineWalkShMem(walker):
+    """src/online_walk.cu:245-327."""
+    return _walk(walker, MODE_ONLINE)
+
+
+OnlineWalkGMem = OnlineWalkShMem  # same result; the reference differs only in scratch placement
+
+
+def _sample(sampler, mode):
+    data, lens, ms, edges = sampler.ctx.sample_khop(sampler.seeds, sampler.hops[1:], mode=mode, flags=sampler.flags,
+                                                    seed=sampler.seed, instance_base=sampler.instance_base)
+    sampler.result = _SampleResult(data, lens)
+    sampler.sampled_edges = edges
+    return ms * 1e-3
+
+
+def OfflineSample(sampler):
+    """src/offline_sample.cu:443-513."""
+    return _sample(sampler, MODE_OFFLINE)
+
+
+def OnlineGBSampleNew(sampler):
+    """src/online_sample_new.cu:459-547."""
+    return _sample(sampler, MODE_ONLINE)

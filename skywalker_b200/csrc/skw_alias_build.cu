@@ -1,0 +1,675 @@
+// Offline alias-table construction for all vertices of a range.
+//
+// Takes over ConstructTable / ConstructAliasTableKernel (src/createTable.cu:48-179 of the
+// reference) and the alias_table_constructor_shmem methods it drives (loadFromGraph, construct,
+// constructBC, SaveAliasTable; include/alias_table_new.cuh:1077-1132, 1211-1316, 334-464,
+// 1105-1115).
+//
+// Construction rule (one vertex, degree n, weights w_0..w_{n-1}; identical to the sequential
+// sweep "smalls in index order are topped up by larges in index order, a large that falls below
+// one bucket is topped up by the next large"):
+//   masses    B = min(40, 62 - ceil(log2 n)), C = 2^B, q_i = trunc(w_i * 2^(B-1-e)) with
+//             e = floor(log2 max w), Q_i = q_0 + .. + q_(i-1), W = Q_n, K = n*C / W (one IEEE
+//             double division), g(Q) = n*C if Q == W else min(n*C, trunc((double)Q * K)),
+//             M_i = g(Q_i + q_i) - g(Q_i).  g is monotone, so zero weights get zero mass and
+//             sum M_i == n*C exactly.
+//   classes   small: M_i < C, large: M_i >= C.
+//   prefixes  D(i) = sum over smalls at positions <= i of (C - M), X(i) = sum over larges at
+//             positions <= i of (M - C)   (both over list positions, zeros elsewhere).
+//   small s   alias = first large l at or after the first position with X >= D(s) - (C - M_s),
+//             prob  = M_s / C.
+//   large l   let S = first position with D(S) > X(l); if none: prob = 1, alias = l; else
+//             prob = (X(l) + C - D(S)) / C, alias = next large after l.
+// Every quantity is an integer or a single correctly rounded IEEE operation, so the table is a
+// pure function of the weight list: no atomics on masses, no dependence on scheduling.
+//
+// Work distribution: vertices are binned by degree into seven classes with warp ballots and
+// shared-memory prefix sums (classify_* kernels); classes of degree <= 32 run one sub-warp
+// group of 4/8/16/32 lanes per vertex entirely in registers, degree <= 1024 and <= 8192 one CTA
+// per vertex with the prefix arrays in shared memory, larger vertices one CTA per vertex with
+// the prefix arrays in a global scratch slab.
+#include <math_constants.h>
+
+#include "skw_ctx.h"
+
+namespace skw {
+
+enum { K_G4 = 0, K_G8, K_G16, K_G32, K_M, K_L, K_H, K_CLASSES };
+constexpr u32 kMediumMax = 1024;
+constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 8192
+
+__device__ __forceinline__ float sane_weight(float w) {
+  return (w > 0.0f && w < CUDART_INF_F) ? w : 0.0f;
+}
+__device__ __forceinline__ int bucket_bits(u32 n) {
+  const int L = n <= 1 ? 0 : 32 - __clz((int)(n - 1));
+  return min(40, 62 - L);
+}
+__device__ __forceinline__ double pow2d(int e) {
+  return __longlong_as_double((long long)(e + 1023) << 52);
+}
+// 2^(B-1-e), e = exponent of the largest weight.
+__device__ __forceinline__ double weight_scale(float wmax, int B) {
+  const int e = (int)((__double_as_longlong((double)wmax) >> 52) & 0x7FF) - 1023;
+  return pow2d(B - 1 - e);
+}
+__device__ __forceinline__ u64 quantise(float w, double scale) {
+  return __double2ull_rz(__dmul_rn((double)w, scale));
+}
+__device__ __forceinline__ double mass_factor(u32 n, int B, u64 W) {
+  return __ddiv_rn(__ull2double_rn((u64)n << B), __ull2double_rn(W));
+}
+// g(Q): cumulative mass up to cumulative quantised weight Q.
+__device__ __forceinline__ u64 cum_mass(u64 Q, u64 W, u64 nC, double K) {
+  if (Q == W) return nC;
+  const u64 g = __double2ull_rz(__dmul_rn(__ull2double_rn(Q), K));
+  return g < nC ? g : nC;
+}
+__device__ __forceinline__ float mass_to_prob(u64 m, int B) {
+  return __double2float_rn(__dmul_rn(__ull2double_rn(m), pow2d(-B)));
+}
+
+__device__ __forceinline__ int degree_class(u32 deg) {
+  if (deg <= 4) return K_G4;
+  if (deg <= 8) return K_G8;
+  if (deg <= 16) return K_G16;
+  if (deg <= 32) return K_G32;
+  if (deg <= kMediumMax) return K_M;
+  if (deg <= kLargeMax) return K_L;
+  return K_H;
+}
+
+// cls[0..K) counts, cls[K..2K) fill cursors, cls[2K..3K) bases of the classes in the work list.
+__global__ void __launch_bounds__(256) classify_count_kernel(const u32* __restrict__ xadj,
+                                                             u32 v_begin, u32 v_end,
+                                                             u32* __restrict__ cls,
+                                                             uint8_t* __restrict__ valid) {
+  __shared__ u32 s_cnt[K_CLASSES];
+  if (threadIdx.x < K_CLASSES) s_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  const u32 lane = threadIdx.x & 31;
+  for (u64 v0 = v_begin + (u64)blockIdx.x * blockDim.x; v0 < v_end; v0 += (u64)gridDim.x * blockDim.x) {
+    const u64 v = v0 + threadIdx.x;
+    int c = -1;
+    if (v < v_end) {
+      const u32 deg = xadj[v + 1] - xadj[v];
+      if (deg == 0) valid[v] = 0;
+      else c = degree_class(deg);
+    }
+#pragma unroll
+    for (int k = 0; k < K_CLASSES; ++k) {
+      const u32 m = __ballot_sync(0xFFFFFFFFu, c == k);
+      if (lane == 0 && m) atomicAdd(&s_cnt[k], __popc(m));
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < K_CLASSES && s_cnt[threadIdx.x]) atomicAdd(&cls[threadIdx.x], s_cnt[threadIdx.x]);
+}
+
+__global__ void classify_bases_kernel(u32* __restrict__ cls) {
+  if (threadIdx.x == 0) {
+    u32 run = 0;
+    for (int k = 0; k < K_CLASSES; ++k) {
+      cls[2 * K_CLASSES + k] = run;
+      cls[K_CLASSES + k] = 0;
+      run += cls[k];
+    }
+  }
+}
+
+// Ordered compaction inside a block (ballot + shared prefix), one atomic per class per block
+// tile to reserve the output range.
+__global__ void __launch_bounds__(256) classify_fill_kernel(const u32* __restrict__ xadj,
+                                                            u32 v_begin, u32 v_end,
+                                                            u32* __restrict__ cls,
+                                                            u32* __restrict__ worklist) {
+  __shared__ u32 s_warp[K_CLASSES][8];
+  __shared__ u32 s_base[K_CLASSES];
+  const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (u64 v0 = v_begin + (u64)blockIdx.x * blockDim.x; v0 < v_end; v0 += (u64)gridDim.x * blockDim.x) {
+    const u64 v = v0 + threadIdx.x;
+    int c = -1;
+    if (v < v_end) {
+      const u32 deg = xadj[v + 1] - xadj[v];
+      if (deg) c = degree_class(deg);
+    }
+    u32 my_rank = 0;
+#pragma unroll
+    for (int k = 0; k < K_CLASSES; ++k) {
+      const u32 m = __ballot_sync(0xFFFFFFFFu, c == k);
+      if (c == k) my_rank = __popc(m & ((1u << lane) - 1u));
+      if (lane == 0) s_warp[k][warp] = __popc(m);
+    }
+    __syncthreads();
+    if (threadIdx.x < K_CLASSES) {
+      u32 run = 0;
+      for (int w = 0; w < 8; ++w) {
+        const u32 t = s_warp[threadIdx.x][w];
+        s_warp[threadIdx.x][w] = run;
+        run += t;
+      }
+      s_base[threadIdx.x] =
+          run ? cls[2 * K_CLASSES + threadIdx.x] + atomicAdd(&cls[K_CLASSES + threadIdx.x], run) : 0;
+    }
+    __syncthreads();
+    if (c >= 0) worklist[s_base[c] + s_warp[c][warp] + my_rank] = (u32)v;
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------ sub-warp groups --------
+template <int G>
+__device__ __forceinline__ u64 group_sum(u64 x) {
+#pragma unroll
+  for (int o = G / 2; o; o >>= 1) x += __shfl_xor_sync(0xFFFFFFFFu, x, o, G);
+  return x;
+}
+template <int G>
+__device__ __forceinline__ u64 group_scan(u64 x, u32 lane) {
+#pragma unroll
+  for (int o = 1; o < G; o <<= 1) {
+    const u64 t = __shfl_up_sync(0xFFFFFFFFu, x, o, G);
+    if (lane >= (u32)o) x += t;
+  }
+  return x;
+}
+
+// One group of G lanes per vertex of degree <= G; lane i owns edge i.
+template <int G>
+__global__ void __launch_bounds__(256) build_group_kernel(const u32* __restrict__ worklist,
+                                                          const u32* __restrict__ cls, int k,
+                                                          const u32* __restrict__ xadj,
+                                                          const float* __restrict__ wgt,
+                                                          Slot* __restrict__ slots,
+                                                          uint8_t* __restrict__ valid,
+                                                          u32* __restrict__ err) {
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  const u32 wlane = threadIdx.x & 31;
+  const u32 lane = wlane & (G - 1);
+  const u32 gshift = wlane & ~(u32)(G - 1);
+  const u32 gmask_all = G == 32 ? 0xFFFFFFFFu : ((1u << G) - 1u);
+  const u32 groups_per_warp = 32 / G;
+  const u32 warp_id = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const u32 nwarps = (gridDim.x * blockDim.x) >> 5;
+  constexpr int B = 40;  // degree <= 32 always gives 40 bucket bits
+  const u64 C = (u64)1 << B;
+  for (u64 it0 = (u64)warp_id * groups_per_warp; it0 < count; it0 += (u64)nwarps * groups_per_warp) {
+    const u64 it = it0 + wlane / G;
+    const bool active = it < count;
+    u32 v = 0, off = 0, n = 0;
+    if (active) {
+      v = worklist[base + it];
+      off = xadj[v];
+      n = xadj[v + 1] - off;
+      if (n > G) {  // classification and kernel disagree: record and skip
+        dev_fail(err, DEV_ERR_INTERNAL, v, n, G);
+        n = 0;
+      }
+    }
+    const bool mine = lane < n;
+    const float w = mine ? sane_weight(__ldg(wgt + off + lane)) : 0.0f;
+    float wmax = w;
+#pragma unroll
+    for (int o = G / 2; o; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xFFFFFFFFu, wmax, o, G));
+    const bool usable = wmax > 0.0f;
+    const double scale = weight_scale(usable ? wmax : 1.0f, B);
+    const u64 q = quantise(w, scale);
+    const u64 Qi = group_scan<G>(q, lane);                         // inclusive
+    const u64 W = __shfl_sync(0xFFFFFFFFu, Qi, G - 1, G);
+    const u64 nC = (u64)n << B;
+    const double K = mass_factor(n ? n : 1, B, W ? W : 1);
+    const u64 m = mine ? cum_mass(Qi, W, nC, K) - cum_mass(Qi - q, W, nC, K) : 0;
+    const bool is_small = mine && m < C;
+    const bool is_large = mine && m >= C;
+    const u32 large_mask = (__ballot_sync(0xFFFFFFFFu, is_large) >> gshift) & gmask_all;
+    const u64 d = is_small ? C - m : 0;
+    const u64 x = is_large ? m - C : 0;
+    const u64 Di = group_scan<G>(d, lane);
+    const u64 Xi = group_scan<G>(x, lane);
+    // first lane whose prefix reaches the target: smalls look in X, larges look in D
+    const u64 target = is_small ? Di - d : Xi + 1;
+    u32 pos = 0;
+#pragma unroll
+    for (int s = G / 2; s; s >>= 1) {
+      const u64 ax = __shfl_sync(0xFFFFFFFFu, Xi, pos + s - 1, G);
+      const u64 ad = __shfl_sync(0xFFFFFFFFu, Di, pos + s - 1, G);
+      if ((is_small ? ax : ad) < target) pos += s;
+    }
+    const u64 ax = __shfl_sync(0xFFFFFFFFu, Xi, pos, G);
+    const u64 ad = __shfl_sync(0xFFFFFFFFu, Di, pos, G);
+    const bool found = (is_small ? ax : ad) >= target;
+    if (mine) {
+      Slot out;
+      if (!usable) {
+        out.prob = -1.0f;  // marks a vertex without usable weight for the draw kernels
+        out.alias = lane;
+      } else if (is_small) {
+        // found is guaranteed by mass conservation; the donor is the first large at or after pos
+        const u32 rest = found ? (large_mask >> pos) : 0u;
+        if (!rest) {
+          dev_fail(err, DEV_ERR_INTERNAL, v, lane, 1);
+          out.alias = lane;
+        } else {
+          out.alias = pos + __ffs(rest) - 1;
+        }
+        out.prob = mass_to_prob(m, B);
+      } else if (!found) {
+        out.prob = 1.0f;
+        out.alias = lane;
+      } else {
+        const u32 rest = lane == 31 ? 0u : (large_mask >> (lane + 1));
+        if (!rest) {
+          dev_fail(err, DEV_ERR_INTERNAL, v, lane, 2);
+          out.alias = lane;
+          out.prob = 1.0f;
+        } else {
+          out.alias = lane + __ffs(rest);
+          out.prob = mass_to_prob(Xi + C - ad, B);
+        }
+      }
+      slots[(u64)off + lane] = out;
+      if (lane == 0) valid[v] = usable ? 1 : 0;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ one CTA per vertex -----
+template <int T>
+__device__ __forceinline__ u64 block_sum(u64 x, u64* s_red) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) x += __shfl_xor_sync(0xFFFFFFFFu, x, o);
+  __syncthreads();  // s_red may still be read from the previous reduction
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  u64 t = 0;
+#pragma unroll
+  for (int w = 0; w < T / 32; ++w) t += s_red[w];
+  return t;
+}
+template <int T>
+__device__ __forceinline__ float block_max(float x, float* s_red) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xFFFFFFFFu, x, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  float t = 0.0f;
+#pragma unroll
+  for (int w = 0; w < T / 32; ++w) t = fmaxf(t, s_red[w]);
+  return t;
+}
+
+// First index in [0, n) with a[i] >= t (a non-decreasing); n when there is none.
+template <typename V>
+__device__ __forceinline__ u32 lower_bound_dev(const V* a, u32 n, V t) {
+  u32 lo = 0, hi = n;
+  while (lo < hi) {
+    const u32 mid = lo + ((hi - lo) >> 1);
+    if (a[mid] < t) lo = mid + 1;
+    else hi = mid;
+  }
+  return lo;
+}
+
+// Builds the table of one vertex with T threads.  D, X (u64) and LR (u32) hold n entries each,
+// in shared memory or in a global slab.
+template <int T>
+__device__ void build_vertex_cta(u32 v, u32 off, u32 n, const float* __restrict__ wgt,
+                                 Slot* __restrict__ slots, uint8_t* __restrict__ valid, u64* D,
+                                 u64* X, u32* LR, u64* s_red, u32* err) {
+  const u32 tid = threadIdx.x;
+  const float* w = wgt + off;
+  float wmax = 0.0f;
+  for (u32 i = tid; i < n; i += T) wmax = fmaxf(wmax, sane_weight(__ldg(w + i)));
+  wmax = block_max<T>(wmax, reinterpret_cast<float*>(s_red));
+  if (!(wmax > 0.0f)) {
+    for (u32 i = tid; i < n; i += T) slots[(u64)off + i] = Slot{-1.0f, i};
+    if (tid == 0) valid[v] = 0;
+    return;
+  }
+  const int B = bucket_bits(n);
+  const u64 C = (u64)1 << B;
+  const double scale = weight_scale(wmax, B);
+  u64 acc = 0;
+  for (u32 i = tid; i < n; i += T) acc += quantise(sane_weight(__ldg(w + i)), scale);
+  const u64 W = block_sum<T>(acc, s_red);
+  const double K = mass_factor(n, B, W);
+  const u64 nC = (u64)n << B;
+
+  // tile-wise inclusive scans: first the quantised weights (-> masses), then deficit, excess and
+  // large count
+  __shared__ u64 s_wq[T / 32], s_wd[T / 32], s_wx[T / 32];
+  __shared__ u32 s_wl[T / 32];
+  __shared__ u64 s_cq, s_cd, s_cx;
+  __shared__ u32 s_cl;
+  if (tid == 0) {
+    s_cq = 0;
+    s_cd = 0;
+    s_cx = 0;
+    s_cl = 0;
+  }
+  __syncthreads();
+  const u32 lane = tid & 31, warp = tid >> 5;
+  for (u32 t0 = 0; t0 < n; t0 += T) {
+    const u32 i = t0 + tid;
+    const u64 q = i < n ? quantise(sane_weight(__ldg(w + i)), scale) : 0;
+    u64 Qi = q;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const u64 tq = __shfl_up_sync(0xFFFFFFFFu, Qi, o);
+      if (lane >= (u32)o) Qi += tq;
+    }
+    if (lane == 31) s_wq[warp] = Qi;
+    __syncthreads();
+    u64 bq = s_cq;
+    for (u32 ww = 0; ww < warp; ++ww) bq += s_wq[ww];
+    Qi += bq;
+    u64 d = 0, x = 0;
+    u32 l = 0;
+    if (i < n) {
+      const u64 m = cum_mass(Qi, W, nC, K) - cum_mass(Qi - q, W, nC, K);
+      if (m < C) d = C - m;
+      else {
+        x = m - C;
+        l = 1;
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const u64 td = __shfl_up_sync(0xFFFFFFFFu, d, o);
+      const u64 tx = __shfl_up_sync(0xFFFFFFFFu, x, o);
+      const u32 tl = __shfl_up_sync(0xFFFFFFFFu, l, o);
+      if (lane >= (u32)o) {
+        d += td;
+        x += tx;
+        l += tl;
+      }
+    }
+    if (lane == 31) {
+      s_wd[warp] = d;
+      s_wx[warp] = x;
+      s_wl[warp] = l;
+    }
+    __syncthreads();
+    u64 bd = s_cd, bx = s_cx;
+    u32 bl = s_cl;
+    for (u32 ww = 0; ww < warp; ++ww) {
+      bd += s_wd[ww];
+      bx += s_wx[ww];
+      bl += s_wl[ww];
+    }
+    if (i < n) {
+      D[i] = d + bd;
+      X[i] = x + bx;
+      LR[i] = l + bl;
+    }
+    __syncthreads();
+    if (tid == T - 1) {
+      s_cq = Qi;
+      s_cd = d + bd;
+      s_cx = x + bx;
+      s_cl = l + bl;
+    }
+    __syncthreads();
+  }
+
+  for (u32 i = tid; i < n; i += T) {
+    const u64 Di = D[i], Xi = X[i];
+    const u64 Dp = i ? D[i - 1] : 0;
+    const u32 Li = LR[i], Lp = i ? LR[i - 1] : 0;
+    Slot out;
+    if (Li == Lp) {  // small
+      const u64 d = Di - Dp;
+      u32 p = Dp ? lower_bound_dev<u64>(X, n, Dp) : lower_bound_dev<u32>(LR, n, 1u);
+      if (p >= n) {
+        dev_fail(err, DEV_ERR_INTERNAL, v, i, 3);
+        p = i;
+      }
+      out.alias = p;
+      out.prob = mass_to_prob(C - d, B);
+    } else {
+      const u32 S = lower_bound_dev<u64>(D, n, Xi + 1);
+      if (S >= n) {
+        out.prob = 1.0f;
+        out.alias = i;
+      } else {
+        u32 nx = lower_bound_dev<u32>(LR, n, Li + 1);
+        if (nx >= n) {
+          dev_fail(err, DEV_ERR_INTERNAL, v, i, 4);
+          nx = i;
+        }
+        out.alias = nx;
+        out.prob = mass_to_prob(Xi + C - D[S], B);
+      }
+    }
+    slots[(u64)off + i] = out;
+  }
+  if (tid == 0) valid[v] = 1;
+}
+
+template <int T, int CAP>
+__global__ void __launch_bounds__(T) build_cta_smem_kernel(const u32* __restrict__ worklist,
+                                                           const u32* __restrict__ cls, int k,
+                                                           const u32* __restrict__ xadj,
+                                                           const float* __restrict__ wgt,
+                                                           Slot* __restrict__ slots,
+                                                           uint8_t* __restrict__ valid,
+                                                           u32* __restrict__ err) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  u64* D = reinterpret_cast<u64*>(smem);
+  u64* X = D + CAP;
+  u32* LR = reinterpret_cast<u32*>(X + CAP);
+  __shared__ u64 s_red[T / 32];
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  for (u32 it = blockIdx.x; it < count; it += gridDim.x) {
+    const u32 v = worklist[base + it];
+    const u32 off = xadj[v], n = xadj[v + 1] - off;
+    if (n > CAP) {
+      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
+      continue;
+    }
+    build_vertex_cta<T>(v, off, n, wgt, slots, valid, D, X, LR, s_red, err);
+    __syncthreads();
+  }
+}
+
+// Vertices above the shared-memory capacity: same construction, prefix arrays in a per-CTA slab
+// of global scratch (slab_elems entries of 20 bytes).
+template <int T>
+__global__ void __launch_bounds__(T) build_cta_gmem_kernel(const u32* __restrict__ worklist,
+                                                           const u32* __restrict__ cls, int k,
+                                                           const u32* __restrict__ xadj,
+                                                           const float* __restrict__ wgt,
+                                                           Slot* __restrict__ slots,
+                                                           uint8_t* __restrict__ valid,
+                                                           unsigned char* __restrict__ scratch,
+                                                           u64 slab_elems, u32* __restrict__ err) {
+  __shared__ u64 s_red[T / 32];
+  unsigned char* slab = scratch + (u64)blockIdx.x * slab_elems * 20ull;
+  u64* D = reinterpret_cast<u64*>(slab);
+  u64* X = D + slab_elems;
+  u32* LR = reinterpret_cast<u32*>(X + slab_elems);
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  for (u32 it = blockIdx.x; it < count; it += gridDim.x) {
+    const u32 v = worklist[base + it];
+    const u32 off = xadj[v], n = xadj[v + 1] - off;
+    if (n > slab_elems) {
+      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)slab_elems);
+      continue;
+    }
+    build_vertex_cta<T>(v, off, n, wgt, slots, valid, D, X, LR, s_red, err);
+    __syncthreads();
+  }
+}
+
+// Launch the seven class builders over work lists laid out as cls describes (counts at [k],
+// bases at [2K + k]).
+static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
+  cudaStream_t st = ctx->stream;
+  constexpr int kLargeSmem = kLargeMax * 20;
+  constexpr int kMediumSmem = kMediumMax * 20;
+  static bool attr_set[64] = {false};
+  if (!attr_set[ctx->device & 63]) {
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_smem_kernel<512, kLargeMax>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kLargeSmem));
+    attr_set[ctx->device & 63] = true;
+  }
+  const int gmem_ctas = ctx->sm_count;
+  const uint64_t slab_elems = ctx->max_degree > kLargeMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
+  if (slab_elems) {
+    int rc = ensure_bytes(ctx, &ctx->cta_scratch, &ctx->cta_scratch_bytes, slab_elems * 20ull * gmem_ctas);
+    if (rc != SKW_OK) return rc;
+  }
+  const int ggrid = ctx->sm_count * 8;
+#define GROUP(GSZ, KCLS)                                                                          \
+  build_group_kernel<GSZ><<<ggrid, 256, 0, st>>>(worklist, cls, KCLS, ctx->xadj, ctx->adjwgt,     \
+                                                 ctx->slots, ctx->valid, ctx->d_err);             \
+  SKW_LAUNCHED(ctx)
+  GROUP(4, K_G4);
+  GROUP(8, K_G8);
+  GROUP(16, K_G16);
+  GROUP(32, K_G32);
+#undef GROUP
+  build_cta_smem_kernel<128, kMediumMax><<<ctx->sm_count * 8, 128, kMediumSmem, st>>>(
+      worklist, cls, K_M, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+  SKW_LAUNCHED(ctx);
+  if (ctx->max_degree > kMediumMax) {
+    build_cta_smem_kernel<512, kLargeMax><<<ctx->sm_count, 512, kLargeSmem, st>>>(
+        worklist, cls, K_L, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  if (slab_elems) {
+    build_cta_gmem_kernel<1024><<<gmem_ctas, 1024, 0, st>>>(
+        worklist, cls, K_H, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid,
+        static_cast<unsigned char*>(ctx->cta_scratch), slab_elems, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  return SKW_OK;
+}
+
+// ------------------------------------------------------------------ online frontier --------
+// Collect the distinct vertices the live units stand on and bin them by degree class.  Unit u
+// reads verts[(u / width) * cells + offs + u % width]; alive (optional) holds kAliveMark for
+// units still running.  A vertex is claimed by the first unit that stamps it this round.
+constexpr u32 kAliveMark = 0xFFFFFFFFu;
+
+__global__ void frontier_reset_kernel(u32* __restrict__ cls, u32 cap) {
+  if (threadIdx.x < K_CLASSES) {
+    cls[threadIdx.x] = 0;
+    cls[K_CLASSES + threadIdx.x] = 0;
+    cls[2 * K_CLASSES + threadIdx.x] = threadIdx.x * cap;
+  }
+}
+
+__global__ void __launch_bounds__(256) frontier_collect_kernel(
+    const u32* __restrict__ verts, u64 units, u32 width, u32 cells, u32 offs,
+    const u32* __restrict__ alive, const u32* __restrict__ xadj, u32 V, u32* __restrict__ stamp,
+    u32 round, u32* __restrict__ cls, u32* __restrict__ lists, u32 cap, u32* __restrict__ err) {
+  const u32 lane = threadIdx.x & 31;
+  const u64 T = (u64)gridDim.x * blockDim.x;
+  for (u64 u0 = (u64)blockIdx.x * blockDim.x; u0 < units; u0 += T) {
+    const u64 u = u0 + threadIdx.x;
+    int c = -1;
+    u32 v = 0;
+    if (u < units && (!alive || alive[u / width] == kAliveMark)) {
+      v = verts[(u / width) * cells + offs + u % width];
+      if (v != 0xFFFFFFFFu) {
+        if (v >= V) {
+          dev_fail(err, DEV_ERR_INDEX, v, (u32)u, 10);
+        } else {
+          const u32 deg = xadj[v + 1] - xadj[v];
+          if (deg && atomicExch(&stamp[v], round) != round) c = degree_class(deg);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < K_CLASSES; ++k) {
+      const u32 m = __ballot_sync(0xFFFFFFFFu, c == k);
+      if (!m) continue;
+      u32 base = 0;
+      if (lane == (u32)(__ffs(m) - 1)) base = atomicAdd(&cls[k], __popc(m));
+      base = __shfl_sync(0xFFFFFFFFu, base, __ffs(m) - 1);
+      if (c == k) {
+        const u32 idx = base + __popc(m & ((1u << lane) - 1u));
+        if (idx < cap) lists[(u64)k * cap + idx] = v;
+        else dev_fail(err, DEV_ERR_CAPACITY, idx, cap, 11);
+      }
+    }
+  }
+}
+
+int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 cells, u32 offs,
+                     const u32* alive_lengths) {
+  if (units > 0xFFFFFFFFull) return fail(ctx, SKW_ERR_ARG, "frontier of %llu units is too large",
+                                         (unsigned long long)units);
+  const u32 cap = (u32)(units < ctx->V ? units : ctx->V);
+  void* p = ctx->frontier_lists;
+  int rc = ensure_bytes(ctx, &p, &ctx->frontier_lists_bytes, sizeof(u32) * (size_t)K_CLASSES * (cap ? cap : 1));
+  ctx->frontier_lists = static_cast<u32*>(p);
+  if (rc != SKW_OK) return rc;
+  if (!ctx->stamp) {
+    SKW_CUDA(ctx, cudaMalloc(&ctx->stamp, sizeof(u32) * ((size_t)ctx->V + 1)));
+    SKW_CUDA(ctx, cudaMemsetAsync(ctx->stamp, 0, sizeof(u32) * ((size_t)ctx->V + 1), ctx->stream));
+    ctx->stamp_round = 0;
+  }
+  if (++ctx->stamp_round == 0) {  // wrapped: forget every old claim
+    SKW_CUDA(ctx, cudaMemsetAsync(ctx->stamp, 0, sizeof(u32) * ((size_t)ctx->V + 1), ctx->stream));
+    ctx->stamp_round = 1;
+  }
+  cudaStream_t st = ctx->stream;
+  frontier_reset_kernel<<<1, 32, 0, st>>>(ctx->frontier_cls, cap);
+  SKW_LAUNCHED(ctx);
+  if (units) {
+    const u64 want = (units + 255) / 256;
+    const int grid = (int)(want < (u64)ctx->sm_count * 8 ? want : (u64)ctx->sm_count * 8);
+    frontier_collect_kernel<<<grid, 256, 0, st>>>(verts, units, width, cells, offs, alive_lengths,
+                                                  ctx->xadj, ctx->V, ctx->stamp, ctx->stamp_round,
+                                                  ctx->frontier_cls, ctx->frontier_lists, cap, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+    rc = launch_builders(ctx, ctx->frontier_lists, ctx->frontier_cls);
+    if (rc != SKW_OK) return rc;
+  }
+  return SKW_OK;
+}
+
+}  // namespace skw
+
+using namespace skw;
+
+extern "C" int skw_alias_build_offline(skw_ctx* ctx, uint32_t v_begin, uint32_t v_end, float* ms) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_alias_build_offline: no graph resident");
+  if (!ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_alias_build_offline: weights were released");
+  if (v_begin > v_end || v_end > ctx->V)
+    return fail(ctx, SKW_ERR_ARG, "skw_alias_build_offline: vertex range [%u,%u) outside [0,%u]",
+                v_begin, v_end, ctx->V);
+  DeviceGuard g(ctx->device);
+  int rc = alloc_table(ctx);
+  if (rc != SKW_OK) return rc;
+  void* wl = ctx->worklist;
+  rc = ensure_bytes(ctx, &wl, &ctx->worklist_cap, sizeof(uint32_t) * ((size_t)ctx->V + 1));
+  ctx->worklist = static_cast<uint32_t*>(wl);
+  if (rc != SKW_OK) return rc;
+  rc = err_reset(ctx);
+  if (rc != SKW_OK) return rc;
+  cudaStream_t st = ctx->stream;
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->cls_counts, 0, 3 * K_CLASSES * sizeof(uint32_t), st));
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+  if (v_end > v_begin) {
+    const int cgrid = ctx->sm_count * 8;
+    classify_count_kernel<<<cgrid, 256, 0, st>>>(ctx->xadj, v_begin, v_end, ctx->cls_counts, ctx->valid);
+    SKW_LAUNCHED(ctx);
+    classify_bases_kernel<<<1, 32, 0, st>>>(ctx->cls_counts);
+    SKW_LAUNCHED(ctx);
+    classify_fill_kernel<<<cgrid, 256, 0, st>>>(ctx->xadj, v_begin, v_end, ctx->cls_counts, ctx->worklist);
+    SKW_LAUNCHED(ctx);
+    rc = launch_builders(ctx, ctx->worklist, ctx->cls_counts);
+    if (rc != SKW_OK) return rc;
+  }
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+  rc = err_check(ctx, "skw_alias_build_offline");
+  if (rc != SKW_OK) return rc;
+  if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+  ctx->table_ready = true;
+  return SKW_OK;
+}

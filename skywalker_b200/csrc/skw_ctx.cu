@@ -1,0 +1,497 @@
+// Context, resident graph, table import/export and the Galois .gr reader.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "skw_ctx.h"
+
+namespace skw {
+
+static std::mutex g_err_mu;
+static std::string g_err;
+
+void set_global_error(const char* msg) {
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  g_err = msg;
+}
+
+int fail(skw_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf;
+  else set_global_error(buf);
+  return code;
+}
+
+int fail_cuda(skw_ctx* ctx, cudaError_t e, const char* what, const char* file, int line) {
+  const char* base = strrchr(file, '/');
+  return fail(ctx, SKW_ERR_CUDA, "%s: %s (%s:%d)", what, cudaGetErrorString(e),
+              base ? base + 1 : file, line);
+}
+
+int ensure_bytes(skw_ctx* ctx, void** p, size_t* cap, size_t want) {
+  if (*cap >= want && *p) return SKW_OK;
+  if (*p) SKW_CUDA(ctx, cudaFree(*p));
+  *p = nullptr;
+  *cap = 0;
+  if (want == 0) want = 256;
+  SKW_CUDA(ctx, cudaMalloc(p, want));
+  *cap = want;
+  return SKW_OK;
+}
+
+int err_reset(skw_ctx* ctx) {
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_err, 0, 4 * sizeof(uint32_t), ctx->stream));
+  return SKW_OK;
+}
+
+int err_check(skw_ctx* ctx, const char* where) {
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, 4 * sizeof(uint32_t),
+                                cudaMemcpyDeviceToHost, ctx->stream));
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->h_err[0] != DEV_OK) {
+    static const char* names[] = {"ok", "index out of range", "bounded wait ran out",
+                                  "capacity exceeded", "construction invariant broken"};
+    const uint32_t c = ctx->h_err[0];
+    return fail(ctx, SKW_ERR_DEVICE, "%s: device error %u (%s), detail %u %u %u", where, c,
+                c < 5 ? names[c] : "?", ctx->h_err[1], ctx->h_err[2], ctx->h_err[3]);
+  }
+  return SKW_OK;
+}
+
+static void free_graph(skw_ctx* ctx) {
+  if (ctx->owns_graph) {
+    cudaFree(ctx->xadj);
+    cudaFree(ctx->adjncy);
+  }
+  if (ctx->owns_weights) cudaFree(ctx->adjwgt);
+  ctx->xadj = ctx->adjncy = nullptr;
+  ctx->adjwgt = nullptr;
+  ctx->owns_graph = ctx->owns_weights = false;
+  cudaFree(ctx->slots);
+  cudaFree(ctx->valid);
+  cudaFree(ctx->stamp);
+  ctx->stamp = nullptr;
+  ctx->stamp_round = 0;
+  ctx->slots = nullptr;
+  ctx->valid = nullptr;
+  ctx->table_ready = false;
+  ctx->V = 0;
+  ctx->E = 0;
+  ctx->max_degree = 0;
+}
+
+__global__ void max_degree_kernel(const uint32_t* __restrict__ xadj, uint32_t V,
+                                  uint32_t* __restrict__ out) {
+  uint32_t m = 0;
+  for (size_t v = blockIdx.x * (size_t)blockDim.x + threadIdx.x; v < V;
+       v += (size_t)gridDim.x * blockDim.x)
+    m = max(m, xadj[v + 1] - xadj[v]);
+  for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+__global__ void fill_ones_kernel(float* __restrict__ w, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    w[i] = 1.0f;
+}
+
+// Weight of every edge = out-degree of its source (reference --dw, include/graph.cuh:299-310).
+__global__ void fill_degree_weights_kernel(const uint32_t* __restrict__ xadj, uint32_t V,
+                                           float* __restrict__ w) {
+  const uint32_t lane = threadIdx.x & 31;
+  const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t v = warp; v < V; v += nwarps) {
+    const uint32_t b = xadj[v], e = xadj[v + 1];
+    const float d = (float)(e - b);
+    for (uint32_t i = b + lane; i < e; i += 32) w[i] = d;
+  }
+}
+
+// Seeded uniform weight in [0, range): the reproducible stand-in for the reference's
+// rand() / (RAND_MAX / weightrange) with srand(0) (include/graph.cuh:210-219).
+__global__ void fill_random_weights_kernel(float* __restrict__ w, size_t n, uint64_t seed,
+                                           float range) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const Rand4 r = philox_tagged(seed, TAG_WGHT, i, 1, 0);
+    w[i] = u01(r.x) * range;
+  }
+}
+
+int finish_graph(skw_ctx* ctx) {
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), ctx->stream));
+  if (ctx->V) {
+    max_degree_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(
+        ctx->xadj, ctx->V, reinterpret_cast<uint32_t*>(ctx->d_sum));
+    SKW_LAUNCHED(ctx);
+  }
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost,
+                                ctx->stream));
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->max_degree = (uint32_t)*ctx->h_sum;
+  return SKW_OK;
+}
+
+int alloc_table(skw_ctx* ctx) {
+  if (!ctx->slots) SKW_CUDA(ctx, cudaMalloc(&ctx->slots, sizeof(Slot) * (ctx->E ? ctx->E : 1)));
+  if (!ctx->valid) {
+    SKW_CUDA(ctx, cudaMalloc(&ctx->valid, ctx->V ? ctx->V : 1));
+    SKW_CUDA(ctx, cudaMemsetAsync(ctx->valid, 0, ctx->V ? ctx->V : 1, ctx->stream));
+  }
+  return SKW_OK;
+}
+
+}  // namespace skw
+
+using namespace skw;
+
+extern "C" {
+
+const char* skw_version(void) { return "0.1"; }
+
+const char* skw_last_global_error(void) {
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  static thread_local std::string copy;
+  copy = g_err;
+  return copy.c_str();
+}
+
+const char* skw_last_error(const skw_ctx* ctx) { return ctx ? ctx->err.c_str() : ""; }
+
+int skw_ctx_create(int device, skw_ctx** out) {
+  if (!out) return fail(nullptr, SKW_ERR_ARG, "skw_ctx_create: out is null");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(nullptr, SKW_ERR_CUDA, "skw_ctx_create: no CUDA device (%s); this library has no CPU path",
+                e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  if (device < 0 || device >= count)
+    return fail(nullptr, SKW_ERR_ARG, "skw_ctx_create: device %d out of range [0,%d)", device, count);
+  skw_ctx* ctx = new skw_ctx();
+  ctx->device = device;
+#define CK(call)                                                                 \
+  do {                                                                           \
+    cudaError_t e2 = (call);                                                     \
+    if (e2 != cudaSuccess) {                                                     \
+      fail(nullptr, SKW_ERR_CUDA, "skw_ctx_create: %s: %s", #call, cudaGetErrorString(e2)); \
+      skw_ctx_destroy(ctx);                                                      \
+      return SKW_ERR_CUDA;                                                       \
+    }                                                                            \
+  } while (0)
+  CK(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CK(cudaGetDeviceProperties(&prop, device));
+  ctx->sm_count = prop.multiProcessorCount;
+  CK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
+  ctx->stream = ctx->own_stream;
+  CK(cudaEventCreate(&ctx->ev0));
+  CK(cudaEventCreate(&ctx->ev1));
+  CK(cudaMalloc(&ctx->d_err, 4 * sizeof(uint32_t)));
+  CK(cudaMemset(ctx->d_err, 0, 4 * sizeof(uint32_t)));
+  CK(cudaMallocHost(&ctx->h_err, 4 * sizeof(uint32_t)));
+  CK(cudaMalloc(&ctx->d_sum, 2 * sizeof(uint64_t)));
+  CK(cudaMallocHost(&ctx->h_sum, 2 * sizeof(uint64_t)));
+  CK(cudaMalloc(&ctx->cls_counts, 64 * sizeof(uint32_t)));
+  CK(cudaMalloc(&ctx->frontier_cls, 64 * sizeof(uint32_t)));
+#undef CK
+  *out = ctx;
+  return SKW_OK;
+}
+
+void skw_ctx_destroy(skw_ctx* ctx) {
+  if (!ctx) return;
+  cudaSetDevice(ctx->device);
+  if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+  free_graph(ctx);
+  cudaFree(ctx->d_err);
+  cudaFreeHost(ctx->h_err);
+  cudaFree(ctx->d_sum);
+  cudaFreeHost(ctx->h_sum);
+  cudaFree(ctx->worklist);
+  cudaFree(ctx->cls_counts);
+  cudaFree(ctx->cta_scratch);
+  cudaFree(ctx->frontier_lists);
+  cudaFree(ctx->frontier_cls);
+  for (int i = 0; i < 4; ++i) cudaFree(ctx->stage[i]);
+  if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+  if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+  delete ctx;
+}
+
+int skw_ctx_set_stream(skw_ctx* ctx, void* cuda_stream) {
+  if (!ctx) return SKW_ERR_ARG;
+  ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+  return SKW_OK;
+}
+
+int skw_ctx_synchronize(skw_ctx* ctx) {
+  if (!ctx) return SKW_ERR_ARG;
+  DeviceGuard g(ctx->device);
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return SKW_OK;
+}
+
+uint64_t skw_ctx_kernel_launches(const skw_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int skw_graph_upload(skw_ctx* ctx, uint32_t V, uint64_t E, const uint32_t* h_xadj,
+                     const uint32_t* h_adjncy, const float* h_adjwgt) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (!h_xadj || (E && !h_adjncy)) return fail(ctx, SKW_ERR_ARG, "skw_graph_upload: null CSR array");
+  if (E > 0xFFFFFFFFull) return fail(ctx, SKW_ERR_ARG, "skw_graph_upload: E must fit 32 bits");
+  if (V == 0xFFFFFFFFu) return fail(ctx, SKW_ERR_ARG, "skw_graph_upload: V too large");
+  if (h_xadj[0] != 0 || h_xadj[V] != E)
+    return fail(ctx, SKW_ERR_ARG, "skw_graph_upload: xadj[0] must be 0 and xadj[V] must equal E");
+  DeviceGuard g(ctx->device);
+  free_graph(ctx);
+  SKW_CUDA(ctx, cudaMalloc(&ctx->xadj, sizeof(uint32_t) * ((size_t)V + 1)));
+  SKW_CUDA(ctx, cudaMalloc(&ctx->adjncy, sizeof(uint32_t) * (E ? E : 1)));
+  SKW_CUDA(ctx, cudaMalloc(&ctx->adjwgt, sizeof(float) * (E ? E : 1)));
+  ctx->owns_graph = ctx->owns_weights = true;
+  ctx->V = V;
+  ctx->E = E;
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->xadj, h_xadj, sizeof(uint32_t) * ((size_t)V + 1),
+                                cudaMemcpyHostToDevice, ctx->stream));
+  if (E) {
+    SKW_CUDA(ctx, cudaMemcpyAsync(ctx->adjncy, h_adjncy, sizeof(uint32_t) * E,
+                                  cudaMemcpyHostToDevice, ctx->stream));
+    if (h_adjwgt) {
+      SKW_CUDA(ctx, cudaMemcpyAsync(ctx->adjwgt, h_adjwgt, sizeof(float) * E,
+                                    cudaMemcpyHostToDevice, ctx->stream));
+    } else {
+      fill_ones_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(ctx->adjwgt, E);
+      SKW_LAUNCHED(ctx);
+    }
+  }
+  return finish_graph(ctx);
+}
+
+int skw_graph_adopt_device(skw_ctx* ctx, uint32_t V, uint64_t E, const uint32_t* d_xadj,
+                           const uint32_t* d_adjncy, const float* d_adjwgt) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (!d_xadj || (E && !d_adjncy))
+    return fail(ctx, SKW_ERR_ARG, "skw_graph_adopt_device: null CSR array");
+  if (E > 0xFFFFFFFFull) return fail(ctx, SKW_ERR_ARG, "skw_graph_adopt_device: E must fit 32 bits");
+  DeviceGuard g(ctx->device);
+  free_graph(ctx);
+  ctx->xadj = const_cast<uint32_t*>(d_xadj);
+  ctx->adjncy = const_cast<uint32_t*>(d_adjncy);
+  ctx->adjwgt = const_cast<float*>(d_adjwgt);
+  ctx->V = V;
+  ctx->E = E;
+  if (!d_adjwgt) {
+    SKW_CUDA(ctx, cudaMalloc(&ctx->adjwgt, sizeof(float) * (E ? E : 1)));
+    ctx->owns_weights = true;
+    fill_ones_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(ctx->adjwgt, E);
+    SKW_LAUNCHED(ctx);
+  }
+  return finish_graph(ctx);
+}
+
+int skw_graph_info(const skw_ctx* ctx, uint32_t* V, uint64_t* E, uint32_t* max_degree) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (V) *V = ctx->V;
+  if (E) *E = ctx->E;
+  if (max_degree) *max_degree = ctx->max_degree;
+  return SKW_OK;
+}
+
+int skw_graph_download(skw_ctx* ctx, uint32_t* h_xadj, uint32_t* h_adjncy, float* h_adjwgt) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_graph_download: no graph resident");
+  DeviceGuard g(ctx->device);
+  if (h_xadj)
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_xadj, ctx->xadj, sizeof(uint32_t) * ((size_t)ctx->V + 1),
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+  if (h_adjncy && ctx->E)
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_adjncy, ctx->adjncy, sizeof(uint32_t) * ctx->E,
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+  if (h_adjwgt && ctx->E) {
+    if (!ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_graph_download: weights were released");
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_adjwgt, ctx->adjwgt, sizeof(float) * ctx->E,
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+  }
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return SKW_OK;
+}
+
+int skw_graph_device_ptrs(const skw_ctx* ctx, const uint32_t** d_xadj, const uint32_t** d_adjncy,
+                          const float** d_adjwgt) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (d_xadj) *d_xadj = ctx->xadj;
+  if (d_adjncy) *d_adjncy = ctx->adjncy;
+  if (d_adjwgt) *d_adjwgt = ctx->adjwgt;
+  return SKW_OK;
+}
+
+int skw_graph_free_weights(skw_ctx* ctx) {
+  if (!ctx) return SKW_ERR_ARG;
+  DeviceGuard g(ctx->device);
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->owns_weights) SKW_CUDA(ctx, cudaFree(ctx->adjwgt));
+  ctx->adjwgt = nullptr;
+  ctx->owns_weights = false;
+  return SKW_OK;
+}
+
+// Galois .gr version 1 (include/graph.cuh:164-327 of the reference).
+int skw_graph_load_gr(skw_ctx* ctx, const char* path, int weight_mode, uint32_t weightrange,
+                      uint64_t weight_seed) {
+  if (!ctx || !path) return SKW_ERR_ARG;
+  FILE* f = fopen(path, "rb");
+  if (!f) return fail(ctx, SKW_ERR_IO, "skw_graph_load_gr: cannot open %s", path);
+  struct Closer {
+    FILE* f;
+    ~Closer() { fclose(f); }
+  } closer{f};
+  uint64_t hdr[4];
+  if (fread(hdr, 8, 4, f) != 4) return fail(ctx, SKW_ERR_IO, "%s: short header", path);
+  if (hdr[0] != 1) return fail(ctx, SKW_ERR_IO, "%s: unsupported .gr version %llu", path,
+                               (unsigned long long)hdr[0]);
+  const uint64_t size_edge_ty = hdr[1], num_node = hdr[2], num_edge = hdr[3];
+  if (num_node >= 0xFFFFFFFFull || num_edge > 0xFFFFFFFFull)
+    return fail(ctx, SKW_ERR_IO, "%s: %llu nodes / %llu edges do not fit 32-bit ids", path,
+                (unsigned long long)num_node, (unsigned long long)num_edge);
+  if (size_edge_ty != 0 && size_edge_ty != 4)
+    return fail(ctx, SKW_ERR_IO, "%s: edge data of %llu bytes is not supported (want 0 or 4)",
+                path, (unsigned long long)size_edge_ty);
+  if (weight_mode == 0 && size_edge_ty != 4)
+    return fail(ctx, SKW_ERR_IO, "%s: file carries no edge data but weights were requested", path);
+  std::vector<uint64_t> ends(num_node);
+  if (num_node && fread(ends.data(), 8, num_node, f) != num_node)
+    return fail(ctx, SKW_ERR_IO, "%s: short offset array", path);
+  std::vector<uint32_t> xadj(num_node + 1);
+  xadj[0] = 0;
+  uint64_t prev = 0;
+  for (uint64_t i = 0; i < num_node; ++i) {
+    if (ends[i] < prev || ends[i] > num_edge)
+      return fail(ctx, SKW_ERR_IO, "%s: offset of node %llu is not monotone / exceeds numEdge",
+                  path, (unsigned long long)i);
+    prev = ends[i];
+    xadj[i + 1] = (uint32_t)ends[i];
+  }
+  if (prev != num_edge)
+    return fail(ctx, SKW_ERR_IO, "%s: last offset %llu differs from numEdge %llu", path,
+                (unsigned long long)prev, (unsigned long long)num_edge);
+  std::vector<uint64_t>().swap(ends);
+  std::vector<uint32_t> adj(num_edge ? num_edge : 1);
+  if (num_edge && fread(adj.data(), 4, num_edge, f) != num_edge)
+    return fail(ctx, SKW_ERR_IO, "%s: short destination array", path);
+  for (uint64_t i = 0; i < num_edge; ++i)
+    if (adj[i] >= num_node)
+      return fail(ctx, SKW_ERR_IO, "%s: destination %u of edge %llu is out of range", path, adj[i],
+                  (unsigned long long)i);
+  std::vector<float> wgt;
+  if (weight_mode == 0) {
+    if (num_edge & 1) {
+      uint32_t pad;
+      if (fread(&pad, 4, 1, f) != 1) return fail(ctx, SKW_ERR_IO, "%s: short padding", path);
+    }
+    std::vector<uint32_t> raw(num_edge ? num_edge : 1);
+    if (num_edge && fread(raw.data(), 4, num_edge, f) != num_edge)
+      return fail(ctx, SKW_ERR_IO, "%s: short edge-data array", path);
+    wgt.resize(num_edge);
+    for (uint64_t i = 0; i < num_edge; ++i) wgt[i] = (float)raw[i];
+  }
+  int rc = skw_graph_upload(ctx, (uint32_t)num_node, num_edge, xadj.data(), adj.data(),
+                            weight_mode == 0 ? wgt.data() : nullptr);
+  if (rc != SKW_OK) return rc;
+  DeviceGuard g(ctx->device);
+  if (weight_mode == 2 && num_edge) {
+    fill_degree_weights_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(ctx->xadj, ctx->V,
+                                                                            ctx->adjwgt);
+    SKW_LAUNCHED(ctx);
+  } else if (weight_mode == 3 && num_edge) {
+    fill_random_weights_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(
+        ctx->adjwgt, num_edge, weight_seed, (float)weightrange);
+    SKW_LAUNCHED(ctx);
+  }
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return SKW_OK;
+}
+
+int skw_alias_export(skw_ctx* ctx, float* h_prob, uint32_t* h_alias, uint8_t* h_valid) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (!ctx->table_ready) return fail(ctx, SKW_ERR_STATE, "skw_alias_export: no table built");
+  DeviceGuard g(ctx->device);
+  if ((h_prob || h_alias) && ctx->E) {
+    std::vector<Slot> tmp(ctx->E);
+    SKW_CUDA(ctx, cudaMemcpyAsync(tmp.data(), ctx->slots, sizeof(Slot) * ctx->E,
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+    SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (uint64_t i = 0; i < ctx->E; ++i) {
+      if (h_prob) h_prob[i] = tmp[i].prob < 0.0f ? 1.0f : tmp[i].prob;  // -1 marks "no usable weight"
+      if (h_alias) h_alias[i] = tmp[i].alias;
+    }
+  }
+  if (h_valid && ctx->V) {
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_valid, ctx->valid, ctx->V, cudaMemcpyDeviceToHost, ctx->stream));
+    SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  }
+  return SKW_OK;
+}
+
+int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
+                     const uint8_t* h_valid) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_alias_import: no graph resident");
+  if (!h_prob || !h_alias || !h_valid) return fail(ctx, SKW_ERR_ARG, "skw_alias_import: null array");
+  DeviceGuard g(ctx->device);
+  int rc = alloc_table(ctx);
+  if (rc != SKW_OK) return rc;
+  std::vector<Slot> tmp(ctx->E ? ctx->E : 1);
+  for (uint64_t i = 0; i < ctx->E; ++i) {
+    tmp[i].prob = h_prob[i];
+    tmp[i].alias = h_alias[i];
+  }
+  {  // a vertex flagged invalid carries prob = -1 in all of its slots: the draw kernels test that
+    std::vector<uint32_t> xadj((size_t)ctx->V + 1);
+    SKW_CUDA(ctx, cudaMemcpyAsync(xadj.data(), ctx->xadj, sizeof(uint32_t) * ((size_t)ctx->V + 1),
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+    SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (uint32_t v = 0; v < ctx->V; ++v)
+      if (!h_valid[v])
+        for (uint32_t i = xadj[v]; i < xadj[v + 1]; ++i) tmp[i].prob = -1.0f;
+  }
+  if (ctx->E)
+    SKW_CUDA(ctx, cudaMemcpyAsync(ctx->slots, tmp.data(), sizeof(Slot) * ctx->E,
+                                  cudaMemcpyHostToDevice, ctx->stream));
+  if (ctx->V)
+    SKW_CUDA(ctx, cudaMemcpyAsync(ctx->valid, h_valid, ctx->V, cudaMemcpyHostToDevice, ctx->stream));
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->table_ready = true;
+  return SKW_OK;
+}
+
+int skw_alias_device_ptrs(const skw_ctx* ctx, const void** d_slots, const uint8_t** d_valid) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (d_slots) *d_slots = ctx->slots;
+  if (d_valid) *d_valid = ctx->valid;
+  return SKW_OK;
+}
+
+int skw_host_alloc(size_t bytes, void** out) {
+  if (!out) return SKW_ERR_ARG;
+  cudaError_t e = cudaMallocHost(out, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    *out = nullptr;
+    return fail(nullptr, SKW_ERR_NOMEM, "skw_host_alloc(%zu): %s", bytes, cudaGetErrorString(e));
+  }
+  return SKW_OK;
+}
+
+void skw_host_free(void* p) {
+  if (p) cudaFreeHost(p);
+}
+
+}  // extern "C"

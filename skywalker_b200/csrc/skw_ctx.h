@@ -1,0 +1,118 @@
+// Host-side state behind the opaque skw_ctx handle, and the helpers every translation unit of
+// the library uses to report errors and count launches.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/skywalker_b200.h"
+#include "skw_device.cuh"
+
+namespace skw {
+
+// Degree classes of the offline builder: a group of 4/8/16/32 lanes per vertex, then one CTA per
+// vertex with its arrays in shared memory, then one CTA per vertex with arrays in global scratch.
+enum { CLS_G4 = 0, CLS_G8, CLS_G16, CLS_G32, CLS_CTA_SMEM, CLS_CTA_GMEM, CLS_COUNT };
+
+// Largest degree the shared-memory CTA builder takes (20 bytes of state per edge).
+constexpr uint32_t kCtaSmemMaxDegree = 8192;
+
+struct WalkRecord;  // skw_walk.cu
+
+}  // namespace skw
+
+struct skw_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::string err;
+  uint64_t launches = 0;
+
+  // resident CSR
+  uint32_t V = 0;
+  uint64_t E = 0;
+  uint32_t max_degree = 0;
+  uint32_t* xadj = nullptr;
+  uint32_t* adjncy = nullptr;
+  float* adjwgt = nullptr;
+  bool owns_graph = false;
+  bool owns_weights = false;
+
+  // alias table
+  skw::Slot* slots = nullptr;
+  uint8_t* valid = nullptr;
+  bool table_ready = false;
+
+  // device error word (4 x u32) and its pinned host mirror
+  uint32_t* d_err = nullptr;
+  uint32_t* h_err = nullptr;
+  // pinned scalar for 64-bit reductions read back after a launch
+  uint64_t* d_sum = nullptr;
+  uint64_t* h_sum = nullptr;
+
+  // builder scratch, grown on demand
+  uint32_t* worklist = nullptr;      // V entries, vertices grouped by degree class
+  size_t worklist_cap = 0;
+  uint32_t* cls_counts = nullptr;    // CLS_COUNT counters + CLS_COUNT cursors + CLS_COUNT bases
+  void* cta_scratch = nullptr;       // slabs of the global-memory CTA builder
+  size_t cta_scratch_bytes = 0;
+
+  // online mode: per-frontier work lists (one per degree class) and the claim stamps that make
+  // every distinct frontier vertex be built once per round
+  uint32_t* frontier_lists = nullptr;
+  size_t frontier_lists_bytes = 0;
+  uint32_t* frontier_cls = nullptr;  // same layout as cls_counts
+  uint32_t* stamp = nullptr;         // V entries, last round that claimed the vertex
+  uint32_t stamp_round = 0;
+
+  // staging buffers of the host-pointer entry points, grown on demand
+  void* stage[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t stage_bytes[4] = {0, 0, 0, 0};
+};
+
+namespace skw {
+
+int fail(skw_ctx* ctx, int code, const char* fmt, ...);
+// after the CSR pointers are set: compute max_degree
+int finish_graph(skw_ctx* ctx);
+// allocate slots[E] / valid[V] if absent
+int alloc_table(skw_ctx* ctx);
+int fail_cuda(skw_ctx* ctx, cudaError_t e, const char* what, const char* file, int line);
+void set_global_error(const char* msg);
+
+// Grow-only device buffer.
+int ensure_bytes(skw_ctx* ctx, void** p, size_t* cap, size_t want);
+// Zero the device error word before a group of launches / check it after synchronising.
+int err_reset(skw_ctx* ctx);
+int err_check(skw_ctx* ctx, const char* where);
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+    else prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace skw
+
+#define SKW_CUDA(ctx, call)                                                          \
+  do {                                                                               \
+    cudaError_t e__ = (call);                                                        \
+    if (e__ != cudaSuccess) return skw::fail_cuda((ctx), e__, #call, __FILE__, __LINE__); \
+  } while (0)
+
+// Count a kernel launch and surface a launch-configuration error at once.
+#define SKW_LAUNCHED(ctx)                                                            \
+  do {                                                                               \
+    (ctx)->launches++;                                                               \
+    cudaError_t e__ = cudaGetLastError();                                            \
+    if (e__ != cudaSuccess) return skw::fail_cuda((ctx), e__, "kernel launch", __FILE__, __LINE__); \
+  } while (0)

@@ -1,0 +1,212 @@
+// k-hop neighbour sampling, offline and online.
+//
+// Takes over OfflineSample / sample_kernel (src/offline_sample.cu:72-141, 443-513 of the
+// reference) and OnlineGBSampleNew / sample_kernel (src/online_sample_new.cu:191-270, 459-547),
+// writing the Jobs_result<NS> tree (include/sampler_result.cuh:226-260, 334-352, 421-426).
+//
+// The reference drains per-hop job queues with one thread (offline) or one warp (online) per
+// frontier vertex.  Here a hop is one launch with one thread per OUTPUT cell: thread
+// (seed s, parent idx, child j) reads the parent vertex, makes its own Philox draw keyed by
+// (seed id, child cell, hop) and stores one coalesced word; no queues and no atomics on the data
+// path.  Online mode first builds the tables of the distinct vertices of the hop's frontier with
+// the degree-bucketed builders, then runs the same draw kernel.
+#include "skw_ctx.h"
+
+namespace skw {
+
+int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 cells, u32 offs,
+                     const u32* alive_lengths);
+
+struct KhopArgs {
+  const u32* xadj;
+  const u32* adjncy;
+  const Slot* slots;
+  u32* data;
+  u32* lens;
+  unsigned long long* sum;
+  u32* err;
+  u64 n;
+  u64 seed;
+  u64 instance_base;
+  u32 V;
+  u32 cells, lens_per;
+  u32 offs_parent, offs_child, width_parent, fanout, hop, flags;
+};
+
+__global__ void __launch_bounds__(256) khop_init_kernel(const u32* __restrict__ seeds, u64 n,
+                                                        u32 cells, u32* __restrict__ data) {
+  for (u64 s = (u64)blockIdx.x * blockDim.x + threadIdx.x; s < n; s += (u64)gridDim.x * blockDim.x)
+    data[s * cells] = seeds[s];
+}
+
+__global__ void __launch_bounds__(256) khop_hop_kernel(const KhopArgs a) {
+  const u64 per_seed = (u64)a.width_parent * a.fanout;
+  const u64 total = a.n * per_seed;
+  u64 got_sum = 0;
+  for (u64 u = (u64)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (u64)gridDim.x * blockDim.x) {
+    const u64 s = u / per_seed;
+    const u32 rem = (u32)(u - s * per_seed);
+    const u32 idx = rem / a.fanout, j = rem - idx * a.fanout;
+    u32* row = a.data + s * a.cells;
+    const u32 v = row[a.offs_parent + idx];
+    u32 out = SKW_INVALID_VERTEX, got = 0;
+    if (v != SKW_INVALID_VERTEX) {
+      if (v >= a.V) {
+        dev_fail(a.err, DEV_ERR_INDEX, v, idx, a.hop);
+      } else {
+        const u32 off = __ldg(a.xadj + v), deg = __ldg(a.xadj + v + 1) - off;
+        if (deg) {
+          if ((a.flags & SKW_KHOP_TAKE_ALL) && a.fanout >= deg) {
+            got = deg;
+            if (j < deg) out = __ldg(a.adjncy + (u64)off + j);
+          } else {
+            const Rand4 r = philox_tagged(a.seed, TAG_KHOP, a.instance_base + s, rem, a.hop);
+            const u32 col = __umulhi(r.x, deg);
+            const Slot sl = load_slot(a.slots + (u64)off + col);
+            if (!(sl.prob < 0.0f)) {
+              const u32 cand = u01(r.y) < sl.prob ? col : sl.alias;
+              out = __ldg(a.adjncy + (u64)off + cand);
+              got = a.fanout;
+            }
+          }
+        }
+      }
+    }
+    row[a.offs_child + rem] = out;
+    if (j == 0) {
+      a.lens[s * a.lens_per + a.offs_parent + idx] = got;
+      got_sum += got;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) got_sum += __shfl_xor_sync(0xFFFFFFFFu, got_sum, o);
+  if ((threadIdx.x & 31) == 0 && got_sum) atomicAdd(a.sum, (unsigned long long)got_sum);
+}
+
+static int khop_check(skw_ctx* ctx, const skw_khop_params* prm) {
+  if (prm->nhops < 1 || prm->nhops > 4) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: nhops must be 1..4");
+  if (prm->mode > SKW_MODE_ONLINE) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: unknown mode %u", prm->mode);
+  u64 w = 1, cells = 1;
+  for (u32 h = 0; h < prm->nhops; ++h) {
+    if (prm->fanout[h] == 0) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: fan-out of hop %u is 0", h + 1);
+    w *= prm->fanout[h];
+    cells += w;
+    if (cells > 0x7FFFFFFFull) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: tree of %llu cells per seed is too large",
+                                            (unsigned long long)cells);
+  }
+  return SKW_OK;
+}
+
+}  // namespace skw
+
+using namespace skw;
+
+extern "C" {
+
+int skw_khop_layout(const skw_khop_params* prm, uint32_t* cells_per_seed, uint32_t* lengths_per_seed) {
+  if (!prm) return SKW_ERR_ARG;
+  int rc = khop_check(nullptr, prm);
+  if (rc != SKW_OK) return rc;
+  uint32_t w = 1, cells = 0, lens = 0;
+  for (uint32_t h = 0; h <= prm->nhops; ++h) {
+    if (h) w *= prm->fanout[h - 1];
+    if (h == prm->nhops) lens = cells;
+    cells += w;
+  }
+  if (cells_per_seed) *cells_per_seed = cells;
+  if (lengths_per_seed) *lengths_per_seed = lens;
+  return SKW_OK;
+}
+
+int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds,
+                           uint64_t n, uint32_t* d_data, uint32_t* d_sample_lengths, float* ms,
+                           uint64_t* sampled_edges) {
+  if (!ctx || !prm) return SKW_ERR_ARG;
+  int rc = khop_check(ctx, prm);
+  if (rc != SKW_OK) return rc;
+  if (n && (!d_seeds || !d_data || !d_sample_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: null buffer");
+  if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: no graph resident");
+  const bool online = prm->mode == SKW_MODE_ONLINE;
+  if (!online && !ctx->table_ready)
+    return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: offline mode needs skw_alias_build_offline or skw_alias_import first");
+  if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: online mode needs the edge weights");
+  DeviceGuard g(ctx->device);
+  if (online && (rc = alloc_table(ctx)) != SKW_OK) return rc;
+  uint32_t width[6], offs[6], cells = 0, w = 1;
+  for (uint32_t h = 0; h <= prm->nhops; ++h) {
+    if (h) w *= prm->fanout[h - 1];
+    width[h] = w;
+    offs[h] = cells;
+    cells += w;
+  }
+  KhopArgs a;
+  a.xadj = ctx->xadj;
+  a.adjncy = ctx->adjncy;
+  a.slots = ctx->slots;
+  a.data = d_data;
+  a.lens = d_sample_lengths;
+  a.sum = reinterpret_cast<unsigned long long*>(ctx->d_sum);
+  a.err = ctx->d_err;
+  a.n = n;
+  a.seed = prm->seed;
+  a.instance_base = prm->instance_base;
+  a.V = ctx->V;
+  a.cells = cells;
+  a.lens_per = offs[prm->nhops];
+  a.flags = prm->flags;
+  cudaStream_t st = ctx->stream;
+  if ((rc = err_reset(ctx)) != SKW_OK) return rc;
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+  if (n) {
+    const uint64_t cap = (uint64_t)ctx->sm_count * 16;
+    uint64_t want = (n + 255) / 256;
+    khop_init_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(d_seeds, n, cells, d_data);
+    SKW_LAUNCHED(ctx);
+    for (uint32_t h = 0; h < prm->nhops; ++h) {
+      if (online && (rc = frontier_collect(ctx, d_data, n * width[h], width[h], cells, offs[h], nullptr)) != SKW_OK)
+        return rc;
+      a.offs_parent = offs[h];
+      a.offs_child = offs[h + 1];
+      a.width_parent = width[h];
+      a.fanout = prm->fanout[h];
+      a.hop = h + 1;
+      want = (n * width[h + 1] + 255) / 256;
+      khop_hop_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
+      SKW_LAUNCHED(ctx);
+    }
+  }
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
+  if ((rc = err_check(ctx, "skw_sample_khop")) != SKW_OK) return rc;
+  if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+  if (sampled_edges) *sampled_edges = *ctx->h_sum;
+  return SKW_OK;
+}
+
+int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_seeds, uint64_t n,
+                    uint32_t* h_data, uint32_t* h_sample_lengths, float* ms, uint64_t* sampled_edges) {
+  if (!ctx || !prm) return SKW_ERR_ARG;
+  uint32_t cells = 0, lens = 0;
+  int rc = skw_khop_layout(prm, &cells, &lens);
+  if (rc != SKW_OK) return fail(ctx, rc, "skw_sample_khop: bad hop description");
+  if (n && (!h_seeds || !h_data || !h_sample_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: null buffer");
+  DeviceGuard g(ctx->device);
+  const size_t nb = sizeof(uint32_t) * (size_t)n;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], nb)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], nb * cells)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], nb * lens)) != SKW_OK) return rc;
+  if (n) SKW_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0], h_seeds, nb, cudaMemcpyHostToDevice, ctx->stream));
+  rc = skw_sample_khop_device(ctx, prm, static_cast<uint32_t*>(ctx->stage[0]), n,
+                              static_cast<uint32_t*>(ctx->stage[1]), static_cast<uint32_t*>(ctx->stage[2]),
+                              ms, sampled_edges);
+  if (rc != SKW_OK) return rc;
+  if (n) {
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_data, ctx->stage[1], nb * cells, cudaMemcpyDeviceToHost, ctx->stream));
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_sample_lengths, ctx->stage[2], nb * lens, cudaMemcpyDeviceToHost, ctx->stream));
+  }
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return SKW_OK;
+}
+
+}  // extern "C"

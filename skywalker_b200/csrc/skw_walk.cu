@@ -1,0 +1,303 @@
+// Random-walk step kernels (DeepWalk / PPR / node2vec), offline and online.
+//
+// Offline: takes over OfflineWalk and sample_kernel_static (src/offline_walk.cu:75-124, 181-230
+// of the reference).  One lane carries one walker at a time through all of its steps and picks
+// up the next walker of its stride when the current one ends, so lanes stay busy when PPR walks
+// stop early; a step is: two offsets, one 8-byte {prob, alias} slot, one neighbour id, one path
+// store.  Online: takes over OnlineWalkShMem / OnlineWalkKernel (src/online_walk.cu:82-166,
+// 245-327): at every step the tables of the vertices the live walkers stand on are built (once
+// per distinct vertex of the frontier, by the degree-bucketed builders of skw_alias_build.cu),
+// then every walker draws from the table of its vertex.
+//
+// Randomness: Philox4x32-10, counter (walker id low, high, step, trial), key seed ^ TAG_WALK;
+// word x -> column (multiply-high by the degree), y -> acceptance uniform, z -> PPR stop test,
+// w -> node2vec rejection uniform.
+#include "skw_ctx.h"
+
+namespace skw {
+
+int build_from_worklists(skw_ctx* ctx, const u32* worklist, const u32* cls);
+int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 cells, u32 offs,
+                     const u32* alive_lengths);
+int alloc_table(skw_ctx* ctx);
+
+constexpr u32 kAlive = 0xFFFFFFFFu;
+constexpr u32 kNoVertex = 0xFFFFFFFFu;
+constexpr u32 kN2vMaxTrials = 64;
+
+struct WalkArgs {
+  const u32* xadj;
+  const u32* adjncy;
+  const Slot* slots;
+  const u32* starts;
+  u32* paths;
+  u32* lengths;
+  unsigned long long* sum;
+  u32* err;
+  u64 n;
+  u64 seed;
+  u64 walker_base;
+  u32 V;
+  u32 hop_num;
+  float tp, inv_p, inv_q, fmax;
+};
+
+// bool CheckConnect(src, dst) of the reference (include/gpu_graph.cuh:204-238): binary search of
+// dst in the sorted adjacency of src.
+__device__ __forceinline__ bool connected(const u32* __restrict__ xadj,
+                                          const u32* __restrict__ adjncy, u32 src, u32 dst) {
+  u32 lo = __ldg(xadj + src), hi = __ldg(xadj + src + 1);
+  while (lo < hi) {
+    const u32 mid = lo + ((hi - lo) >> 1);
+    const u32 x = __ldg(adjncy + mid);
+    if (x == dst) return true;
+    if (x < dst) lo = mid + 1;
+    else hi = mid;
+  }
+  return false;
+}
+
+// One step of one walker standing on `cur`.  Returns false when the walk ends here.
+template <int APP>
+__device__ __forceinline__ bool walk_step(const WalkArgs& a, u64 gw, u32 step, u32 cur, u32 prev,
+                                          u32& next) {
+  Rand4 r = philox_tagged(a.seed, TAG_WALK, gw, step, 0);
+  if (APP == SKW_APP_PPR && u01(r.z) < a.tp) return false;
+  if (cur >= a.V) {
+    dev_fail(a.err, DEV_ERR_INDEX, cur, step, (u32)gw);
+    return false;
+  }
+  const u32 off = __ldg(a.xadj + cur);
+  const u32 deg = __ldg(a.xadj + cur + 1) - off;
+  if (deg == 0) return false;
+  if (APP == SKW_APP_NODE2VEC && prev != kNoVertex) {
+    for (u32 trial = 0;;) {
+      const u32 col = __umulhi(r.x, deg);
+      const Slot s = load_slot(a.slots + (u64)off + col);
+      if (s.prob < 0.0f) return false;  // vertex without usable weight
+      const u32 cand = u01(r.y) < s.prob ? col : s.alias;
+      next = __ldg(a.adjncy + (u64)off + cand);
+      const float f = next == prev ? a.inv_p : (connected(a.xadj, a.adjncy, prev, next) ? 1.0f : a.inv_q);
+      if (__fmul_rn(u01(r.w), a.fmax) < f) break;
+      if (++trial == kN2vMaxTrials) break;  // keep the last proposal
+      r = philox_tagged(a.seed, TAG_WALK, gw, step, trial);
+    }
+    return true;
+  }
+  const u32 col = __umulhi(r.x, deg);
+  const Slot s = load_slot(a.slots + (u64)off + col);
+  if (s.prob < 0.0f) return false;
+  const u32 cand = u01(r.y) < s.prob ? col : s.alias;
+  next = __ldg(a.adjncy + (u64)off + cand);
+  return true;
+}
+
+__device__ __forceinline__ void add_edges(unsigned long long* sum, u64 edges) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) edges += __shfl_xor_sync(0xFFFFFFFFu, edges, o);
+  if ((threadIdx.x & 31) == 0 && edges) atomicAdd(sum, (unsigned long long)edges);
+}
+
+// All steps of all walkers in one launch.  Each lane owns walkers tid, tid + T, tid + 2T ...;
+// the loop body is one step, so lanes of a warp stay converged although their walkers differ.
+template <int APP>
+__global__ void __launch_bounds__(256) walk_offline_kernel(const WalkArgs a) {
+  const u64 T = (u64)gridDim.x * blockDim.x;
+  u64 w = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+  u64 edges = 0;
+  bool have = w < a.n;
+  u32 cur = 0, prev = kNoVertex, step = 0;
+  u32* row = nullptr;
+  if (have) {
+    cur = __ldg(a.starts + w);
+    row = a.paths + w * a.hop_num;
+    row[0] = cur;
+  }
+  while (have) {
+    u32 next = 0;
+    const bool go = step + 1 < a.hop_num && walk_step<APP>(a, a.walker_base + w, step, cur, prev, next);
+    if (go) {
+      ++step;
+      row[step] = next;
+      prev = cur;
+      cur = next;
+    } else {
+      a.lengths[w] = step;
+      edges += step;
+      w += T;
+      have = w < a.n;
+      if (have) {
+        cur = __ldg(a.starts + w);
+        row = a.paths + w * a.hop_num;
+        row[0] = cur;
+        prev = kNoVertex;
+        step = 0;
+      }
+    }
+  }
+  add_edges(a.sum, edges);
+}
+
+// Online mode: start of a run (row[0] = start, length = "alive").
+__global__ void __launch_bounds__(256) walk_online_init_kernel(const WalkArgs a) {
+  for (u64 w = (u64)blockIdx.x * blockDim.x + threadIdx.x; w < a.n; w += (u64)gridDim.x * blockDim.x) {
+    a.paths[w * a.hop_num] = __ldg(a.starts + w);
+    a.lengths[w] = a.hop_num > 1 ? kAlive : 0u;
+  }
+}
+
+// Online mode: one step of every live walker, after the tables of the frontier were built.
+template <int APP>
+__global__ void __launch_bounds__(256) walk_online_step_kernel(const WalkArgs a, u32 step) {
+  u64 edges = 0;
+  for (u64 w = (u64)blockIdx.x * blockDim.x + threadIdx.x; w < a.n; w += (u64)gridDim.x * blockDim.x) {
+    if (a.lengths[w] != kAlive) continue;
+    u32* row = a.paths + w * a.hop_num;
+    const u32 cur = row[step];
+    const u32 prev = (APP == SKW_APP_NODE2VEC && step) ? row[step - 1] : kNoVertex;
+    u32 next = 0;
+    if (walk_step<APP>(a, a.walker_base + w, step, cur, prev, next)) {
+      row[step + 1] = next;
+      if (step + 2 == a.hop_num) {
+        a.lengths[w] = step + 1;
+        edges += step + 1;
+      }
+    } else {
+      a.lengths[w] = step;
+      edges += step;
+    }
+  }
+  add_edges(a.sum, edges);
+}
+
+__global__ void __launch_bounds__(256) generate_starts_kernel(u32* __restrict__ starts, u64 n,
+                                                              u64 id_base, u64 seed, u32 V) {
+  for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (u64)gridDim.x * blockDim.x) {
+    const Rand4 r = philox_tagged(seed, TAG_STRT, id_base + i, 0, 0);
+    starts[i] = __umulhi(r.x, V);
+  }
+}
+
+static int grid_for(const skw_ctx* ctx, u64 n, int per_sm) {
+  const u64 want = (n + 255) / 256;
+  const u64 cap = (u64)ctx->sm_count * per_sm;
+  return (int)(want < cap ? (want ? want : 1) : cap);
+}
+
+}  // namespace skw
+
+using namespace skw;
+
+extern "C" {
+
+int skw_generate_starts_device(skw_ctx* ctx, uint64_t n, uint64_t id_base, uint64_t seed,
+                               uint32_t* d_starts) {
+  if (!ctx || (n && !d_starts)) return SKW_ERR_ARG;
+  if (!ctx->V) return fail(ctx, SKW_ERR_STATE, "skw_generate_starts_device: no graph resident");
+  DeviceGuard g(ctx->device);
+  if (n) {
+    generate_starts_kernel<<<grid_for(ctx, n, 8), 256, 0, ctx->stream>>>(d_starts, n, id_base, seed, ctx->V);
+    SKW_LAUNCHED(ctx);
+  }
+  return SKW_OK;
+}
+
+int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_starts, uint64_t n,
+                    uint32_t* d_paths, uint32_t* d_lengths, float* ms, uint64_t* sampled_edges) {
+  if (!ctx || !prm) return SKW_ERR_ARG;
+  if (n && (!d_starts || !d_paths || !d_lengths))
+    return fail(ctx, SKW_ERR_ARG, "skw_walk: null buffer");
+  if (prm->hop_num < 1) return fail(ctx, SKW_ERR_ARG, "skw_walk: hop_num must be >= 1");
+  if (prm->app > SKW_APP_NODE2VEC) return fail(ctx, SKW_ERR_ARG, "skw_walk: unknown app %u", prm->app);
+  if (prm->mode > SKW_MODE_ONLINE) return fail(ctx, SKW_ERR_ARG, "skw_walk: unknown mode %u", prm->mode);
+  if (prm->app == SKW_APP_PPR && !(prm->tp >= 0.0f && prm->tp <= 1.0f))
+    return fail(ctx, SKW_ERR_ARG, "skw_walk: tp must be in [0,1]");
+  if (prm->app == SKW_APP_NODE2VEC && !(prm->p > 0.0f && prm->q > 0.0f))
+    return fail(ctx, SKW_ERR_ARG, "skw_walk: p and q must be positive");
+  if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_walk: no graph resident");
+  const bool online = prm->mode == SKW_MODE_ONLINE;
+  if (!online && !ctx->table_ready)
+    return fail(ctx, SKW_ERR_STATE, "skw_walk: offline mode needs skw_alias_build_offline or skw_alias_import first");
+  if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_walk: online mode needs the edge weights");
+  DeviceGuard g(ctx->device);
+  int rc;
+  if (online && (rc = alloc_table(ctx)) != SKW_OK) return rc;
+  WalkArgs a;
+  a.xadj = ctx->xadj;
+  a.adjncy = ctx->adjncy;
+  a.slots = ctx->slots;
+  a.starts = d_starts;
+  a.paths = d_paths;
+  a.lengths = d_lengths;
+  a.sum = reinterpret_cast<unsigned long long*>(ctx->d_sum);
+  a.err = ctx->d_err;
+  a.n = n;
+  a.seed = prm->seed;
+  a.walker_base = prm->walker_base;
+  a.V = ctx->V;
+  a.hop_num = prm->hop_num;
+  a.tp = prm->tp;
+  a.inv_p = prm->app == SKW_APP_NODE2VEC ? 1.0f / prm->p : 1.0f;
+  a.inv_q = prm->app == SKW_APP_NODE2VEC ? 1.0f / prm->q : 1.0f;
+  a.fmax = fmaxf(1.0f, fmaxf(a.inv_p, a.inv_q));
+  cudaStream_t st = ctx->stream;
+  if ((rc = err_reset(ctx)) != SKW_OK) return rc;
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+  if (n) {
+    if (!online) {
+      const int grid = grid_for(ctx, n, 8);
+      switch (prm->app) {
+        case SKW_APP_DEEPWALK: walk_offline_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a); break;
+        case SKW_APP_PPR: walk_offline_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a); break;
+        default: walk_offline_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a); break;
+      }
+      SKW_LAUNCHED(ctx);
+    } else {
+      const int grid = grid_for(ctx, n, 8);
+      walk_online_init_kernel<<<grid, 256, 0, st>>>(a);
+      SKW_LAUNCHED(ctx);
+      for (uint32_t step = 0; step + 1 < prm->hop_num; ++step) {
+        if ((rc = frontier_collect(ctx, d_paths, n, 1, prm->hop_num, step, d_lengths)) != SKW_OK) return rc;
+        switch (prm->app) {
+          case SKW_APP_DEEPWALK: walk_online_step_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, step); break;
+          case SKW_APP_PPR: walk_online_step_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, step); break;
+          default: walk_online_step_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a, step); break;
+        }
+        SKW_LAUNCHED(ctx);
+      }
+    }
+  }
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
+  if ((rc = err_check(ctx, "skw_walk")) != SKW_OK) return rc;
+  if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+  if (sampled_edges) *sampled_edges = *ctx->h_sum;
+  return SKW_OK;
+}
+
+int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+             uint32_t* h_paths, uint32_t* h_lengths, float* ms, uint64_t* sampled_edges) {
+  if (!ctx || !prm) return SKW_ERR_ARG;
+  if (n && (!h_starts || !h_paths || !h_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_walk: null buffer");
+  if (prm->hop_num < 1) return fail(ctx, SKW_ERR_ARG, "skw_walk: hop_num must be >= 1");
+  DeviceGuard g(ctx->device);
+  int rc;
+  const size_t nb = sizeof(uint32_t) * (size_t)n;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], nb)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], nb * prm->hop_num)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], nb)) != SKW_OK) return rc;
+  if (n) SKW_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0], h_starts, nb, cudaMemcpyHostToDevice, ctx->stream));
+  rc = skw_walk_device(ctx, prm, static_cast<uint32_t*>(ctx->stage[0]), n,
+                       static_cast<uint32_t*>(ctx->stage[1]), static_cast<uint32_t*>(ctx->stage[2]), ms,
+                       sampled_edges);
+  if (rc != SKW_OK) return rc;
+  if (n) {
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_paths, ctx->stage[1], nb * prm->hop_num, cudaMemcpyDeviceToHost, ctx->stream));
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths, ctx->stage[2], nb, cudaMemcpyDeviceToHost, ctx->stream));
+  }
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return SKW_OK;
+}
+
+}  // extern "C"

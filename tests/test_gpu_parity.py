@@ -1,0 +1,259 @@
+"""GPU parity tests: every entry point of the C ABI against the CPU oracle, bit for bit.
+
+Run on a B200 with `pytest -m gpu`.  Everything goes through libskywalker_b200.so via ctypes.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from skywalker_b200 import APP_DEEPWALK, APP_NODE2VEC, APP_PPR, KHOP_TAKE_ALL, MODE_OFFLINE, MODE_ONLINE
+
+
+def _upload(ctx, g):
+    ctx.upload(g.xadj, g.adjncy, g.adjwgt)
+
+
+def _cmp_walks(paths, lens, opaths, olens):
+    assert np.array_equal(lens, olens)
+    cols = np.arange(paths.shape[1])[None, :]
+    live = cols <= lens[:, None]
+    assert np.array_equal(paths[live], opaths[live])
+
+
+def test_graph_roundtrip(ctx, rmat12):
+    _upload(ctx, rmat12)
+    V, E, md = ctx.graph_info()
+    assert (V, E) == (rmat12.V, rmat12.E)
+    assert md == int(np.diff(rmat12.xadj.astype(np.int64)).max())
+    x, a, w = ctx.download()
+    assert np.array_equal(x, rmat12.xadj) and np.array_equal(a, rmat12.adjncy) and np.array_equal(w, rmat12.adjwgt)
+
+
+def test_rmat_generator_matches_oracle(ctx, oracle):
+    for scale, sym in ((12, False), (14, True)):
+        ctx.generate_rmat(scale, 16 << scale, symmetric=sym, graph_seed=5, weight_seed=6)
+        x, a, w = ctx.download()
+        ox, oa = oracle.gen_rmat(scale, 16 << scale, symmetric=sym, seed=5)
+        assert np.array_equal(x, ox) and np.array_equal(a, oa)
+        assert np.array_equal(w, oracle.gen_weights(len(oa), 6))
+
+
+def test_powerlaw_generator_matches_oracle(ctx, oracle):
+    ctx.generate_powerlaw(20000, 300000, 2.1, 4.0, 3000, graph_seed=5, weight_seed=11)
+    x, a, w = ctx.download()
+    ox, oa = oracle.gen_powerlaw(20000, 300000, 2.1, 4.0, 3000, seed=5)
+    assert np.array_equal(x, ox) and np.array_equal(a, oa)
+    assert np.array_equal(w, oracle.gen_weights(len(oa), 11))
+
+
+def test_starts_match_oracle(ctx, oracle, rmat12):
+    import torch
+    _upload(ctx, rmat12)
+    d = torch.zeros(1000, dtype=torch.int32, device="cuda")
+    ctx.generate_starts(1000, 42, d, id_base=17)
+    ctx.synchronize()
+    got = d.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got, oracle.gen_starts(1000, rmat12.V, 42, id_base=17))
+
+
+@pytest.mark.parametrize("gname", ["rmat12", "rmat16", "plaw"])
+def test_alias_table_bit_exact(ctx, oracle, request, gname):
+    g = request.getfixturevalue(gname)
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    prob, alias, valid = ctx.alias_export()
+    oprob, oalias, ovalid = oracle.alias_build(g.xadj, g.adjwgt)
+    assert np.array_equal(valid, ovalid)
+    assert np.array_equal(alias, oalias)
+    assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
+    assert oracle.alias_reconstruct_maxrel(g.xadj, g.adjwgt, prob, alias, valid) < 1e-6
+
+
+def _star_graph(weights_per_vertex):
+    """Vertex i has the given weight list; all edges point to sink vertices."""
+    degs = [len(w) for w in weights_per_vertex]
+    nsrc = len(degs)
+    maxd = max(degs) if degs else 0
+    V = nsrc + max(maxd, 1)
+    xadj = np.zeros(V + 1, np.uint32)
+    xadj[1:nsrc + 1] = np.cumsum(degs)
+    xadj[nsrc + 1:] = xadj[nsrc]
+    adj = np.concatenate([nsrc + np.arange(d, dtype=np.uint32) for d in degs]) if degs else np.zeros(0, np.uint32)
+    w = np.concatenate([np.asarray(x, np.float32) for x in weights_per_vertex])
+    return xadj, adj.astype(np.uint32), w
+
+
+def test_alias_every_degree_class_and_edge_cases(ctx, oracle):
+    rng = np.random.default_rng(1)
+    lists = []
+    for n in list(range(1, 70)) + [127, 128, 129, 1023, 1024, 1025, 4000, 8192, 8193, 20000, 70000]:
+        lists.append(rng.uniform(1, 10, n).astype(np.float32))
+    lists.append(np.asarray([0.5] * 35 + [2.0] * 5, np.float32))       # reference smoke vector
+    lists.append(np.full(40, 3.0, np.float32))                         # uniform
+    lists.append(np.asarray([1e-3] * 30 + [1000.0], np.float32))       # one dominant
+    lists.append(np.zeros(5, np.float32))                              # all zero -> invalid
+    lists.append(np.zeros(100, np.float32))                            # all zero, CTA class
+    lists.append(np.asarray([0, 1, 2, 0, 5], np.float32))              # zeros inside
+    lists.append(np.asarray([np.nan, -1, np.inf, 2, 3], np.float32))   # unusable entries
+    lists.append((2.0 ** -np.arange(20)).astype(np.float32))           # wide range
+    lists.append(rng.uniform(0, 1, 3000).astype(np.float32) ** 8)      # skewed, many tiny
+    xadj, adj, w = _star_graph(lists)
+    ctx.upload(xadj, adj, w)
+    ctx.alias_build_offline()
+    prob, alias, valid = ctx.alias_export()
+    oprob, oalias, ovalid = oracle.alias_build(xadj, w)
+    assert np.array_equal(valid, ovalid)
+    assert np.array_equal(alias, oalias)
+    assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
+
+
+def test_alias_build_partial_range(ctx, oracle, rmat12):
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline(0, g.V // 2)
+    ctx.alias_build_offline(g.V // 2, g.V)
+    prob, alias, valid = ctx.alias_export()
+    oprob, oalias, ovalid = oracle.alias_build(g.xadj, g.adjwgt)
+    assert np.array_equal(valid, ovalid) and np.array_equal(alias, oalias)
+    assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
+
+
+def test_alias_import_export(ctx, oracle, rmat12):
+    g = rmat12
+    _upload(ctx, g)
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    ctx.alias_import(*table)
+    prob, alias, valid = ctx.alias_export()
+    assert np.array_equal(prob, table[0]) and np.array_equal(alias, table[1]) and np.array_equal(valid, table[2])
+
+
+def test_config1_deepwalk_bit_exact(ctx, oracle, rmat16):
+    """BASELINE config 1: 4,096 walkers, length 80, seed 42, tables from the oracle."""
+    g = rmat16
+    _upload(ctx, g)
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    ctx.alias_import(*table)
+    starts = oracle.gen_starts(4096, g.V, 42)
+    paths, lens, ms, edges = ctx.walk(starts, 81, app=APP_DEEPWALK, seed=42)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 81, seed=42)
+    _cmp_walks(paths, lens, opaths, olens)
+    assert edges == int(olens.sum())
+    # the same through GPU-built tables
+    ctx.alias_build_offline()
+    paths2, lens2, _, _ = ctx.walk(starts, 81, app=APP_DEEPWALK, seed=42)
+    _cmp_walks(paths2, lens2, opaths, olens)
+
+
+@pytest.mark.parametrize("app,kw", [(APP_DEEPWALK, {}), (APP_PPR, {"tp": 0.15}), (APP_NODE2VEC, {"p": 2.0, "q": 0.5}),
+                                    (APP_NODE2VEC, {"p": 0.25, "q": 4.0})])
+@pytest.mark.parametrize("mode", [MODE_OFFLINE, MODE_ONLINE])
+def test_walks_bit_exact(ctx, oracle, plaw, app, kw, mode):
+    g = plaw
+    _upload(ctx, g)
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    if mode == MODE_OFFLINE:
+        ctx.alias_build_offline()
+    starts = oracle.gen_starts(3000, g.V, 7)
+    hop = 41 if app != APP_PPR else 101
+    paths, lens, ms, edges = ctx.walk(starts, hop, app=app, mode=mode, seed=99, walker_base=1000, **kw)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, hop, app=app, seed=99, walker_base=1000,
+                                online=False, **kw)
+    _cmp_walks(paths, lens, opaths, olens)
+    assert edges == int(olens.sum())
+
+
+def test_walk_dead_ends_and_invalid_vertices(ctx, oracle):
+    # 0 -> 1 (weight 0: unusable), 2 -> 3 -> 2 cycle, 4 isolated
+    xadj = np.asarray([0, 1, 1, 2, 3, 3], np.uint32)
+    adj = np.asarray([1, 3, 2], np.uint32)
+    w = np.asarray([0.0, 1.0, 2.0], np.float32)
+    ctx.upload(xadj, adj, w)
+    ctx.alias_build_offline()
+    starts = np.asarray([0, 1, 2, 3, 4], np.uint32)
+    for mode in (MODE_OFFLINE, MODE_ONLINE):
+        paths, lens, _, edges = ctx.walk(starts, 6, mode=mode)
+        assert list(lens) == [0, 0, 5, 5, 0]
+        assert list(paths[2]) == [2, 3, 2, 3, 2, 3]
+        assert edges == 10
+
+
+def test_walk_empty_and_single_hop(ctx, rmat12):
+    _upload(ctx, rmat12)
+    ctx.alias_build_offline()
+    paths, lens, _, edges = ctx.walk(np.zeros(0, np.uint32), 10)
+    assert edges == 0
+    paths, lens, _, edges = ctx.walk(np.asarray([5, 6], np.uint32), 1)
+    assert list(paths[:, 0]) == [5, 6] and list(lens) == [0, 0]
+
+
+def test_walk_sharding_is_invisible(ctx, oracle, rmat12):
+    """Rows do not depend on how walkers are split between calls (multi-GPU sharding rule)."""
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    starts = oracle.gen_starts(2000, g.V, 3)
+    full, flen, _, _ = ctx.walk(starts, 31, app=APP_PPR, tp=0.1, seed=5)
+    a, al, _, _ = ctx.walk(starts[:700], 31, app=APP_PPR, tp=0.1, seed=5, walker_base=0)
+    b, bl, _, _ = ctx.walk(starts[700:], 31, app=APP_PPR, tp=0.1, seed=5, walker_base=700)
+    _cmp_walks(np.vstack([a, b]), np.concatenate([al, bl]), full, flen)
+
+
+@pytest.mark.parametrize("mode", [MODE_OFFLINE, MODE_ONLINE])
+@pytest.mark.parametrize("flags", [0, KHOP_TAKE_ALL])
+def test_khop_bit_exact(ctx, oracle, rmat16, mode, flags):
+    g = rmat16
+    _upload(ctx, g)
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    if mode == MODE_OFFLINE:
+        ctx.alias_build_offline()
+    seeds = oracle.gen_starts(2048, g.V, 11)
+    data, sl, ms, edges = ctx.sample_khop(seeds, [25, 10], mode=mode, flags=flags, seed=77, instance_base=3)
+    odata, osl = oracle.khop(g.xadj, g.adjncy, g.adjwgt, table, seeds, [25, 10], flags=flags, seed=77,
+                             instance_base=3)
+    assert np.array_equal(sl, osl)
+    assert np.array_equal(data, odata)
+    assert edges == int(osl.sum())
+
+
+def test_khop_three_hops_and_layout(ctx, oracle, rmat12):
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    assert ctx.khop_layout([25, 10]) == (276, 26)
+    seeds = oracle.gen_starts(100, g.V, 2)
+    data, sl, _, _ = ctx.sample_khop(seeds, [3, 4, 2])
+    odata, osl = oracle.khop(g.xadj, g.adjncy, g.adjwgt, table, seeds, [3, 4, 2])
+    assert np.array_equal(data, odata) and np.array_equal(sl, osl)
+
+
+def test_chi_square_on_gpu_walks(ctx):
+    from scipy import stats
+    rng = np.random.default_rng(3)
+    for n in (2, 7, 33, 300):
+        w = rng.uniform(1, 10, n).astype(np.float32)
+        xadj = np.asarray([0, n] + [n] * n, np.uint32)
+        adj = np.arange(1, n + 1, dtype=np.uint32)
+        ctx.upload(xadj, adj, w)
+        ctx.alias_build_offline()
+        N = 400000
+        paths, lens, _, _ = ctx.walk(np.zeros(N, np.uint32), 2, seed=n)
+        counts = np.bincount(paths[:, 1].astype(np.int64) - 1, minlength=n)
+        wf = w.astype(np.float64)
+        chi, pval = stats.chisquare(counts, f_exp=wf / wf.sum() * N)
+        assert pval > 0.01, (n, pval)
+
+
+def test_errors_are_reported_not_fatal(ctx, rmat12):
+    from skywalker_b200.api import SkwError
+    _upload(ctx, rmat12)
+    with pytest.raises(SkwError):            # offline walk without a table
+        ctx.walk(np.zeros(4, np.uint32), 5)
+    ctx.alias_build_offline()
+    with pytest.raises(SkwError):            # start vertex out of range: device error word, no fault
+        ctx.walk(np.asarray([rmat12.V + 5], np.uint32), 5)
+    with pytest.raises(SkwError):
+        ctx.alias_build_offline(10, 5)
+    paths, lens, _, _ = ctx.walk(np.asarray([1], np.uint32), 5)   # context still usable
+    assert paths[0, 0] == 1
