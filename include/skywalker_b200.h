@@ -145,6 +145,31 @@ int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
 /* Device address of the packed table: E slots of {float prob; uint32 alias} and V valid bytes. */
 int skw_alias_device_ptrs(const skw_ctx* ctx, const void** d_slots, const uint8_t** d_valid);
 
+/* Alias table of ONE weight list without any allocation.  No counterpart in the reference (its
+ * builders cudaMalloc their scratch per launch, src/createTable.cu:143-159); added for hosts that
+ * cannot allocate device memory when they call: a plug-in inside a process whose framework took
+ * all HBM for its own pool at start-up, or a serving loop that cannot take the device-wide
+ * synchronisation of cudaMalloc / cudaFree on its request path.
+ *   d_weights[n]  device, float    the weight list (same rules as an adjacency list's weights)
+ *   d_slots[n]    device, 8 bytes each, 8-byte aligned: {float prob; uint32 alias}; prob = -1 in
+ *                 every slot when no weight is usable
+ *   d_valid[1]    device, 1 if the list has a usable weight, else 0
+ *   cuda_stream   a cudaStream_t (NULL = legacy default stream); the call returns after the
+ *                 stream has finished the build
+ *   errbuf        optional caller buffer that receives the text of a failure
+ * All buffers belong to the caller and to the CURRENT device of the calling thread.  n must be
+ * 1 .. 131072: the prefix arrays (20 bytes per weight) live in a 2.5 MiB array inside the library
+ * image, present on every GPU that loads the library until the process exits; longer lists are
+ * rejected with SKW_ERR_ARG.  The result is bit-identical to what skw_alias_build_offline writes
+ * for a vertex with this weight list.
+ * The first call on a device looks up the array's device address; make that first call outside
+ * any stream capture.  Every call uses the same array, which keeps whatever the previous call
+ * left (the call clears the part that must start at zero): two calls whose kernels can overlap
+ * on the GPU (different streams, different threads) race on it and must be serialised by the
+ * caller.  The function calls no cudaMalloc / cudaFree and no allocating library routine. */
+int skw_alias_build_list_static(const float* d_weights, uint32_t n, void* d_slots, uint8_t* d_valid,
+                                void* cuda_stream, char* errbuf, size_t errbuf_len);
+
 /* ---------------------------------------------------------------- walks ------------------ */
 
 /* Parameters shared by the walk entry points.  hop_num = walk length + 1 (reference

@@ -30,6 +30,10 @@
 // the prefix arrays in a global scratch slab.
 #include <math_constants.h>
 
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
 #include "skw_ctx.h"
 
 namespace skw {
@@ -671,5 +675,111 @@ extern "C" int skw_alias_build_offline(skw_ctx* ctx, uint32_t v_begin, uint32_t 
   if (rc != SKW_OK) return rc;
   if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
   ctx->table_ready = true;
+  return SKW_OK;
+}
+
+// ------------------------------------------------------------------ allocation-free variant --
+// skw_alias_build_list_static: the table of ONE weight list, for hosts that must not allocate
+// device memory at the time of the call.  Two kinds of caller are meant: a sampler plugged into a
+// process whose framework reserved the whole HBM for its own pooling allocator at start-up (a raw
+// cudaMalloc from a plug-in then fails, or takes memory behind the pool's back), and a serving
+// loop that cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply on its
+// request path.  The prefix arrays the CTA builder needs (20 bytes per edge) therefore live in a
+// fixed array inside the library image instead of a slab allocated on demand.
+namespace skw {
+
+constexpr u32 kStaticMaxDegree = 131072;  // longest weight list the static scratch holds
+constexpr size_t kStaticHeader = 256;     // error record, kept apart from the arrays
+// 256 B + 131072 * 20 B = 2,621,696 bytes of device memory on every GPU that loads the library,
+// held until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticHeader + (size_t)kStaticMaxDegree * 20];
+
+// Same construction as build_cta_gmem_kernel, for the single list wgt[0..n), with the prefix arrays
+// at `scratch` (the device address of g_static_scratch, looked up by the host).
+__global__ void __launch_bounds__(1024) build_list_static_kernel(const float* __restrict__ wgt, u32 n,
+                                                                 Slot* __restrict__ slots,
+                                                                 uint8_t* __restrict__ valid,
+                                                                 unsigned char* __restrict__ scratch) {
+  __shared__ u64 s_red[1024 / 32];
+  u32* err = reinterpret_cast<u32*>(scratch);
+  u64* D = reinterpret_cast<u64*>(scratch + kStaticHeader);
+  u64* X = D + kStaticMaxDegree;
+  u32* LR = reinterpret_cast<u32*>(X + kStaticMaxDegree);
+  build_vertex_cta<1024>(0, 0, n, wgt, slots, valid, D, X, LR, s_red, err);
+}
+
+static std::mutex g_static_mu;
+static unsigned char* g_static_ptr[64] = {nullptr};  // device address of the array, per device
+
+static int static_fail(char* buf, size_t len, int code, const char* fmt, ...) {
+  if (buf && len) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, len, fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+}  // namespace skw
+
+extern "C" int skw_alias_build_list_static(const float* d_weights, uint32_t n, void* d_slots,
+                                           uint8_t* d_valid, void* cuda_stream, char* errbuf,
+                                           size_t errbuf_len) {
+  if (errbuf && errbuf_len) errbuf[0] = 0;
+  if (!d_weights || !d_slots || !d_valid)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_ARG, "skw_alias_build_list_static: null buffer");
+  if (n == 0) return static_fail(errbuf, errbuf_len, SKW_ERR_ARG, "skw_alias_build_list_static: empty weight list");
+  if (n > kStaticMaxDegree)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_ARG,
+                       "skw_alias_build_list_static: %u weights exceed the static scratch, which holds %u "
+                       "(use skw_alias_build_offline for longer lists)", n, kStaticMaxDegree);
+  if ((reinterpret_cast<uintptr_t>(d_slots) & 7u) || (reinterpret_cast<uintptr_t>(d_weights) & 3u))
+    return static_fail(errbuf, errbuf_len, SKW_ERR_ARG, "skw_alias_build_list_static: misaligned buffer");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_CUDA, "skw_alias_build_list_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_ARG, "skw_alias_build_list_static: device %d not supported", dev);
+  cudaPointerAttributes at;
+  e = cudaPointerGetAttributes(&at, d_weights);
+  if (e != cudaSuccess || at.type != cudaMemoryTypeDevice || at.device != dev) {
+    cudaGetLastError();
+    return static_fail(errbuf, errbuf_len, SKW_ERR_ARG,
+                       "skw_alias_build_list_static: d_weights is not device memory of the current device %d", dev);
+  }
+  unsigned char* scratch = nullptr;
+  {
+    // First call on this device: ask the runtime where the array lives on it.  The array's name is
+    // only a host-side handle; the kernel must be given this looked-up address.
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || !p)
+        return static_fail(errbuf, errbuf_len, SKW_ERR_CUDA, "skw_alias_build_list_static: cudaGetSymbolAddress: %s",
+                           cudaGetErrorString(e));
+      g_static_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    scratch = g_static_ptr[dev];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  // the error record must start at zero; the prefix arrays are fully rewritten before they are read
+  e = cudaMemsetAsync(scratch, 0, kStaticHeader, st);
+  if (e != cudaSuccess)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_CUDA, "skw_alias_build_list_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  build_list_static_kernel<<<1, 1024, 0, st>>>(d_weights, n, static_cast<Slot*>(d_slots), d_valid, scratch);
+  e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_CUDA, "skw_alias_build_list_static: launch: %s", cudaGetErrorString(e));
+  uint32_t rec[4] = {0, 0, 0, 0};
+  e = cudaMemcpyAsync(rec, scratch, sizeof rec, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_CUDA, "skw_alias_build_list_static: %s", cudaGetErrorString(e));
+  if (rec[0] != DEV_OK)
+    return static_fail(errbuf, errbuf_len, SKW_ERR_DEVICE,
+                       "skw_alias_build_list_static: device error %u, detail %u %u %u", rec[0], rec[1], rec[2], rec[3]);
   return SKW_OK;
 }
