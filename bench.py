@@ -160,6 +160,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-records", action="store_true", help="walk over the 8-byte slot table only")
     ap.add_argument("--cpu-threads", type=int, default=0)
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
@@ -246,6 +247,16 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the same walks over the plain 8-byte slot table first (3 accesses per step), for comparison
+    slots_ms, slots_edges = [], 0
+    for i in range(args.warmup + 2):
+        _, _, ms, edges = step(100 + i)
+        if i >= args.warmup:
+            slots_ms.append(ms)
+            slots_edges += edges
+    records_build_ms = None
+    if not args.no_records:
+        records_build_ms = ctx.walk_records_build()
     for i in range(args.warmup):
         step(i)
     sampler = ClockSampler(local_rank)
@@ -353,7 +364,12 @@ def main():
                                          "peak": peak, "unit": "GB/s",
                                          "frac": E * ALG_BYTES_PER_BUILD_EDGE / (build_best * 1e-3) / 1e9 / peak,
                                          "peak_kind": peak_kind}},
-            "roofline": {"bound": "hbm", "kernel": "walk_offline_kernel", "achieved": achieved, "peak": peak,
+            "layout": "8-byte slots" if args.no_records else "fused 32-byte walk records",
+            "walk_records_build_ms": records_build_ms,
+            "slots_layout": {"kernel_ms_per_step": float(np.mean(slots_ms)),
+                             "value": slots_edges / (sum(slots_ms) * 1e-3) if slots_ms else None,
+                             "unit": "sampled edges/s (this rank, kernel time)"},
+            "roofline": {"bound": "hbm", "kernel": "walk_offline_kernel" if args.no_records else "walk_records_walk_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
                          "algorithmic_bytes_per_sampled_edge": ALG_BYTES_PER_EDGE},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,

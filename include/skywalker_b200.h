@@ -184,6 +184,16 @@ typedef struct skw_walk_params {
   uint64_t walker_base; /* global id of walker 0 of this call (multi-GPU sharding)     */
 } skw_walk_params;
 
+/* Optional wider layout of the same table for offline DeepWalk / PPR.  No counterpart in the
+ * reference (whose step reads xadj, prob_array, alias_array and adjncy separately,
+ * src/offline_walk.cu:89-112).  Derives from the alias table one 32-byte record per edge slot
+ * {prob, neighbour-if-kept, its offset, its usable degree, neighbour-via-alias, its offset, its
+ * usable degree, alias} (32 B x E of device memory, plus 8 B x V), so that a step is a single
+ * random 32-byte access.  Once built, skw_walk* use it for offline DeepWalk and PPR; walks are
+ * bit-identical with and without it.  Must be rebuilt after the table changes. */
+int skw_walk_records_build(skw_ctx* ctx, float* ms);
+int skw_walk_records_free(skw_ctx* ctx);
+
 /* Run n walkers.  Replaces OfflineWalk (src/offline_walk.cu:181-230) for mode OFFLINE and
  * OnlineWalkShMem / OnlineWalkGMem (src/online_walk.cu:245-327, src/online_walk_gmem.cu) for
  * mode ONLINE.  Output layout is Jobs_result<RW> (include/sampler_result.cuh:607-612):

@@ -155,6 +155,15 @@ class Context:
         pad = lambda a: a if a.size else np.zeros(1, a.dtype)
         self._ck(self._lib.skw_alias_import(self._h, _ptr(pad(prob)), _ptr(pad(alias)), _ptr(pad(valid))))
 
+    def walk_records_build(self):
+        """Build the fused 32-byte walk records from the alias table; returns milliseconds."""
+        ms = C.c_float()
+        self._ck(self._lib.skw_walk_records_build(self._h, C.byref(ms)))
+        return ms.value
+
+    def walk_records_free(self):
+        self._ck(self._lib.skw_walk_records_free(self._h))
+
     # -- walks
     def walk(self, starts, hop_num, app=APP_DEEPWALK, mode=MODE_OFFLINE, tp=0.0, p=2.0, q=0.5, seed=42,
              walker_base=0, paths=None, lengths=None, n=None):

@@ -648,6 +648,7 @@ extern "C" int skw_alias_build_offline(skw_ctx* ctx, uint32_t v_begin, uint32_t 
     return fail(ctx, SKW_ERR_ARG, "skw_alias_build_offline: vertex range [%u,%u) outside [0,%u]",
                 v_begin, v_end, ctx->V);
   DeviceGuard g(ctx->device);
+  drop_records(ctx);
   int rc = alloc_table(ctx);
   if (rc != SKW_OK) return rc;
   void* wl = ctx->worklist;

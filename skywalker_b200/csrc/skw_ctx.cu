@@ -77,6 +77,10 @@ static void free_graph(skw_ctx* ctx) {
   cudaFree(ctx->slots);
   cudaFree(ctx->valid);
   cudaFree(ctx->stamp);
+  cudaFree(ctx->records);
+  cudaFree(ctx->vinfo);
+  ctx->records = nullptr;
+  ctx->vinfo = nullptr;
   ctx->stamp = nullptr;
   ctx->stamp_round = 0;
   ctx->slots = nullptr;
@@ -139,6 +143,14 @@ int finish_graph(skw_ctx* ctx) {
   SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   ctx->max_degree = (uint32_t)*ctx->h_sum;
   return SKW_OK;
+}
+
+void drop_records(skw_ctx* ctx) {
+  if (ctx->records || ctx->vinfo) cudaStreamSynchronize(ctx->stream);
+  cudaFree(ctx->records);
+  cudaFree(ctx->vinfo);
+  ctx->records = nullptr;
+  ctx->vinfo = nullptr;
 }
 
 int alloc_table(skw_ctx* ctx) {
@@ -447,6 +459,7 @@ int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
   if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_alias_import: no graph resident");
   if (!h_prob || !h_alias || !h_valid) return fail(ctx, SKW_ERR_ARG, "skw_alias_import: null array");
   DeviceGuard g(ctx->device);
+  drop_records(ctx);
   int rc = alloc_table(ctx);
   if (rc != SKW_OK) return rc;
   std::vector<Slot> tmp(ctx->E ? ctx->E : 1);

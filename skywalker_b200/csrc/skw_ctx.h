@@ -45,6 +45,9 @@ struct skw_ctx {
   skw::Slot* slots = nullptr;
   uint8_t* valid = nullptr;
   bool table_ready = false;
+  // optional fused walk records (32 B per edge slot) and per-vertex {offset, usable degree}
+  void* records = nullptr;
+  void* vinfo = nullptr;
 
   // device error word (4 x u32) and its pinned host mirror
   uint32_t* d_err = nullptr;
@@ -80,6 +83,8 @@ int fail(skw_ctx* ctx, int code, const char* fmt, ...);
 int finish_graph(skw_ctx* ctx);
 // allocate slots[E] / valid[V] if absent
 int alloc_table(skw_ctx* ctx);
+// forget the fused walk records (they are derived from the table and die with it)
+void drop_records(skw_ctx* ctx);
 int fail_cuda(skw_ctx* ctx, cudaError_t e, const char* what, const char* file, int line);
 void set_global_error(const char* msg);
 

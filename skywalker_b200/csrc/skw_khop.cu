@@ -131,7 +131,10 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
     return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: offline mode needs skw_alias_build_offline or skw_alias_import first");
   if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: online mode needs the edge weights");
   DeviceGuard g(ctx->device);
-  if (online && (rc = alloc_table(ctx)) != SKW_OK) return rc;
+  if (online) {
+    drop_records(ctx);  // online builds overwrite table slots
+    if ((rc = alloc_table(ctx)) != SKW_OK) return rc;
+  }
   uint32_t width[6], offs[6], cells = 0, w = 1;
   for (uint32_t h = 0; h <= prm->nhops; ++h) {
     if (h) w *= prm->fanout[h - 1];

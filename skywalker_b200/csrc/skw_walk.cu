@@ -170,6 +170,140 @@ __global__ void __launch_bounds__(256) walk_online_step_kernel(const WalkArgs a,
   add_edges(a.sum, edges);
 }
 
+// ------------------------------------------------------------------ fused walk records -----
+// B200 has room for a wider table: one 32-byte record per edge slot that already holds both
+// outcomes of the draw together with what the NEXT step needs (offset and degree of the vertex
+// reached), so a step is ONE random 32-byte access (one 256-bit load) instead of three dependent
+// ones (offsets -> slot -> neighbour id).  Random DRAM accesses per step, not bytes, bound the
+// walk on this memory system, so this is worth 4x the table size.  The records are derived from
+// the alias table and the CSR and give bit-identical walks.
+//   w0 prob | w1 neighbour if kept | w2 its first-edge offset | w3 its usable degree
+//           | w4 neighbour via alias | w5 its offset          | w6 its usable degree | w7 alias
+// "usable degree" is 0 for a vertex without out-edges or without usable weight: the walk ends there.
+struct __align__(32) WalkRecord {
+  u32 w[8];
+};
+
+__device__ __forceinline__ void load_record(const WalkRecord* p, u32 (&w)[8]) {
+  asm volatile("ld.global.nc.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(p));
+}
+
+// vinfo[v] = {first-edge offset, usable degree}
+__global__ void __launch_bounds__(256) vertex_info_kernel(const u32* __restrict__ xadj,
+                                                          const Slot* __restrict__ slots, u32 V,
+                                                          uint2* __restrict__ vinfo) {
+  for (u64 v = (u64)blockIdx.x * blockDim.x + threadIdx.x; v < V; v += (u64)gridDim.x * blockDim.x) {
+    const u32 off = xadj[v], deg = xadj[v + 1] - off;
+    u32 eff = deg;
+    if (deg && load_slot(slots + off).prob < 0.0f) eff = 0;
+    vinfo[v] = make_uint2(off, eff);
+  }
+}
+
+// One thread per edge slot e: find the first-edge offset of its source vertex by binary search
+// in xadj, then gather both outcomes.
+__global__ void __launch_bounds__(256) walk_records_kernel(const u32* __restrict__ xadj,
+                                                           const u32* __restrict__ adjncy,
+                                                           const Slot* __restrict__ slots,
+                                                           const uint2* __restrict__ vinfo, u32 V,
+                                                           u64 E, WalkRecord* __restrict__ rec) {
+  for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (u64)gridDim.x * blockDim.x) {
+    u32 lo = 0, hi = V;  // last v with xadj[v] <= e
+    while (lo < hi) {
+      const u32 mid = lo + ((hi - lo + 1) >> 1);
+      if (__ldg(xadj + mid) <= (u32)e) lo = mid;
+      else hi = mid - 1;
+    }
+    const u32 off = __ldg(xadj + lo);
+    const Slot s = load_slot(slots + e);
+    const u32 n_self = __ldg(adjncy + e);
+    const u32 n_alias = __ldg(adjncy + (u64)off + s.alias);
+    const uint2 i_self = __ldg(vinfo + n_self);
+    const uint2 i_alias = __ldg(vinfo + n_alias);
+    uint4 a, b;
+    a.x = __float_as_uint(s.prob);
+    a.y = n_self;
+    a.z = i_self.x;
+    a.w = i_self.y;
+    b.x = n_alias;
+    b.y = i_alias.x;
+    b.z = i_alias.y;
+    b.w = s.alias;
+    uint4* out = reinterpret_cast<uint4*>(rec + e);
+    out[0] = a;
+    out[1] = b;
+  }
+}
+
+struct RecordWalkArgs {
+  const WalkRecord* rec;
+  const uint2* vinfo;
+  const u32* starts;
+  u32* paths;
+  u32* lengths;
+  unsigned long long* sum;
+  u32* err;
+  u64 n;
+  u64 seed;
+  u64 walker_base;
+  u32 V;
+  u32 hop_num;
+  float tp;
+};
+
+// Same lane-owns-a-stride loop as walk_offline_kernel; a step is one record load.
+template <int APP>
+__global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalkArgs a) {
+  const u64 T = (u64)gridDim.x * blockDim.x;
+  u64 w = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+  u64 edges = 0;
+  bool have = w < a.n;
+  u32 off = 0, deg = 0, step = 0;
+  u32* row = nullptr;
+  auto begin = [&]() {
+    const u32 cur = __ldg(a.starts + w);
+    row = a.paths + w * a.hop_num;
+    row[0] = cur;
+    step = 0;
+    if (cur >= a.V) {
+      dev_fail(a.err, DEV_ERR_INDEX, cur, 0, (u32)w);
+      off = 0;
+      deg = 0;
+    } else {
+      const uint2 vi = __ldg(a.vinfo + cur);
+      off = vi.x;
+      deg = vi.y;
+    }
+  };
+  if (have) begin();
+  while (have) {
+    bool go = step + 1 < a.hop_num && deg != 0;
+    Rand4 r{0, 0, 0, 0};
+    if (go) {
+      r = philox_tagged(a.seed, TAG_WALK, a.walker_base + w, step, 0);
+      if (APP == SKW_APP_PPR && u01(r.z) < a.tp) go = false;
+    }
+    if (go) {
+      u32 rw[8];
+      load_record(a.rec + (u64)off + __umulhi(r.x, deg), rw);
+      const bool keep = u01(r.y) < __uint_as_float(rw[0]);
+      ++step;
+      row[step] = keep ? rw[1] : rw[4];
+      off = keep ? rw[2] : rw[5];
+      deg = keep ? rw[3] : rw[6];
+    } else {
+      a.lengths[w] = step;
+      edges += step;
+      w += T;
+      have = w < a.n;
+      if (have) begin();
+    }
+  }
+  add_edges(a.sum, edges);
+}
+
 __global__ void __launch_bounds__(256) generate_starts_kernel(u32* __restrict__ starts, u64 n,
                                                               u64 id_base, u64 seed, u32 V) {
   for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (u64)gridDim.x * blockDim.x) {
@@ -202,6 +336,41 @@ int skw_generate_starts_device(skw_ctx* ctx, uint64_t n, uint64_t id_base, uint6
   return SKW_OK;
 }
 
+int skw_walk_records_build(skw_ctx* ctx, float* ms) {
+  if (!ctx) return SKW_ERR_ARG;
+  if (!ctx->table_ready) return fail(ctx, SKW_ERR_STATE, "skw_walk_records_build: build or import the alias table first");
+  DeviceGuard g(ctx->device);
+  if (!ctx->records) SKW_CUDA(ctx, cudaMalloc(&ctx->records, sizeof(WalkRecord) * (ctx->E ? ctx->E : 1)));
+  if (!ctx->vinfo) SKW_CUDA(ctx, cudaMalloc(&ctx->vinfo, sizeof(uint2) * ((size_t)ctx->V + 1)));
+  cudaStream_t st = ctx->stream;
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+  const int grid = ctx->sm_count * 16;
+  if (ctx->V) {
+    vertex_info_kernel<<<grid, 256, 0, st>>>(ctx->xadj, ctx->slots, ctx->V, static_cast<uint2*>(ctx->vinfo));
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->E) {
+    walk_records_kernel<<<grid, 256, 0, st>>>(ctx->xadj, ctx->adjncy, ctx->slots, static_cast<const uint2*>(ctx->vinfo),
+                                              ctx->V, ctx->E, static_cast<WalkRecord*>(ctx->records));
+    SKW_LAUNCHED(ctx);
+  }
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+  SKW_CUDA(ctx, cudaStreamSynchronize(st));
+  if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+  return SKW_OK;
+}
+
+int skw_walk_records_free(skw_ctx* ctx) {
+  if (!ctx) return SKW_ERR_ARG;
+  DeviceGuard g(ctx->device);
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  cudaFree(ctx->records);
+  cudaFree(ctx->vinfo);
+  ctx->records = nullptr;
+  ctx->vinfo = nullptr;
+  return SKW_OK;
+}
+
 int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_starts, uint64_t n,
                     uint32_t* d_paths, uint32_t* d_lengths, float* ms, uint64_t* sampled_edges) {
   if (!ctx || !prm) return SKW_ERR_ARG;
@@ -221,7 +390,10 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_walk: online mode needs the edge weights");
   DeviceGuard g(ctx->device);
   int rc;
-  if (online && (rc = alloc_table(ctx)) != SKW_OK) return rc;
+  if (online) {
+    drop_records(ctx);  // online builds overwrite table slots
+    if ((rc = alloc_table(ctx)) != SKW_OK) return rc;
+  }
   WalkArgs a;
   a.xadj = ctx->xadj;
   a.adjncy = ctx->adjncy;
@@ -245,7 +417,26 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
   if (n) {
-    if (!online) {
+    if (!online && ctx->records && prm->app != SKW_APP_NODE2VEC) {
+      RecordWalkArgs ra;
+      ra.rec = static_cast<const WalkRecord*>(ctx->records);
+      ra.vinfo = static_cast<const uint2*>(ctx->vinfo);
+      ra.starts = d_starts;
+      ra.paths = d_paths;
+      ra.lengths = d_lengths;
+      ra.sum = a.sum;
+      ra.err = a.err;
+      ra.n = n;
+      ra.seed = a.seed;
+      ra.walker_base = a.walker_base;
+      ra.V = a.V;
+      ra.hop_num = a.hop_num;
+      ra.tp = a.tp;
+      const int grid = grid_for(ctx, n, 8);
+      if (prm->app == SKW_APP_PPR) walk_records_walk_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(ra);
+      else walk_records_walk_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(ra);
+      SKW_LAUNCHED(ctx);
+    } else if (!online) {
       const int grid = grid_for(ctx, n, 8);
       switch (prm->app) {
         case SKW_APP_DEEPWALK: walk_offline_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a); break;

@@ -163,6 +163,41 @@ def test_walks_bit_exact(ctx, oracle, plaw, app, kw, mode):
     assert edges == int(olens.sum())
 
 
+@pytest.mark.parametrize("app,kw", [(APP_DEEPWALK, {}), (APP_PPR, {"tp": 0.15})])
+@pytest.mark.parametrize("gname", ["rmat16", "plaw"])
+def test_walk_records_bit_exact(ctx, oracle, request, gname, app, kw):
+    """The fused 32-byte record layout gives the same walks as the oracle (and as the 8-byte slots)."""
+    g = request.getfixturevalue(gname)
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    starts = oracle.gen_starts(4096, g.V, 42)
+    hop = 81 if app != APP_PPR else 101
+    base, blen, _, bedges = ctx.walk(starts, hop, app=app, seed=42, **kw)
+    ctx.walk_records_build()
+    paths, lens, _, edges = ctx.walk(starts, hop, app=app, seed=42, **kw)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, hop, app=app, seed=42, **kw)
+    _cmp_walks(paths, lens, opaths, olens)
+    _cmp_walks(base, blen, opaths, olens)
+    assert edges == bedges == int(olens.sum())
+    ctx.walk_records_free()
+
+
+def test_walk_records_dead_ends_and_invalid(ctx):
+    xadj = np.asarray([0, 1, 1, 2, 3, 3, 5], np.uint32)
+    adj = np.asarray([1, 3, 2, 0, 4], np.uint32)     # 5 -> {0 (unusable weights), 4 (isolated)}
+    w = np.asarray([0.0, 1.0, 2.0, 1.0, 1.0], np.float32)
+    ctx.upload(xadj, adj, w)
+    ctx.alias_build_offline()
+    ctx.walk_records_build()
+    starts = np.asarray([0, 1, 2, 3, 4, 5, 5, 5, 5], np.uint32)
+    paths, lens, _, edges = ctx.walk(starts, 6, seed=1)
+    assert list(lens[:5]) == [0, 0, 5, 5, 0]
+    assert list(paths[2]) == [2, 3, 2, 3, 2, 3]
+    assert (lens[5:] == 1).all() and np.isin(paths[5:, 1], [0, 4]).all()
+    ctx.walk_records_free()
+
+
 def test_walk_dead_ends_and_invalid_vertices(ctx, oracle):
     # 0 -> 1 (weight 0: unusable), 2 -> 3 -> 2 cycle, 4 isolated
     xadj = np.asarray([0, 1, 1, 2, 3, 3], np.uint32)
