@@ -23,11 +23,11 @@
 // Every quantity is an integer or a single correctly rounded IEEE operation, so the table is a
 // pure function of the weight list: no atomics on masses, no dependence on scheduling.
 //
-// Work distribution: vertices are binned by degree into seven classes with warp ballots and
+// Work distribution: vertices are binned by degree into eight classes with warp ballots and
 // shared-memory prefix sums (classify_* kernels); classes of degree <= 32 run one sub-warp
-// group of 4/8/16/32 lanes per vertex entirely in registers, degree <= 1024 and <= 8192 one CTA
-// per vertex with the prefix arrays in shared memory, larger vertices one CTA per vertex with
-// the prefix arrays in a global scratch slab.
+// group of 4/8/16/32 lanes per vertex entirely in registers; degree <= 256 and <= 1024 one warp
+// per vertex, degree <= 12288 one CTA of 512 threads per vertex, with the two prefix lists in
+// shared memory; larger vertices one CTA of 1024 threads with the lists in a global scratch slab.
 #include <math_constants.h>
 
 #include <cstdarg>
@@ -38,9 +38,13 @@
 
 namespace skw {
 
-enum { K_G4 = 0, K_G8, K_G16, K_G32, K_M, K_L, K_H, K_CLASSES };
-constexpr u32 kMediumMax = 1024;
-constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 8192
+// degree classes: groups of 4/8/16/32 lanes; one warp per vertex (two capacities); one CTA of
+// 512 threads with its lists in shared memory; one CTA of 1024 threads with its lists in a
+// global scratch slab
+enum { K_G4 = 0, K_G8, K_G16, K_G32, K_W256, K_W1K, K_C, K_H, K_CLASSES };
+constexpr u32 kWarpSmallMax = 256;
+constexpr u32 kWarpMax = 1024;
+constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 12288: 12 bytes of list state per edge
 
 __device__ __forceinline__ float sane_weight(float w) {
   return (w > 0.0f && w < CUDART_INF_F) ? w : 0.0f;
@@ -60,6 +64,30 @@ __device__ __forceinline__ double weight_scale(float wmax, int B) {
 __device__ __forceinline__ u64 quantise(float w, double scale) {
   return __double2ull_rz(__dmul_rn((double)w, scale));
 }
+// The same value as quantise(w, 2^s) from the bits of w (w > 0 finite or 0), without the
+// fp64 conversions: trunc(w * 2^s) = mantissa shifted by (exponent + s).
+__device__ __forceinline__ u64 quantise_bits(float w, int s) {
+  const u32 b = __float_as_uint(w);
+  const u32 ew = b >> 23;
+  const u32 mant = b & 0x7FFFFFu;
+  const u64 M = ew ? (u64)(mant | 0x800000u) : (u64)mant;
+  const int sh = s + (ew ? (int)ew - 150 : -149);
+  if (sh >= 0) return sh < 64 ? M << sh : 0;  // sh < 40 by construction
+  return sh > -64 ? M >> (-sh) : 0;
+}
+// s of quantise_bits for the largest weight wmax (> 0): B - 1 - floor(log2 wmax)
+__device__ __forceinline__ int weight_shift(float wmax, int B) {
+  const u32 b = __float_as_uint(wmax);
+  const u32 ew = b >> 23;
+  const int e = ew ? (int)ew - 127 : (31 - __clz((int)(b & 0x7FFFFFu))) - 149;
+  return B - 1 - e;
+}
+__device__ __forceinline__ float mass_to_prob_fast(u64 m, int B) {
+  // one rounding (u64 -> fp32, nearest even) then an exact power-of-two scale: the same bits as
+  // rounding the exact quotient m / 2^B once
+  return __ull2float_rn(m) * __uint_as_float((u32)(127 - B) << 23);
+}
+
 __device__ __forceinline__ double mass_factor(u32 n, int B, u64 W) {
   return __ddiv_rn(__ull2double_rn((u64)n << B), __ull2double_rn(W));
 }
@@ -78,8 +106,9 @@ __device__ __forceinline__ int degree_class(u32 deg) {
   if (deg <= 8) return K_G8;
   if (deg <= 16) return K_G16;
   if (deg <= 32) return K_G32;
-  if (deg <= kMediumMax) return K_M;
-  if (deg <= kLargeMax) return K_L;
+  if (deg <= kWarpSmallMax) return K_W256;
+  if (deg <= kWarpMax) return K_W1K;
+  if (deg <= kLargeMax) return K_C;
   return K_H;
 }
 
@@ -277,6 +306,277 @@ __global__ void __launch_bounds__(256) build_group_kernel(const u32* __restrict_
   }
 }
 
+// ------------------------------------------------------------------ merge-path builders ----
+// NT cooperating threads (one warp, or a CTA) build one vertex.
+//
+// The sweep "smalls in index order are topped up by larges in index order" is a MERGE of two
+// sorted lists: small i (key = deficit of the smalls before it) comes before large j (key = excess
+// of the larges up to and including it) iff its key is <= the large's key.  When small i is
+// emitted at state (i, j) its donor is large j; when large j is emitted while smalls remain it
+// has fallen below one bucket, keeps X(j) + C - D(i-1) of it and is topped up by large j+1; larges
+// emitted after the last small own exactly one bucket.  So after the two prefix lists are in
+// memory, every thread takes an equal slice of the merged order (merge-path partition by one
+// bisection per thread) and runs the sweep serially on it: the same number of steps in every
+// lane, no per-element searches.
+//
+// Phase 1 walks the weight list in tiles of NT*4 elements (4 consecutive elements per thread, so a
+// prefix sum is a short serial scan plus one cross-thread scan) and writes
+//   A[i] = inclusive deficit prefix of small i,   P[i] = its position        (smalls from the front)
+//   A[n-1-j] = inclusive excess prefix of large j, P[n-1-j] = its position   (larges from the back)
+template <int NT>
+__device__ __forceinline__ void coop_sync() {
+  if constexpr (NT == 32) __syncwarp();
+  else __syncthreads();
+}
+
+// Exclusive cross-thread prefix and total of one u64 per thread.
+template <int NT>
+__device__ __forceinline__ void coop_scan_u64(u64& v, u64& total, u64* s_tmp) {
+  const u32 lane = threadIdx.x & 31;
+  u64 inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const u64 t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= (u32)o) inc += t;
+  }
+  if constexpr (NT == 32) {
+    total = __shfl_sync(0xFFFFFFFFu, inc, 31);
+    v = inc - v;
+  } else {
+    const u32 warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 31) s_tmp[warp] = inc;
+    __syncthreads();
+    u64 before = 0, all = 0;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) {
+      const u64 t = s_tmp[w];
+      if ((u32)w < warp) before += t;
+      all += t;
+    }
+    total = all;
+    v = before + inc - v;
+  }
+}
+template <int NT>
+__device__ __forceinline__ float coop_max(float v, float* s_tmp) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  if constexpr (NT != 32) {
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_tmp[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) t = fmaxf(t, s_tmp[w]);
+    v = t;
+  }
+  return v;
+}
+
+template <int NT>
+__device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __restrict__ wgt,
+                                   Slot* __restrict__ slots, uint8_t* __restrict__ valid, u64* A,
+                                   u32* P, u64* s_tmp, u32* err) {
+  const float* w = wgt + off;
+  float wmax = 0.0f;
+  for (u32 p = t; p < n; p += NT) wmax = fmaxf(wmax, sane_weight(__ldg(w + p)));
+  wmax = coop_max<NT>(wmax, reinterpret_cast<float*>(s_tmp));
+  if (!(wmax > 0.0f)) {
+    for (u32 p = t; p < n; p += NT) slots[(u64)off + p] = Slot{-1.0f, p};
+    if (t == 0) valid[v] = 0;
+    return;
+  }
+  const int B = bucket_bits(n);
+  const u64 C = (u64)1 << B;
+  const int sh = weight_shift(wmax, B);
+  u64 W = 0;
+  {
+    u64 acc = 0, dummy;
+    for (u32 p = t; p < n; p += NT) acc += quantise_bits(sane_weight(__ldg(w + p)), sh);
+    // total only: the exclusive prefix is not needed here
+    u64 x = acc;
+    coop_scan_u64<NT>(x, W, s_tmp);
+    (void)dummy;
+  }
+  const u64 nC = (u64)n << B;
+  const double K = mass_factor(n, B, W);
+
+  u64 cQ = 0, cD = 0, cX = 0;  // carries between tiles (the same value in every thread)
+  u32 cL = 0;
+  for (u32 base = 0; base < n; base += NT * 4) {
+    const u32 p0 = base + t * 4;
+    u64 m[4];
+    u64 Qex = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      m[k] = p0 + k < n ? quantise_bits(sane_weight(__ldg(w + p0 + k)), sh) : 0;
+      Qex += m[k];
+    }
+    u64 tq;
+    coop_scan_u64<NT>(Qex, tq, s_tmp);
+    Qex += cQ;
+    cQ += tq;
+    u64 g_prev = cum_mass(Qex, W, nC, K), Q = Qex;
+    u64 sd = 0, sx = 0, sl = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (p0 + k < n) {
+        Q += m[k];
+        const u64 g = cum_mass(Q, W, nC, K);
+        m[k] = g - g_prev;
+        g_prev = g;
+        if (m[k] < C) sd += C - m[k];
+        else {
+          sx += m[k] - C;
+          ++sl;
+        }
+      }
+    }
+    u64 td, tx, tl;
+    coop_scan_u64<NT>(sd, td, s_tmp);
+    coop_scan_u64<NT>(sx, tx, s_tmp);
+    coop_scan_u64<NT>(sl, tl, s_tmp);
+    u64 Dr = sd + cD, Xr = sx + cX;
+    u32 Lr = (u32)sl + cL;
+    cD += td;
+    cX += tx;
+    cL += (u32)tl;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const u32 p = p0 + k;
+      if (p < n) {
+        if (m[k] < C) {
+          Dr += C - m[k];
+          const u32 i = p - Lr;  // smalls before p
+          A[i] = Dr;
+          P[i] = p;
+        } else {
+          Xr += m[k] - C;
+          const u32 j = Lr++;    // larges before p
+          A[n - 1 - j] = Xr;
+          P[n - 1 - j] = p;
+        }
+      }
+    }
+  }
+  coop_sync<NT>();
+  const u32 L = cL, S = n - L;
+  if (L == 0 || cD != cX) {  // mass conservation guarantees both
+    if (t == 0) dev_fail(err, DEV_ERR_INTERNAL, v, L, 7);
+    for (u32 p = t; p < n; p += NT) slots[(u64)off + p] = Slot{1.0f, p};
+    if (t == 0) valid[v] = 1;
+    return;
+  }
+  // merge-path partition: this thread emits merged outputs [k0, k1)
+  const u32 VT = (n + NT - 1) / NT;
+  const u32 k0 = min(t * VT, n), k1 = min(k0 + VT, n);
+  u32 i, j;
+  {
+    u32 lo = k0 > L ? k0 - L : 0, hi = min(k0, S);
+    while (lo < hi) {
+      const u32 mid = (lo + hi) >> 1;
+      const u64 a = mid ? A[mid - 1] : 0;         // key of small mid
+      const u64 b = A[n - 1 - (k0 - 1 - mid)];    // key of large k0-1-mid
+      if (a <= b) lo = mid + 1;
+      else hi = mid;
+    }
+    i = lo;
+    j = k0 - lo;
+  }
+  u64 dsx = i ? A[i - 1] : 0;  // deficit of the smalls before small i
+  for (u32 k = k0; k < k1; ++k) {
+    Slot out;
+    u32 p;
+    const u64 xl = j < L ? A[n - 1 - j] : 0;
+    if (i < S && j < L && dsx <= xl) {
+      p = P[i];
+      const u64 dincl = A[i];
+      out.alias = P[n - 1 - j];
+      out.prob = mass_to_prob_fast(C - (dincl - dsx), B);
+      dsx = dincl;
+      ++i;
+    } else {
+      if (j >= L) {  // cannot happen: the last merged element is always the last large
+        dev_fail(err, DEV_ERR_INTERNAL, v, k, 9);
+        break;
+      }
+      p = P[n - 1 - j];
+      if (dsx <= xl) {  // only possible once every small is placed: the large owns one full bucket
+        out.alias = p;
+        out.prob = 1.0f;
+      } else if (j + 1 < L) {
+        out.alias = P[n - 2 - j];
+        out.prob = mass_to_prob_fast(xl + C - dsx, B);
+      } else {
+        dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
+        out.alias = p;
+        out.prob = 1.0f;
+      }
+      ++j;
+    }
+    slots[(u64)off + p] = out;
+  }
+  if (t == 0) valid[v] = 1;
+}
+
+// One warp per vertex of degree <= CAP; WPB warps per CTA; lists in dynamic shared memory
+// (12 bytes per edge per warp).
+template <int CAP, int WPB>
+__global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* __restrict__ worklist,
+                                                                    const u32* __restrict__ cls, int k,
+                                                                    const u32* __restrict__ xadj,
+                                                                    const float* __restrict__ wgt,
+                                                                    Slot* __restrict__ slots,
+                                                                    uint8_t* __restrict__ valid,
+                                                                    u32* __restrict__ err) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  const u32 lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  u64* A = reinterpret_cast<u64*>(smem) + (size_t)wib * CAP;
+  u32* P = reinterpret_cast<u32*>(reinterpret_cast<u64*>(smem) + (size_t)WPB * CAP) + (size_t)wib * CAP;
+  const u32 warp = blockIdx.x * WPB + wib, nwarps = gridDim.x * WPB;
+  for (u32 it = warp; it < count; it += nwarps) {
+    const u32 v = worklist[base + it];
+    const u32 off = xadj[v], n = xadj[v + 1] - off;
+    if (n > CAP) {
+      if (lane == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
+      continue;
+    }
+    build_vertex_merge<32>(lane, v, off, n, wgt, slots, valid, A, P, nullptr, err);
+    __syncwarp();
+  }
+}
+
+// One CTA of NT threads per vertex of degree <= cap; lists in dynamic shared memory, or, when
+// scratch != nullptr, in this CTA's slab of global scratch (cap entries of 12 bytes).
+template <int NT>
+__global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restrict__ worklist,
+                                                             const u32* __restrict__ cls, int k,
+                                                             const u32* __restrict__ xadj,
+                                                             const float* __restrict__ wgt,
+                                                             Slot* __restrict__ slots,
+                                                             uint8_t* __restrict__ valid,
+                                                             unsigned char* __restrict__ scratch,
+                                                             u64 cap, u32* __restrict__ err) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ u64 s_tmp[NT / 32];
+  unsigned char* store = scratch ? scratch + (u64)blockIdx.x * cap * 12ull : smem;
+  u64* A = reinterpret_cast<u64*>(store);
+  u32* P = reinterpret_cast<u32*>(A + cap);
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  for (u32 it = blockIdx.x; it < count; it += gridDim.x) {
+    const u32 v = worklist[base + it];
+    const u32 off = xadj[v], n = xadj[v + 1] - off;
+    if (n > cap) {
+      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)cap);
+      continue;
+    }
+    build_vertex_merge<NT>(threadIdx.x, v, off, n, wgt, slots, valid, A, P, s_tmp, err);
+    __syncthreads();
+  }
+}
+
 // ------------------------------------------------------------------ one CTA per vertex -----
 template <int T>
 __device__ __forceinline__ u64 block_sum(u64 x, u64* s_red) {
@@ -451,77 +751,25 @@ __device__ void build_vertex_cta(u32 v, u32 off, u32 n, const float* __restrict_
   if (tid == 0) valid[v] = 1;
 }
 
-template <int T, int CAP>
-__global__ void __launch_bounds__(T) build_cta_smem_kernel(const u32* __restrict__ worklist,
-                                                           const u32* __restrict__ cls, int k,
-                                                           const u32* __restrict__ xadj,
-                                                           const float* __restrict__ wgt,
-                                                           Slot* __restrict__ slots,
-                                                           uint8_t* __restrict__ valid,
-                                                           u32* __restrict__ err) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  u64* D = reinterpret_cast<u64*>(smem);
-  u64* X = D + CAP;
-  u32* LR = reinterpret_cast<u32*>(X + CAP);
-  __shared__ u64 s_red[T / 32];
-  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
-  for (u32 it = blockIdx.x; it < count; it += gridDim.x) {
-    const u32 v = worklist[base + it];
-    const u32 off = xadj[v], n = xadj[v + 1] - off;
-    if (n > CAP) {
-      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
-      continue;
-    }
-    build_vertex_cta<T>(v, off, n, wgt, slots, valid, D, X, LR, s_red, err);
-    __syncthreads();
-  }
-}
-
-// Vertices above the shared-memory capacity: same construction, prefix arrays in a per-CTA slab
-// of global scratch (slab_elems entries of 20 bytes).
-template <int T>
-__global__ void __launch_bounds__(T) build_cta_gmem_kernel(const u32* __restrict__ worklist,
-                                                           const u32* __restrict__ cls, int k,
-                                                           const u32* __restrict__ xadj,
-                                                           const float* __restrict__ wgt,
-                                                           Slot* __restrict__ slots,
-                                                           uint8_t* __restrict__ valid,
-                                                           unsigned char* __restrict__ scratch,
-                                                           u64 slab_elems, u32* __restrict__ err) {
-  __shared__ u64 s_red[T / 32];
-  unsigned char* slab = scratch + (u64)blockIdx.x * slab_elems * 20ull;
-  u64* D = reinterpret_cast<u64*>(slab);
-  u64* X = D + slab_elems;
-  u32* LR = reinterpret_cast<u32*>(X + slab_elems);
-  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
-  for (u32 it = blockIdx.x; it < count; it += gridDim.x) {
-    const u32 v = worklist[base + it];
-    const u32 off = xadj[v], n = xadj[v + 1] - off;
-    if (n > slab_elems) {
-      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)slab_elems);
-      continue;
-    }
-    build_vertex_cta<T>(v, off, n, wgt, slots, valid, D, X, LR, s_red, err);
-    __syncthreads();
-  }
-}
-
-// Launch the seven class builders over work lists laid out as cls describes (counts at [k],
+// Launch the class builders over work lists laid out as cls describes (counts at [k],
 // bases at [2K + k]).
 static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
   cudaStream_t st = ctx->stream;
-  constexpr int kLargeSmem = kLargeMax * 20;
-  constexpr int kMediumSmem = kMediumMax * 20;
+  constexpr int kCtaSmem = kLargeMax * 12;
+  constexpr int kW256Smem = 8 * kWarpSmallMax * 12;
+  constexpr int kW1KSmem = 8 * kWarpMax * 12;
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
-    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_smem_kernel<512, kLargeMax>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kLargeSmem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaSmem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_warp_merge_kernel<kWarpMax, 8>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kW1KSmem));
     attr_set[ctx->device & 63] = true;
   }
+  // slabs of the global-scratch builder: one per CTA, sized by the largest degree
   const int gmem_ctas = ctx->sm_count;
   const uint64_t slab_elems = ctx->max_degree > kLargeMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
   if (slab_elems) {
-    int rc = ensure_bytes(ctx, &ctx->cta_scratch, &ctx->cta_scratch_bytes, slab_elems * 20ull * gmem_ctas);
+    int rc = ensure_bytes(ctx, &ctx->cta_scratch, &ctx->cta_scratch_bytes, slab_elems * 12ull * gmem_ctas);
     if (rc != SKW_OK) return rc;
   }
   const int ggrid = ctx->sm_count * 8;
@@ -534,16 +782,23 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
   GROUP(16, K_G16);
   GROUP(32, K_G32);
 #undef GROUP
-  build_cta_smem_kernel<128, kMediumMax><<<ctx->sm_count * 8, 128, kMediumSmem, st>>>(
-      worklist, cls, K_M, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
-  SKW_LAUNCHED(ctx);
-  if (ctx->max_degree > kMediumMax) {
-    build_cta_smem_kernel<512, kLargeMax><<<ctx->sm_count, 512, kLargeSmem, st>>>(
-        worklist, cls, K_L, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+  if (ctx->max_degree > 32) {
+    build_warp_merge_kernel<kWarpSmallMax, 8><<<ctx->sm_count * 8, 256, kW256Smem, st>>>(
+        worklist, cls, K_W256, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->max_degree > kWarpSmallMax) {
+    build_warp_merge_kernel<kWarpMax, 8><<<ctx->sm_count * 2, 256, kW1KSmem, st>>>(
+        worklist, cls, K_W1K, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->max_degree > kWarpMax) {
+    build_cta_merge_kernel<512><<<ctx->sm_count, 512, kCtaSmem, st>>>(
+        worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
     SKW_LAUNCHED(ctx);
   }
   if (slab_elems) {
-    build_cta_gmem_kernel<1024><<<gmem_ctas, 1024, 0, st>>>(
+    build_cta_merge_kernel<1024><<<gmem_ctas, 1024, 0, st>>>(
         worklist, cls, K_H, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid,
         static_cast<unsigned char*>(ctx->cta_scratch), slab_elems, ctx->d_err);
     SKW_LAUNCHED(ctx);
@@ -695,7 +950,7 @@ constexpr size_t kStaticHeader = 256;     // error record, kept apart from the a
 // held until the process exits.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticHeader + (size_t)kStaticMaxDegree * 20];
 
-// Same construction as build_cta_gmem_kernel, for the single list wgt[0..n), with the prefix arrays
+// The tile-wise CTA construction (build_vertex_cta) for the single list wgt[0..n), with the prefix arrays
 // at `scratch` (the device address of g_static_scratch, looked up by the host).
 __global__ void __launch_bounds__(1024) build_list_static_kernel(const float* __restrict__ wgt, u32 n,
                                                                  Slot* __restrict__ slots,

@@ -15,8 +15,8 @@ namespace skw {
 // vertex with its arrays in shared memory, then one CTA per vertex with arrays in global scratch.
 enum { CLS_G4 = 0, CLS_G8, CLS_G16, CLS_G32, CLS_CTA_SMEM, CLS_CTA_GMEM, CLS_COUNT };
 
-// Largest degree the shared-memory CTA builder takes (20 bytes of state per edge).
-constexpr uint32_t kCtaSmemMaxDegree = 8192;
+// Largest degree the shared-memory CTA builder takes (12 bytes of list state per edge).
+constexpr uint32_t kCtaSmemMaxDegree = 12288;
 
 struct WalkRecord;  // skw_walk.cu
 

@@ -87,7 +87,7 @@ def _star_graph(weights_per_vertex):
 def test_alias_every_degree_class_and_edge_cases(ctx, oracle):
     rng = np.random.default_rng(1)
     lists = []
-    for n in list(range(1, 70)) + [127, 128, 129, 1023, 1024, 1025, 4000, 8192, 8193, 20000, 70000]:
+    for n in list(range(1, 70)) + [127, 128, 129, 200, 511, 512, 513, 1023, 1024, 1025, 4000, 8191, 8192, 8193, 20000, 70000]:
         lists.append(rng.uniform(1, 10, n).astype(np.float32))
     lists.append(np.asarray([0.5] * 35 + [2.0] * 5, np.float32))       # reference smoke vector
     lists.append(np.full(40, 3.0, np.float32))                         # uniform
