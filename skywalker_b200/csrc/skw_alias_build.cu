@@ -358,6 +358,65 @@ __device__ __forceinline__ void coop_scan_u64(u64& v, u64& total, u64* s_tmp) {
     v = before + inc - v;
   }
 }
+// The same for three values at once (one pair of barriers instead of three).  s_tmp holds
+// 3 * NT/32 entries.
+template <int NT>
+__device__ __forceinline__ void coop_scan3(u64& a, u64& b, u32& c, u64& ta, u64& tb, u32& tc, u64* s_tmp) {
+  const u32 lane = threadIdx.x & 31;
+  u64 ia = a, ib = b;
+  u32 ic = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const u64 xa = __shfl_up_sync(0xFFFFFFFFu, ia, o);
+    const u64 xb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
+    const u32 xc = __shfl_up_sync(0xFFFFFFFFu, ic, o);
+    if (lane >= (u32)o) {
+      ia += xa;
+      ib += xb;
+      ic += xc;
+    }
+  }
+  if constexpr (NT == 32) {
+    ta = __shfl_sync(0xFFFFFFFFu, ia, 31);
+    tb = __shfl_sync(0xFFFFFFFFu, ib, 31);
+    tc = __shfl_sync(0xFFFFFFFFu, ic, 31);
+    a = ia - a;
+    b = ib - b;
+    c = ic - c;
+  } else {
+    constexpr int NW = NT / 32;
+    const u32 warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 31) {
+      s_tmp[warp] = ia;
+      s_tmp[NW + warp] = ib;
+      s_tmp[2 * NW + warp] = ic;
+    }
+    __syncthreads();
+    u64 pa = 0, pb = 0, sa = 0, sb = 0;
+    u32 pc = 0, sc = 0;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const u64 va = s_tmp[w], vb = s_tmp[NW + w];
+      const u32 vc = (u32)s_tmp[2 * NW + w];
+      if ((u32)w < warp) {
+        pa += va;
+        pb += vb;
+        pc += vc;
+      }
+      sa += va;
+      sb += vb;
+      sc += vc;
+    }
+    ta = sa;
+    tb = sb;
+    tc = sc;
+    a = pa + ia - a;
+    b = pb + ib - b;
+    c = pc + ic - c;
+  }
+}
+
 template <int NT>
 __device__ __forceinline__ float coop_max(float v, float* s_tmp) {
 #pragma unroll
@@ -374,7 +433,7 @@ __device__ __forceinline__ float coop_max(float v, float* s_tmp) {
   return v;
 }
 
-template <int NT>
+template <int NT, int EPT>
 __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __restrict__ wgt,
                                    Slot* __restrict__ slots, uint8_t* __restrict__ valid, u64* A,
                                    u32* P, u64* s_tmp, u32* err) {
@@ -404,12 +463,12 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
 
   u64 cQ = 0, cD = 0, cX = 0;  // carries between tiles (the same value in every thread)
   u32 cL = 0;
-  for (u32 base = 0; base < n; base += NT * 4) {
-    const u32 p0 = base + t * 4;
-    u64 m[4];
+  for (u32 base = 0; base < n; base += NT * EPT) {
+    const u32 p0 = base + t * EPT;
+    u64 m[EPT];
     u64 Qex = 0;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < EPT; ++k) {
       m[k] = p0 + k < n ? quantise_bits(sane_weight(__ldg(w + p0 + k)), sh) : 0;
       Qex += m[k];
     }
@@ -418,9 +477,10 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
     Qex += cQ;
     cQ += tq;
     u64 g_prev = cum_mass(Qex, W, nC, K), Q = Qex;
-    u64 sd = 0, sx = 0, sl = 0;
+    u64 sd = 0, sx = 0;
+    u32 sl = 0;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < EPT; ++k) {
       if (p0 + k < n) {
         Q += m[k];
         const u64 g = cum_mass(Q, W, nC, K);
@@ -433,17 +493,16 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
         }
       }
     }
-    u64 td, tx, tl;
-    coop_scan_u64<NT>(sd, td, s_tmp);
-    coop_scan_u64<NT>(sx, tx, s_tmp);
-    coop_scan_u64<NT>(sl, tl, s_tmp);
+    u64 td, tx;
+    u32 tl;
+    coop_scan3<NT>(sd, sx, sl, td, tx, tl, s_tmp);
     u64 Dr = sd + cD, Xr = sx + cX;
-    u32 Lr = (u32)sl + cL;
+    u32 Lr = sl + cL;
     cD += td;
     cX += tx;
-    cL += (u32)tl;
+    cL += tl;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < EPT; ++k) {
       const u32 p = p0 + k;
       if (p < n) {
         if (m[k] < C) {
@@ -543,7 +602,7 @@ __global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* _
       if (lane == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
       continue;
     }
-    build_vertex_merge<32>(lane, v, off, n, wgt, slots, valid, A, P, nullptr, err);
+    build_vertex_merge<32, 4>(lane, v, off, n, wgt, slots, valid, A, P, nullptr, err);
     __syncwarp();
   }
 }
@@ -560,7 +619,7 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
                                                              unsigned char* __restrict__ scratch,
                                                              u64 cap, u32* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ u64 s_tmp[NT / 32];
+  __shared__ u64 s_tmp[3 * NT / 32];
   unsigned char* store = scratch ? scratch + (u64)blockIdx.x * cap * 12ull : smem;
   u64* A = reinterpret_cast<u64*>(store);
   u32* P = reinterpret_cast<u32*>(A + cap);
@@ -572,7 +631,7 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
       if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)cap);
       continue;
     }
-    build_vertex_merge<NT>(threadIdx.x, v, off, n, wgt, slots, valid, A, P, s_tmp, err);
+    build_vertex_merge<NT, 8>(threadIdx.x, v, off, n, wgt, slots, valid, A, P, s_tmp, err);
     __syncthreads();
   }
 }
