@@ -107,6 +107,18 @@ def shard(n_total, world, rank):
     return lo, hi - lo
 
 
+def combine_over_ranks(dist, values, device=None):
+    """(max over ranks, sum over ranks) of a list of floats; identity without a process group."""
+    import torch
+    t = torch.tensor(values, dtype=torch.float64, device=device)
+    if dist is None:
+        return t.tolist(), t.tolist()
+    mx, sm = t.clone(), t.clone()
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    return mx.tolist(), sm.tolist()
+
+
 def make_graph(ctx, wl):
     raw = wl["edge_factor"] << wl["scale"]
     ctx.generate_rmat(wl["scale"], raw, 0.57, 0.19, 0.19, False, GRAPH_SEED, WEIGHT_SEED)
@@ -276,16 +288,9 @@ def main():
     launches = ctx.kernel_launches - launches0
     span_ms = ev0.elapsed_time(ev1)
 
-    tot = torch.tensor([span_ms, kernel_ms, float(edges_local), float(launches)], dtype=torch.float64, device=dev)
-    if dist is not None:
-        mx = tot.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = tot.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        span_ms, kernel_ms = float(mx[0]), float(mx[1])
-        edges_all, launches = float(sm[2]), int(sm[3])
-    else:
-        edges_all = float(edges_local)
+    mx, sm = combine_over_ranks(dist, [span_ms, kernel_ms, float(edges_local), float(launches)], dev)
+    span_ms, kernel_ms = mx[0], mx[1]
+    edges_all, launches = sm[2], int(sm[3])
     value = edges_all / (span_ms * 1e-3)
 
     # end to end through the host-buffer entry point: pinned starts in, paths + lengths out
@@ -311,13 +316,8 @@ def main():
             e_edges += estep(100 + i)[3]
         barrier()
         e_ms = (time.perf_counter() - t0) * 1e3
-        et = torch.tensor([e_ms, float(e_edges)], dtype=torch.float64, device=dev)
-        if dist is not None:
-            m2 = et.clone()
-            dist.all_reduce(m2, op=dist.ReduceOp.MAX)
-            s2 = et.clone()
-            dist.all_reduce(s2, op=dist.ReduceOp.SUM)
-            e_ms, e_edges = float(m2[0]), float(s2[1])
+        m2, s2 = combine_over_ranks(dist, [e_ms, float(e_edges)], dev)
+        e_ms, e_edges = m2[0], s2[1]
         e2e = {"value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
                "ms_per_step": e_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
                "d2h_bytes_per_step": 4 * n_local * hop + 4 * n_local,
@@ -327,6 +327,7 @@ def main():
     gather_ms = None
     if dist is not None:
         bufs = [torch.empty_like(lengths) for _ in range(world)] if rank == 0 else None
+        dist.gather(lengths, bufs, dst=0)       # first collective sets NCCL up
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         dist.gather(lengths, bufs, dst=0)

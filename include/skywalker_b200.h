@@ -182,6 +182,9 @@ typedef struct skw_walk_params {
   float p, q;           /* node2vec hyper-parameters                                   */
   uint64_t seed;        /* Philox seed                                                 */
   uint64_t walker_base; /* global id of walker 0 of this call (multi-GPU sharding)     */
+  uint64_t walker_stride; /* global id of walker i = walker_base + i * walker_stride; 0 means 1. *
+                           * The reference interleaves walkers over GPUs (id = dev + i * ngpu,  *
+                           * include/sampler.cuh:494-503): stride = ngpu reproduces that.         */
 } skw_walk_params;
 
 /* Optional wider layout of the same table for offline DeepWalk / PPR.  No counterpart in the
@@ -217,6 +220,7 @@ typedef struct skw_khop_params {
   uint32_t flags;       /* SKW_KHOP_*                                                  */
   uint64_t seed;
   uint64_t instance_base; /* global id of seed vertex 0 of this call                    */
+  uint64_t instance_stride; /* global id of seed i = instance_base + i * instance_stride; 0 = 1 */
 } skw_khop_params;
 
 /* Cells per seed in `data` (1 + f1 + f1*f2 ...) and in `sample_lengths` (1 + f1 + ... without

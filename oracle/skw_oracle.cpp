@@ -330,8 +330,8 @@ static void walk_one(const u32* xadj, const u32* adjncy, const float* adjwgt, co
 // Cells after paths[w*hop_num + lengths[w]] are left untouched.
 void orc_walk(const u32* xadj, const u32* adjncy, const float* adjwgt, const float* prob,
               const u32* alias, const uint8_t* valid, int online, int app, u32 hop_num, float tp,
-              float p, float q, u64 seed, u64 walker_base, const u32* starts, u64 n, u32* paths,
-              u32* lengths, int threads) {
+              float p, float q, u64 seed, u64 walker_base, u64 walker_stride, const u32* starts, u64 n,
+              u32* paths, u32* lengths, int threads) {
   const float inv_p = 1.0f / p, inv_q = 1.0f / q;
 #pragma omp parallel num_threads(threads > 0 ? threads : orc_num_threads())
   {
@@ -340,7 +340,7 @@ void orc_walk(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
 #pragma omp for schedule(dynamic, 64)
     for (long long w = 0; w < (long long)n; ++w)
       walk_one(xadj, adjncy, adjwgt, prob, alias, valid, online, app, hop_num, tp, inv_p, inv_q,
-               seed, walker_base + (u64)w, starts[w], paths + (u64)w * hop_num, lengths + w, tprob,
+               seed, walker_base + (u64)w * walker_stride, starts[w], paths + (u64)w * hop_num, lengths + w, tprob,
                talias);
   }
 }
@@ -353,8 +353,8 @@ void orc_walk(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
 // hold 0xFFFFFFFF.  fanout[0..nhops-1] are the reference's hops[1..].
 void orc_khop(const u32* xadj, const u32* adjncy, const float* adjwgt, const float* prob,
               const u32* alias, const uint8_t* valid, int online, u32 nhops, const u32* fanout,
-              u32 flags, u64 seed, u64 instance_base, const u32* seeds, u64 n, u32* data,
-              u32* sample_lengths, int threads) {
+              u32 flags, u64 seed, u64 instance_base, u64 instance_stride, const u32* seeds, u64 n,
+              u32* data, u32* sample_lengths, int threads) {
   u32 width[8], offs[8];
   u32 cells = 0, w = 1;
   for (u32 h = 0; h <= nhops; ++h) {
@@ -372,7 +372,7 @@ void orc_khop(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
     for (long long s = 0; s < (long long)n; ++s) {
       u32* row = data + (u64)s * cells;
       u32* len = sample_lengths + (u64)s * lens;
-      const u64 gi = instance_base + (u64)s;
+      const u64 gi = instance_base + (u64)s * instance_stride;
       row[0] = seeds[s];
       for (u32 h = 0; h < nhops; ++h) {
         const u32 f = fanout[h];

@@ -18,12 +18,13 @@ INVALID_VERTEX = 0xFFFFFFFF
 class WalkParams(C.Structure):
     _fields_ = [("app", C.c_uint32), ("mode", C.c_uint32), ("hop_num", C.c_uint32),
                 ("tp", C.c_float), ("p", C.c_float), ("q", C.c_float),
-                ("seed", C.c_uint64), ("walker_base", C.c_uint64)]
+                ("seed", C.c_uint64), ("walker_base", C.c_uint64), ("walker_stride", C.c_uint64)]
 
 
 class KhopParams(C.Structure):
     _fields_ = [("mode", C.c_uint32), ("nhops", C.c_uint32), ("fanout", C.c_uint32 * 4),
-                ("flags", C.c_uint32), ("seed", C.c_uint64), ("instance_base", C.c_uint64)]
+                ("flags", C.c_uint32), ("seed", C.c_uint64), ("instance_base", C.c_uint64),
+                ("instance_stride", C.c_uint64)]
 
 
 # name -> (restype, argtypes); every symbol include/skywalker_b200.h declares

@@ -166,9 +166,9 @@ class Context:
 
     # -- walks
     def walk(self, starts, hop_num, app=APP_DEEPWALK, mode=MODE_OFFLINE, tp=0.0, p=2.0, q=0.5, seed=42,
-             walker_base=0, paths=None, lengths=None, n=None):
+             walker_base=0, paths=None, lengths=None, n=None, walker_stride=1):
         """Host arrays (numpy) or device buffers.  Returns (paths, lengths, ms, sampled_edges)."""
-        prm = WalkParams(app, mode, hop_num, tp, p, q, seed, walker_base)
+        prm = WalkParams(app, mode, hop_num, tp, p, q, seed, walker_base, walker_stride)
         ms, edges = C.c_float(), C.c_uint64()
         if _is_device(starts):
             n = int(starts.numel()) if n is None else n
@@ -188,7 +188,7 @@ class Context:
     # -- k-hop
     @staticmethod
     def khop_layout(fanout):
-        prm = KhopParams(0, len(fanout), (C.c_uint32 * 4)(*(list(fanout) + [0] * (4 - len(fanout)))), 0, 0, 0)
+        prm = KhopParams(0, len(fanout), (C.c_uint32 * 4)(*(list(fanout) + [0] * (4 - len(fanout)))), 0, 0, 0, 1)
         cells, lens = C.c_uint32(), C.c_uint32()
         rc = _capi.load().skw_khop_layout(C.byref(prm), C.byref(cells), C.byref(lens))
         if rc:
@@ -196,11 +196,11 @@ class Context:
         return cells.value, lens.value
 
     def sample_khop(self, seeds, fanout, mode=MODE_OFFLINE, flags=0, seed=42, instance_base=0, data=None,
-                    sample_lengths=None, n=None):
+                    sample_lengths=None, n=None, instance_stride=1):
         """Returns (data[n, cells], sample_lengths[n, lens], ms, sampled_edges)."""
         cells, lens = self.khop_layout(fanout)
         prm = KhopParams(mode, len(fanout), (C.c_uint32 * 4)(*(list(fanout) + [0] * (4 - len(fanout)))),
-                         flags, seed, instance_base)
+                         flags, seed, instance_base, instance_stride)
         ms, edges = C.c_float(), C.c_uint64()
         if _is_device(seeds):
             n = int(seeds.numel()) if n is None else n

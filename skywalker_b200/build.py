@@ -76,12 +76,11 @@ def build(force=False, verbose=False):
             raise RuntimeError("link failed:\n%s\n%s" % (p.stdout, p.stderr))
     cli_src = os.path.join(CSRC, "cli", "main.cpp")
     if os.path.exists(cli_src) and (force or _newer(CLI, [cli_src, LIB] + _headers())):
-        cmd = [host_cxx(), "-O2", "-std=c++17", "-fopenmp", "-I", os.path.join(ROOT, "include"),
-               cli_src, "-o", CLI, "-L", PKG, "-lskywalker_b200", "-Wl,-rpath,$ORIGIN"]
-        nccl_h = "/usr/include/nccl.h"
-        if os.path.exists(nccl_h):
-            cmd += ["-DSKW_HAVE_NCCL", "-I", "/usr/local/cuda/include", "-L", "/usr/local/cuda/lib64",
-                    "-lnccl", "-lcudart"]
+        cmd = [host_cxx(), "-O2", "-std=c++17", "-pthread", "-I", os.path.join(ROOT, "include"),
+               "-I", "/usr/local/cuda/include", cli_src, "-o", CLI, "-L", PKG, "-lskywalker_b200",
+               "-L", "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"]
+        if os.path.exists("/usr/include/nccl.h"):
+            cmd += ["-DSKW_HAVE_NCCL", "-lnccl"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode:
             raise RuntimeError("CLI build failed:\n%s\n%s" % (p.stdout, p.stderr))

@@ -28,6 +28,7 @@ struct KhopArgs {
   u64 n;
   u64 seed;
   u64 instance_base;
+  u64 instance_stride;
   u32 V;
   u32 cells, lens_per;
   u32 offs_parent, offs_child, width_parent, fanout, hop, flags;
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(256) khop_hop_kernel(const KhopArgs a) {
             got = deg;
             if (j < deg) out = __ldg(a.adjncy + (u64)off + j);
           } else {
-            const Rand4 r = philox_tagged(a.seed, TAG_KHOP, a.instance_base + s, rem, a.hop);
+            const Rand4 r = philox_tagged(a.seed, TAG_KHOP, a.instance_base + s * a.instance_stride, rem, a.hop);
             const u32 col = __umulhi(r.x, deg);
             const Slot sl = load_slot(a.slots + (u64)off + col);
             if (!(sl.prob < 0.0f)) {
@@ -153,6 +154,7 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
   a.n = n;
   a.seed = prm->seed;
   a.instance_base = prm->instance_base;
+  a.instance_stride = prm->instance_stride ? prm->instance_stride : 1;
   a.V = ctx->V;
   a.cells = cells;
   a.lens_per = offs[prm->nhops];

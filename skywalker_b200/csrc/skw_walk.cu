@@ -37,6 +37,7 @@ struct WalkArgs {
   u64 n;
   u64 seed;
   u64 walker_base;
+  u64 walker_stride;
   u32 V;
   u32 hop_num;
   float tp, inv_p, inv_q, fmax;
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(256) walk_offline_kernel(const WalkArgs a) {
   }
   while (have) {
     u32 next = 0;
-    const bool go = step + 1 < a.hop_num && walk_step<APP>(a, a.walker_base + w, step, cur, prev, next);
+    const bool go = step + 1 < a.hop_num && walk_step<APP>(a, a.walker_base + w * a.walker_stride, step, cur, prev, next);
     if (go) {
       ++step;
       row[step] = next;
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(256) walk_online_step_kernel(const WalkArgs a,
     const u32 cur = row[step];
     const u32 prev = (APP == SKW_APP_NODE2VEC && step) ? row[step - 1] : kNoVertex;
     u32 next = 0;
-    if (walk_step<APP>(a, a.walker_base + w, step, cur, prev, next)) {
+    if (walk_step<APP>(a, a.walker_base + w * a.walker_stride, step, cur, prev, next)) {
       row[step + 1] = next;
       if (step + 2 == a.hop_num) {
         a.lengths[w] = step + 1;
@@ -248,6 +249,7 @@ struct RecordWalkArgs {
   u64 n;
   u64 seed;
   u64 walker_base;
+  u64 walker_stride;
   u32 V;
   u32 hop_num;
   float tp;
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
     bool go = step + 1 < a.hop_num && deg != 0;
     Rand4 r{0, 0, 0, 0};
     if (go) {
-      r = philox_tagged(a.seed, TAG_WALK, a.walker_base + w, step, 0);
+      r = philox_tagged(a.seed, TAG_WALK, a.walker_base + w * a.walker_stride, step, 0);
       if (APP == SKW_APP_PPR && u01(r.z) < a.tp) go = false;
     }
     if (go) {
@@ -406,6 +408,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   a.n = n;
   a.seed = prm->seed;
   a.walker_base = prm->walker_base;
+  a.walker_stride = prm->walker_stride ? prm->walker_stride : 1;
   a.V = ctx->V;
   a.hop_num = prm->hop_num;
   a.tp = prm->tp;
@@ -429,6 +432,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
       ra.n = n;
       ra.seed = a.seed;
       ra.walker_base = a.walker_base;
+      ra.walker_stride = a.walker_stride;
       ra.V = a.V;
       ra.hop_num = a.hop_num;
       ra.tp = a.tp;

@@ -1,0 +1,80 @@
+"""The `skywalker` command-line driver: reference flag surface and stdout rows."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CLI = os.path.join(ROOT, "skywalker_b200", "skywalker")
+
+
+def _run(*args, check=True):
+    p = subprocess.run([CLI] + list(args), capture_output=True, text=True, timeout=600)
+    if check:
+        assert p.returncode == 0, p.stderr
+    return p
+
+
+def test_cli_rejects_unknown_flags_and_missing_input():
+    assert os.path.exists(CLI), "build the CLI with python -m skywalker_b200.build"
+    p = _run("--bogus", check=False)
+    assert p.returncode == 1 and "unknown command line flag" in p.stderr
+    p = _run("--deepwalk", check=False)
+    assert p.returncode == 1 and "--input" in p.stderr
+    p = _run("--n", check=False)
+    assert p.returncode == 1 and "missing its argument" in p.stderr
+
+
+def _paths_from_printresult(out):
+    rows = []
+    for m in re.finditer(r"(\d+)rd path len (\d+) \n([^\n]*)\n", out):
+        rows.append((int(m.group(2)), [int(x) for x in m.group(3).split()]))
+    return rows
+
+
+@pytest.fixture(scope="module")
+def gr_file(tmp_path_factory, rmat12):
+    from skywalker_b200.gr import write_gr
+    p = str(tmp_path_factory.mktemp("gr") / "rmat12.w.gr")
+    write_gr(p, rmat12.xadj, rmat12.adjncy, np.floor(rmat12.adjwgt).astype(np.uint32))
+    return p
+
+
+@pytest.mark.gpu
+def test_cli_offline_deepwalk_matches_oracle(oracle, rmat12, gr_file):
+    g = rmat12
+    w = np.floor(g.adjwgt).astype(np.float32)
+    out = _run("--deepwalk", "--d", "10", "--bias=1", "--ol=0", "-n", "64", "--input", gr_file, "--printresult").stdout
+    lines = out.strip().split("\n")
+    assert lines[0] == "rmat12.w.gr"                          # graph name first (include/graph.cuh:186-192)
+    nums = re.findall(r"^([\d.]+)\t$", out, re.M)
+    assert len(nums) == 3                                     # table ms, time ms, MSEPS (src/main.cu:408-419)
+    table = oracle.alias_build(g.xadj, w)
+    starts = np.arange(64, dtype=np.uint32)                   # walker g starts at vertex g (sampler.cuh:494-503)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, w, table, starts, 11, seed=42)
+    shown = _paths_from_printresult(out)
+    assert len(shown) == 3
+    for j, (length, row) in enumerate(shown):
+        assert length == olens[j]
+        assert row == list(opaths[j, :length + 1])
+    # online mode walks the same paths; --csv prints one line
+    out2 = _run("--deepwalk", "--d", "10", "--bias=1", "--ol=1", "-n", "64", "--input", gr_file, "--printresult").stdout
+    assert _paths_from_printresult(out2) == shown
+    csv = _run("--deepwalk", "--d", "10", "--bias=1", "--ol=0", "-n", "64", "--input", gr_file, "--csv").stdout
+    assert re.fullmatch(r"rmat12\.w\.gr,[\d.]+,\t[\d.]+,\t[\d.]+,\n", csv)
+
+
+@pytest.mark.gpu
+def test_cli_presets_and_modes(gr_file):
+    # --ppr sets tp = 0.15 and d = 100; --sage samples 25,10; --node2vec runs the rejection walk
+    for args in (["--ppr"], ["--sage"], ["--sage", "--ol=1"], ["--node2vec", "--d", "8"], ["--ppr", "--records"],
+                 ["--k", "3", "--d", "2"]):
+        out = _run(*args, "--bias=1", "-n", "256", "--input", gr_file).stdout
+        mseps = float(out.strip().split("\n")[-1])
+        assert mseps > 0
+    p = _run("--bias=0", "--deepwalk", "--input", gr_file, check=False)
+    assert p.returncode == 2 and "outside this build" in p.stderr
+    p = _run("--deepwalk", "--input", gr_file + ".missing", check=False)
+    assert p.returncode == 2 and "cannot open" in p.stderr

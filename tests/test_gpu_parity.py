@@ -234,6 +234,26 @@ def test_walk_sharding_is_invisible(ctx, oracle, rmat12):
     _cmp_walks(np.vstack([a, b]), np.concatenate([al, bl]), full, flen)
 
 
+def test_interleaved_walker_ids(ctx, oracle, rmat12):
+    """Reference-style interleaving over 3 'GPUs' (id = dev + i*3) gives the rows of one big call."""
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    starts = oracle.gen_starts(1500, g.V, 8)
+    full, flen, _, _ = ctx.walk(starts, 21, seed=4)
+    for dev in range(3):
+        sub = np.ascontiguousarray(starts[dev::3])
+        p, l, _, _ = ctx.walk(sub, 21, seed=4, walker_base=dev, walker_stride=3)
+        _cmp_walks(p, l, full[dev::3], flen[dev::3])
+        op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, sub, 21, seed=4, walker_base=dev, walker_stride=3)
+        _cmp_walks(p, l, op, ol)
+    seeds = starts[:300]
+    d, s_, _, _ = ctx.sample_khop(seeds, [5, 3], seed=9)
+    d1, s1, _, _ = ctx.sample_khop(np.ascontiguousarray(seeds[1::2]), [5, 3], seed=9, instance_base=1, instance_stride=2)
+    assert np.array_equal(d1, d[1::2]) and np.array_equal(s1, s_[1::2])
+
+
 @pytest.mark.parametrize("mode", [MODE_OFFLINE, MODE_ONLINE])
 @pytest.mark.parametrize("flags", [0, KHOP_TAKE_ALL])
 def test_khop_bit_exact(ctx, oracle, rmat16, mode, flags):

@@ -1,0 +1,68 @@
+"""Host-side logic of the multi-GPU path, run as two gloo ranks on the CPU."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, n_total, out_dir):
+    sys.path.insert(0, ROOT)
+    import bench
+    from oracle import oracle as O
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # every rank owns a contiguous range of global walker ids; the oracle stands in for the kernels
+    x, a = O.gen_rmat(10, 16 << 10, seed=1)
+    w = O.gen_weights(len(a), 7)
+    table = O.alias_build(x, w)
+    lo, n_local = bench.shard(n_total, world, rank)
+    starts = O.gen_starts(n_local, len(x) - 1, 42, id_base=lo)
+    paths, lens = O.walk(x, a, w, table, starts, 21, app=O.PPR, tp=0.15, seed=5, walker_base=lo)
+    mx, sm = bench.combine_over_ranks(dist, [float(rank + 1), float(lens.sum())])
+    # results gather to rank 0, as bench.py does with the per-walker lengths
+    sizes = [bench.shard(n_total, world, r)[1] for r in range(world)]
+    pad = max(sizes)
+    mine = torch.zeros(pad, dtype=torch.int64)
+    mine[:n_local] = torch.from_numpy(lens.astype(np.int64))
+    bufs = [torch.zeros(pad, dtype=torch.int64) for _ in range(world)] if rank == 0 else None
+    dist.gather(mine, bufs, dst=0)
+    if rank == 0:
+        got = np.concatenate([b.numpy()[:s] for b, s in zip(bufs, sizes)])
+        np.save(os.path.join(out_dir, "gathered.npy"), got)
+        np.save(os.path.join(out_dir, "stats.npy"), np.asarray([mx[0], sm[1]]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_walks_equal_single_rank(tmp_path, oracle):
+    sys.path.insert(0, ROOT)
+    import bench
+    n_total, world = 1001, 2          # odd on purpose: ragged shards
+    assert [bench.shard(n_total, world, r) for r in range(world)] == [(0, 500), (500, 501)]
+    assert sum(bench.shard(7, 8, r)[1] for r in range(8)) == 7
+    mp.spawn(_worker, args=(world, _free_port(), n_total, str(tmp_path)), nprocs=world, join=True)
+    got = np.load(tmp_path / "gathered.npy")
+    stats = np.load(tmp_path / "stats.npy")
+    x, a = oracle.gen_rmat(10, 16 << 10, seed=1)
+    w = oracle.gen_weights(len(a), 7)
+    table = oracle.alias_build(x, w)
+    starts = oracle.gen_starts(n_total, len(x) - 1, 42)
+    _, lens = oracle.walk(x, a, w, table, starts, 21, app=oracle.PPR, tp=0.15, seed=5)
+    assert np.array_equal(got, lens.astype(np.int64))       # the split is invisible in the result
+    assert stats[0] == 2.0 and stats[1] == float(lens.sum())  # max over ranks, sum over ranks
