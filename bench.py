@@ -1,15 +1,16 @@
 #!/usr/bin/env python
-"""Benchmark of the alias-method walk path.
+"""Benchmark of the alias-method sampling / random-walk path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c2|c1|dw26] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c2|c1|c3|c4|dw26|c5s]
+                    [--impl ours|reference]
 
-One "step" is one pass of the walk kernel over the whole batch of walkers of the workload.
-Default workload: BASELINE config 5 -- biased offline PPR (tp 0.15, max length 100) on a seeded
-R-MAT scale-26 graph (~1.8 G directed edges), 8 M walkers sharded evenly over the N GPUs, graph
-and tables replicated per GPU.  Rank 0 prints ONE JSON line.
+One "step" is one pass of the hot path over one batch: all walkers of the workload (walks) or one
+batch of seed vertices (k-hop).  Default workload: BASELINE config 5 -- biased offline PPR
+(tp 0.15, max length 100) on a seeded R-MAT scale-26 graph (~1.8 G directed edges), 8 M walkers
+sharded evenly over the N GPUs, graph and tables replicated per GPU.  Rank 0 prints ONE JSON line.
 
---impl reference times the CPU implementation of the same path (the OpenMP oracle; the
-reference project itself is CUDA-only) on a bounded sample of the same workload.
+--impl reference times the CPU implementation of the same path (the OpenMP oracle; the reference
+project itself is CUDA-only) on a bounded sample of the same workload.
 """
 import argparse
 import json
@@ -26,22 +27,33 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: scale, raw edge factor, walkers, walk length, app, tp
-    "c1": dict(scale=16, edge_factor=16, walkers=4096, length=80, app="deepwalk", tp=0.0,
+    "c1": dict(graph="rmat", scale=16, edge_factor=16, kind="walk", mode="offline", units=4096, length=80,
+               app="deepwalk", tp=0.0,
                desc="BASELINE config 1: biased offline DeepWalk, R-MAT scale 16, 4,096 walkers x 80"),
-    "c2": dict(scale=22, edge_factor=16, walkers=40000, length=80, app="deepwalk", tp=0.0,
+    "c2": dict(graph="rmat", scale=22, edge_factor=16, kind="walk", mode="offline", units=40000, length=80,
+               app="deepwalk", tp=0.0,
                desc="BASELINE config 2: biased offline DeepWalk, R-MAT scale 22, 40,000 walkers x 80"),
-    "c5": dict(scale=26, edge_factor=28, walkers=8000000, length=100, app="ppr", tp=0.15,
+    "c3": dict(graph="plaw", V=3070000, raw_edges=117000000, exponent=2.1, dmin=12.0, cap=33000, kind="walk",
+               mode="online", units=40000, length=80, app="node2vec", tp=0.0, p=2.0, q=0.5,
+               desc="BASELINE config 3: online biased node2vec p=2 q=0.5 (rejection), undirected power-law graph "
+                    "3.07M vertices / 117M undirected edges, degree ~ Zipf 2.1 capped at 33k, 40,000 walkers x 80"),
+    "c4": dict(graph="rmat", scale=23, V=4850000, raw_edges=72000000, kind="khop", mode="online", units=65536,
+               fanout=[25, 10],
+               desc="BASELINE config 4: online biased 2-hop sampling, fan-out 25 then 10 with replacement, "
+                    "R-MAT-like directed graph 4.85M vertices / ~69M edges, batches of 65,536 random seeds"),
+    "c5": dict(graph="rmat", scale=26, edge_factor=28, kind="walk", mode="offline", units=8000000, length=100,
+               app="ppr", tp=0.15,
                desc="BASELINE config 5: biased offline PPR tp=0.15 max length 100, R-MAT scale 26 "
                     "(~1.8G directed edges), 8M walkers sharded over the GPUs"),
-    "dw26": dict(scale=26, edge_factor=28, walkers=8000000, length=80, app="deepwalk", tp=0.0,
+    "dw26": dict(graph="rmat", scale=26, edge_factor=28, kind="walk", mode="offline", units=8000000, length=80,
+                 app="deepwalk", tp=0.0,
                  desc="biased offline DeepWalk, R-MAT scale 26 (~1.8G directed edges), 8M walkers x 80"),
-    "c5s": dict(scale=22, edge_factor=28, walkers=1000000, length=100, app="ppr", tp=0.15,
-                desc="reduced config 5 for profiling: PPR on R-MAT scale 22, 1M walkers"),
+    "c5s": dict(graph="rmat", scale=22, edge_factor=28, kind="walk", mode="offline", units=1000000, length=100,
+                app="ppr", tp=0.15, desc="reduced config 5 for profiling: PPR on R-MAT scale 22, 1M walkers"),
 }
 GRAPH_SEED, WEIGHT_SEED, START_SEED, WALK_SEED = 1, 7, 42, 42
-ALG_BYTES_PER_EDGE = 24   # 8 offsets + 8 slot + 4 neighbour + 4 path store
-ALG_BYTES_PER_BUILD_EDGE = 12  # 4 weight + 8 slot
+ALG_BYTES_PER_EDGE = 24        # offline step: 8 offsets + 8 slot + 4 neighbour + 4 path store
+ALG_BYTES_PER_BUILD_EDGE = 12  # offline build: 4 weight + 8 slot
 
 
 def measured_peak():
@@ -120,47 +132,81 @@ def combine_over_ranks(dist, values, device=None):
 
 
 def make_graph(ctx, wl):
-    raw = wl["edge_factor"] << wl["scale"]
-    ctx.generate_rmat(wl["scale"], raw, 0.57, 0.19, 0.19, False, GRAPH_SEED, WEIGHT_SEED)
+    if wl["graph"] == "plaw":
+        ctx.generate_powerlaw(wl["V"], wl["raw_edges"], wl["exponent"], wl["dmin"], wl["cap"], GRAPH_SEED, WEIGHT_SEED)
+    else:
+        raw = wl.get("raw_edges") or (wl["edge_factor"] << wl["scale"])
+        ctx.generate_rmat(wl["scale"], raw, 0.57, 0.19, 0.19, False, GRAPH_SEED, WEIGHT_SEED,
+                          num_vertices=wl.get("V", 0))
     return ctx.graph_info()
 
 
-def cpu_leg(ctx, wl, app_id, threads, want_seconds=12.0):
-    """Time the CPU oracle on a bounded sample of the workload: alias build over a vertex range and
-    walks over a walker range, same inputs (downloaded from the GPU), same Philox streams."""
+def app_id(wl):
+    from skywalker_b200 import APP_DEEPWALK, APP_NODE2VEC, APP_PPR
+    return {"deepwalk": APP_DEEPWALK, "ppr": APP_PPR, "node2vec": APP_NODE2VEC}[wl.get("app", "deepwalk")]
+
+
+def cpu_leg(ctx, wl, threads, want_seconds=12.0):
+    """Time the CPU oracle on a bounded sample of the workload, same inputs (downloaded from the GPU)
+    and same Philox streams: alias build over a vertex prefix, then the workload's own step."""
     from oracle import oracle as O
     V, E, _ = ctx.graph_info()
     xadj, adjncy, wgt = ctx.download()
     threads = threads or O.num_threads()
-    # alias build: a vertex prefix holding ~1/16 of the edges (bounded)
+    online = wl["mode"] == "online"
     target = min(E, max(1 << 20, E // 16))
-    v_end = int(np.searchsorted(xadj, target, side="left"))
-    v_end = max(1, min(V, v_end))
+    v_end = max(1, min(V, int(np.searchsorted(xadj, target, side="left"))))
     t0 = time.perf_counter()
     O.alias_build(xadj, wgt, 0, v_end, threads)
-    t_build = time.perf_counter() - t0
-    build_eps = float(xadj[v_end]) / t_build
-    del wgt
-    prob, alias, valid = ctx.alias_export()
-    # walks: calibrate on a small range, then size the sample for ~want_seconds
-    hop = wl["length"] + 1
-    n_total = wl["walkers"]
-    probe = min(n_total, 100000)
-    starts = O.gen_starts(n_total if n_total <= 2000000 else 2000000, V, START_SEED)
+    build_eps = float(xadj[v_end]) / (time.perf_counter() - t0)
+    if online:
+        table = None
+    else:
+        wgt = np.zeros(1, np.float32)
+        table = ctx.alias_export()
+    n_total = wl["units"]
+    cap = min(n_total, 2000000)
+    starts = O.gen_starts(cap, V, START_SEED)
+
+    def run(n):
+        if wl["kind"] == "khop":
+            _, sl = O.khop(xadj, adjncy, wgt, table, starts[:n], wl["fanout"], online=online, seed=WALK_SEED,
+                           threads=threads)
+            return int(sl.sum())
+        _, l = O.walk(xadj, adjncy, wgt, table, starts[:n], wl["length"] + 1, app=app_id(wl), online=online,
+                      tp=wl.get("tp", 0.0), p=wl.get("p", 2.0), q=wl.get("q", 0.5), seed=WALK_SEED, threads=threads)
+        return int(l.sum())
+
+    probe = max(1, min(cap, 100000 if not online else 256))
     t0 = time.perf_counter()
-    _, l0 = O.walk(xadj, adjncy, np.zeros(1, np.float32), (prob, alias, valid), starts[:probe], hop, app=app_id,
-                   tp=wl["tp"], seed=WALK_SEED, threads=threads)
+    run(probe)
     t_probe = time.perf_counter() - t0
-    n_s = int(min(len(starts), max(probe, probe * want_seconds / max(t_probe, 1e-6))))
+    n_s = int(min(cap, max(probe, probe * want_seconds / max(t_probe, 1e-6))))
     t0 = time.perf_counter()
-    _, l1 = O.walk(xadj, adjncy, np.zeros(1, np.float32), (prob, alias, valid), starts[:n_s], hop, app=app_id,
-                   tp=wl["tp"], seed=WALK_SEED, threads=threads)
-    t_walk = time.perf_counter() - t0
-    eps = float(l1.sum()) / t_walk
-    return {"value": eps, "unit": "sampled edges/s", "cores": threads, "kind": "port",
-            "sample": "first %d of %d walkers (%.2f s); alias build of the first %d vertices / %d edges: %.3g edges/s"
-                      % (n_s, n_total, t_walk, v_end, int(xadj[v_end]), build_eps),
-            "alias_build_edges_per_s": build_eps, "seconds": t_walk, "edges": int(l1.sum())}
+    edges = run(n_s)
+    t_run = time.perf_counter() - t0
+    return {"value": edges / t_run, "unit": "sampled edges/s", "cores": threads, "kind": "port",
+            "sample": "first %d of %d %s (%.2f s); alias build of the first %d vertices / %d edges: %.3g edges/s"
+                      % (n_s, n_total, "seeds" if wl["kind"] == "khop" else "walkers", t_run, v_end,
+                         int(xadj[v_end]), build_eps),
+            "alias_build_edges_per_s": build_eps, "seconds": t_run, "edges": edges}
+
+
+def online_algorithmic_bytes(ctx, wl, result, lengths):
+    """Algorithmic bytes of one online step from the realised frontier: 16 + 4*deg(v) per walk step,
+    8 + 4*deg(v) per frontier vertex plus 8 per sample for k-hop."""
+    xadj = ctx.download(weights=False)[0].astype(np.int64)
+    deg = np.diff(xadj)
+    if wl["kind"] == "khop":
+        data, sl = result, lengths
+        f1 = wl["fanout"][0]
+        parents = np.concatenate([data[:, 0], data[:, 1:1 + f1].reshape(-1)])
+        parents = parents[parents != 0xFFFFFFFF]
+        return float((8 + 4 * deg[parents]).sum() + 8 * int(sl.sum()))
+    paths, lens = result, lengths
+    hop = paths.shape[1]
+    live = np.arange(hop)[None, :] < lens[:, None]
+    return float((16 + 4 * deg[paths[live]]).sum())
 
 
 def main():
@@ -179,19 +225,21 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.warmup < 3:
-        args.warmup = 3
+    args.warmup = max(args.warmup, 3)
 
     import torch
-    from skywalker_b200 import APP_DEEPWALK, APP_PPR
-    app_id = APP_PPR if wl["app"] == "ppr" else APP_DEEPWALK
-    hop = wl["length"] + 1
-    config = {"workload": args.workload + ": " + wl["desc"], "graph": "R-MAT a/b/c/d=0.57/0.19/0.19/0.05",
-              "scale": wl["scale"], "raw_edge_factor": wl["edge_factor"], "walkers_total": wl["walkers"],
-              "hop_num": hop, "tp": wl["tp"], "seeds": {"graph": GRAPH_SEED, "weight": WEIGHT_SEED,
-                                                        "start": START_SEED, "walk": WALK_SEED},
+    from skywalker_b200 import MODE_OFFLINE, MODE_ONLINE
+    online = wl["mode"] == "online"
+    mode = MODE_ONLINE if online else MODE_OFFLINE
+    khop = wl["kind"] == "khop"
+    hop = wl.get("length", 0) + 1
+    config = {"workload": args.workload + ": " + wl["desc"], "units_total": wl["units"], "mode": wl["mode"],
+              "seeds": {"graph": GRAPH_SEED, "weight": WEIGHT_SEED, "start": START_SEED, "walk": WALK_SEED},
               "cache": "inputs larger than L2 (table and CSR are GBs; no flush needed)",
-              "parallelism": "walkers sharded, graph+tables replicated"}
+              "parallelism": "units sharded by global id, graph+tables replicated"}
+    for k in ("scale", "edge_factor", "raw_edges", "length", "tp", "p", "q", "fanout"):
+        if k in wl:
+            config[k] = wl[k]
 
     if args.impl == "reference":
         if rank != 0:
@@ -203,18 +251,16 @@ def main():
         torch.cuda.set_device(local_rank)
         ctx = Context(local_rank)
         V, E, md = make_graph(ctx, wl)
-        ctx.alias_build_offline()
-        vals = []
-        for _ in range(max(1, min(args.steps, 3))):
-            leg = cpu_leg(ctx, wl, app_id, args.cpu_threads, want_seconds=10.0)
-            vals.append(leg)
-        best = max(vals, key=lambda d: d["value"])
-        ms = best["seconds"] * 1e3
+        if not online:
+            ctx.alias_build_offline()
+        legs = [cpu_leg(ctx, wl, args.cpu_threads, want_seconds=10.0) for _ in range(max(1, min(args.steps, 3)))]
+        best = max(legs, key=lambda d: d["value"])
         out = {"impl": "reference", "metric": "sampled edges/s", "value": best["value"], "unit": "sampled edges/s",
-               "n_gpus": args.gpus, "steps": len(vals), "warmup": 0, "ms_per_step": ms, "higher_is_better": True,
-               "scaling": "strong", "vs_baseline": None, "dtype": "u32 ids / f32 prob", "data": "synthetic",
-               "config": dict(config, V=V, E=E, inputs="generated on the GPU by the library's seeded R-MAT generator, "
-                              "then copied to the host; only the CPU walk is timed"),
+               "n_gpus": args.gpus, "steps": len(legs), "warmup": 0, "ms_per_step": best["seconds"] * 1e3,
+               "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32 ids / f32 prob",
+               "data": "synthetic",
+               "config": dict(config, V=V, E=E, inputs="generated on the GPU by the library's seeded generator, then "
+                              "copied to the host; only the CPU path is timed"),
                "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
                "e2e": {"value": best["value"], "unit": "sampled edges/s", "h2d_bytes_per_step": 0,
                        "d2h_bytes_per_step": 0}}
@@ -238,36 +284,50 @@ def main():
     t0 = time.perf_counter()
     V, E, max_deg = make_graph(ctx, wl)
     t_gen = time.perf_counter() - t0
-    build_ms = [ctx.alias_build_offline() for _ in range(3)]
-    build_best = min(build_ms)
     peak, peak_kind = measured_peak()
+    build_best = min(ctx.alias_build_offline() for _ in range(3))   # reported for every workload
 
-    n_total = wl["walkers"]
+    n_total = wl["units"]
     lo, n_local = shard(n_total, world, rank)
-    starts = torch.empty(max(n_local, 1), dtype=torch.int32, device=dev)
-    paths = torch.empty(max(n_local, 1) * hop, dtype=torch.int32, device=dev)
-    lengths = torch.empty(max(n_local, 1), dtype=torch.int32, device=dev)
+    nl = max(n_local, 1)
+    starts = torch.empty(nl, dtype=torch.int32, device=dev)
+    if khop:
+        cells, lens_per = Context.khop_layout(wl["fanout"])
+        result = torch.empty(nl * cells, dtype=torch.int32, device=dev)
+        lengths = torch.empty(nl * lens_per, dtype=torch.int32, device=dev)
+    else:
+        result = torch.empty(nl * hop, dtype=torch.int32, device=dev)
+        lengths = torch.empty(nl, dtype=torch.int32, device=dev)
     ctx.generate_starts(n_local, START_SEED, starts, id_base=lo)
     torch.cuda.synchronize()
 
-    def step(i):
-        return ctx.walk(starts, hop, app=app_id, tp=wl["tp"], seed=WALK_SEED + i, walker_base=lo, paths=paths,
-                        lengths=lengths, n=n_local)
+    def step(i, s=starts, r=result, l=lengths):
+        """One pass over the batch; a new seed (and for k-hop a new batch of seed vertices) every step."""
+        if khop:
+            if s is starts:
+                ctx.generate_starts(n_local, START_SEED + i, starts, id_base=lo)
+            return ctx.sample_khop(s, wl["fanout"], mode=mode, seed=WALK_SEED + i, instance_base=lo, data=r,
+                                   sample_lengths=l, n=n_local)
+        return ctx.walk(s, hop, app=app_id(wl), mode=mode, tp=wl.get("tp", 0.0), p=wl.get("p", 2.0),
+                        q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, paths=r, lengths=l, n=n_local)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # the same walks over the plain 8-byte slot table first (3 accesses per step), for comparison
-    slots_ms, slots_edges = [], 0
-    for i in range(args.warmup + 2):
-        _, _, ms, edges = step(100 + i)
-        if i >= args.warmup:
-            slots_ms.append(ms)
-            slots_edges += edges
-    records_build_ms = None
-    if not args.no_records:
+    slots_info, records_build_ms = None, None
+    use_records = (not online) and (not khop) and wl.get("app") != "node2vec" and not args.no_records
+    if use_records:
+        # the same walks over the plain 8-byte slot table first (3 accesses per step), for comparison
+        ms_list, e_sum = [], 0
+        for i in range(args.warmup + 2):
+            _, _, ms, edges = step(100 + i)
+            if i >= args.warmup:
+                ms_list.append(ms)
+                e_sum += edges
+        slots_info = {"kernel_ms_per_step": float(np.mean(ms_list)), "value": e_sum / (sum(ms_list) * 1e-3),
+                      "unit": "sampled edges/s (this rank, kernel time)"}
         records_build_ms = ctx.walk_records_build()
     for i in range(args.warmup):
         step(i)
@@ -287,43 +347,47 @@ def main():
     clocks = sampler.stop()
     launches = ctx.kernel_launches - launches0
     span_ms = ev0.elapsed_time(ev1)
-
     mx, sm = combine_over_ranks(dist, [span_ms, kernel_ms, float(edges_local), float(launches)], dev)
     span_ms, kernel_ms = mx[0], mx[1]
     edges_all, launches = sm[2], int(sm[3])
     value = edges_all / (span_ms * 1e-3)
 
-    # end to end through the host-buffer entry point: pinned starts in, paths + lengths out
+    # algorithmic bytes of an online step need the realised frontier of the last step
+    online_bytes, last_edges = None, 1.0
+    if online and rank == 0:
+        res_h = result.cpu().numpy().view(np.uint32).reshape(nl, -1)
+        len_h = lengths.cpu().numpy().view(np.uint32)
+        online_bytes = online_algorithmic_bytes(ctx, wl, res_h, len_h.reshape(nl, -1) if khop else len_h)
+        last_edges = float(len_h.sum())
+
+    # end to end through the host-buffer entry point: pinned inputs in, full result arrays out
     e2e = None
     if not args.no_e2e:
-        h_starts = torch.empty(max(n_local, 1), dtype=torch.int32).pin_memory()
-        h_paths = torch.empty(max(n_local, 1) * hop, dtype=torch.int32).pin_memory()
-        h_len = torch.empty(max(n_local, 1), dtype=torch.int32).pin_memory()
+        h_starts = torch.empty(nl, dtype=torch.int32).pin_memory()
+        h_res = torch.empty(result.numel(), dtype=torch.int32).pin_memory()
+        h_len = torch.empty(lengths.numel(), dtype=torch.int32).pin_memory()
         h_starts.copy_(starts.cpu())
-        np_starts = h_starts.numpy().view(np.uint32)
-        np_paths = h_paths.numpy().view(np.uint32)
-        np_len = h_len.numpy().view(np.uint32)
-
-        def estep(i):
-            return ctx.walk(np_starts, hop, app=app_id, tp=wl["tp"], seed=WALK_SEED + i, walker_base=lo,
-                            paths=np_paths, lengths=np_len, n=n_local)
-        estep(0)
+        np_s, np_r, np_l = (t.numpy().view(np.uint32) for t in (h_starts, h_res, h_len))
+        if khop:
+            np_r, np_l = np_r.reshape(nl, -1), np_l.reshape(nl, -1)
+        step(0, np_s, np_r, np_l)
         barrier()
         e_steps = max(1, min(args.steps, 5))
         t0 = time.perf_counter()
         e_edges = 0
         for i in range(e_steps):
-            e_edges += estep(100 + i)[3]
+            e_edges += step(100 + i, np_s, np_r, np_l)[3]
         barrier()
         e_ms = (time.perf_counter() - t0) * 1e3
         m2, s2 = combine_over_ranks(dist, [e_ms, float(e_edges)], dev)
         e_ms, e_edges = m2[0], s2[1]
         e2e = {"value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
                "ms_per_step": e_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
-               "d2h_bytes_per_step": 4 * n_local * hop + 4 * n_local,
-               "note": "skw_walk with pinned host buffers: starts H2D, kernel, full path matrix + lengths D2H"}
+               "d2h_bytes_per_step": 4 * (result.numel() + lengths.numel()),
+               "note": "host-buffer entry point with pinned memory: start vertices H2D, kernels, full result "
+                       "arrays D2H"}
 
-    # NCCL gather of the per-walker lengths to rank 0 (results gather; outside the timed region)
+    # NCCL gather of the per-unit lengths to rank 0 (results gather; outside the timed region)
     gather_ms = None
     if dist is not None:
         bufs = [torch.empty_like(lengths) for _ in range(world)] if rank == 0 else None
@@ -336,43 +400,48 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_leg(ctx, wl, app_id, args.cpu_threads)
+        cpu = cpu_leg(ctx, wl, args.cpu_threads)
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample", "alias_build_edges_per_s")}
 
     if rank == 0:
-        per_launch_ms = kernel_ms / args.steps
-        edges_per_launch = edges_all / args.steps / world
-        achieved = edges_per_launch * ALG_BYTES_PER_EDGE / (per_launch_ms * 1e-3) / 1e9
+        per_step_ms = kernel_ms / args.steps
+        edges_per_step_rank = edges_all / args.steps / world
+        if online:
+            bytes_note = ("16 + 4*deg(v) bytes per walk step" if not khop else
+                          "8 + 4*deg(v) per frontier vertex + 8 per sample") + ", summed over the last step's frontier"
+            achieved = online_bytes / (per_step_ms * 1e-3) / 1e9 * (edges_per_step_rank / max(last_edges, 1.0))
+            kernel_name = "frontier_collect + degree-class builders + " + ("khop_hop_kernel" if khop else
+                                                                          "walk_online_step_kernel")
+        else:
+            bytes_note = "24 bytes per sampled edge"
+            achieved = edges_per_step_rank * ALG_BYTES_PER_EDGE / (per_step_ms * 1e-3) / 1e9
+            kernel_name = "walk_records_walk_kernel" if use_records else "walk_offline_kernel"
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tpath):
             try:
-                tj = json.load(open(tpath)).get(args.workload)
+                tj = json.load(open(tpath)).get(kernel_name)
                 if tj:
-                    traffic = tj["dram_bytes_per_sampled_edge"] * edges_per_launch
+                    traffic = tj["dram_bytes_per_sampled_edge"] * edges_per_step_rank
             except Exception:
                 traffic = None
+        build_gbs = E * ALG_BYTES_PER_BUILD_EDGE / (build_best * 1e-3) / 1e9
         out = {
             "metric": "sampled edges/s", "value": value, "unit": "sampled edges/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": span_ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u32 ids / f32 prob", "data": "synthetic",
-            "config": dict(config, V=V, E=E, max_degree=max_deg, walkers_per_gpu=n_local, graph_gen_s=t_gen),
-            "kernel_ms_per_step": per_launch_ms,
+            "config": dict(config, V=V, E=E, max_degree=max_deg, units_per_gpu=n_local, graph_gen_s=t_gen),
+            "kernel_ms_per_step": per_step_ms,
             "sampled_edges_per_step": edges_all / args.steps,
             "alias_build": {"value": E / (build_best * 1e-3), "unit": "edges/s", "ms": build_best,
-                            "roofline": {"bound": "hbm", "achieved": E * ALG_BYTES_PER_BUILD_EDGE / (build_best * 1e-3) / 1e9,
-                                         "peak": peak, "unit": "GB/s",
-                                         "frac": E * ALG_BYTES_PER_BUILD_EDGE / (build_best * 1e-3) / 1e9 / peak,
-                                         "peak_kind": peak_kind}},
-            "layout": "8-byte slots" if args.no_records else "fused 32-byte walk records",
-            "walk_records_build_ms": records_build_ms,
-            "slots_layout": {"kernel_ms_per_step": float(np.mean(slots_ms)),
-                             "value": slots_edges / (sum(slots_ms) * 1e-3) if slots_ms else None,
-                             "unit": "sampled edges/s (this rank, kernel time)"},
-            "roofline": {"bound": "hbm", "kernel": "walk_offline_kernel" if args.no_records else "walk_records_walk_kernel", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                         "algorithmic_bytes_per_sampled_edge": ALG_BYTES_PER_EDGE},
+                            "roofline": {"bound": "hbm", "achieved": build_gbs, "peak": peak, "unit": "GB/s",
+                                         "frac": build_gbs / peak, "peak_kind": peak_kind}},
+            "layout": "fused 32-byte walk records" if use_records else "8-byte slots",
+            "walk_records_build_ms": records_build_ms, "slots_layout": slots_info,
+            "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                         "algorithmic_bytes": bytes_note},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "result_gather_ms": gather_ms,
         }

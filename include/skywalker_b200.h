@@ -112,11 +112,13 @@ int skw_graph_free_weights(skw_ctx* ctx);
 
 /* Seeded synthetic graphs, generated on the GPU (stand-ins for the datasets of
  * scripts/fig8_biased.sh:9-24).  R-MAT: 2^scale vertices, raw_edges draws with quadrant
- * probabilities (a,b,c,1-a-b-c), ids scrambled by a fixed bijection, duplicates and self loops
- * removed, adjacency sorted; symmetric != 0 adds every reverse edge first.  Weights are
+ * probabilities (a,b,c,1-a-b-c), ids scrambled by a fixed bijection (then taken modulo
+ * num_vertices when 0 < num_vertices < 2^scale, for vertex counts that are not powers of two),
+ * duplicates and self loops removed, adjacency sorted; symmetric != 0 adds every reverse edge.  Weights are
  * 1 + 9 * k / 2^24 rounded down to a multiple of 2^-20, k a 24-bit Philox draw per edge. */
-int skw_graph_generate_rmat(skw_ctx* ctx, uint32_t scale, uint64_t raw_edges, double a, double b,
-                            double c, int symmetric, uint64_t graph_seed, uint64_t weight_seed);
+int skw_graph_generate_rmat(skw_ctx* ctx, uint32_t scale, uint32_t num_vertices, uint64_t raw_edges,
+                            double a, double b, double c, int symmetric, uint64_t graph_seed,
+                            uint64_t weight_seed);
 /* Power-law graph: vertex v gets target degree min(cap, floor(dmin * u^(-1/(exponent-1)))),
  * endpoints of raw_edges undirected edges are drawn proportionally to target degree, the edge
  * set is symmetrised, de-duplicated, self loops dropped, adjacency sorted. */

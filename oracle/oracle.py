@@ -50,7 +50,7 @@ def lib():
         L.orc_khop.argtypes = [u32p, u32p, f32p, f32p, u32p, u8p, C.c_int, C.c_uint32, u32p,
                                C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64, u32p, C.c_uint64, u32p, u32p,
                                C.c_int]
-        L.orc_gen_rmat.argtypes = [C.c_uint32, C.c_uint64, C.c_double, C.c_double, C.c_double,
+        L.orc_gen_rmat.argtypes = [C.c_uint32, C.c_uint32, C.c_uint64, C.c_double, C.c_double, C.c_double,
                                    C.c_int, C.c_uint64, C.POINTER(C.c_uint32),
                                    C.POINTER(C.c_uint64), C.POINTER(C.c_void_p),
                                    C.POINTER(C.c_void_p)]
@@ -86,10 +86,10 @@ def _take(ptr, n, dtype):
     return arr
 
 
-def gen_rmat(scale, raw_edges, a=0.57, b=0.19, c=0.19, symmetric=False, seed=1):
+def gen_rmat(scale, raw_edges, a=0.57, b=0.19, c=0.19, symmetric=False, seed=1, num_vertices=0):
     V, E = C.c_uint32(), C.c_uint64()
     px, pa = C.c_void_p(), C.c_void_p()
-    rc = lib().orc_gen_rmat(scale, raw_edges, a, b, c, int(symmetric), seed, C.byref(V),
+    rc = lib().orc_gen_rmat(scale, num_vertices, raw_edges, a, b, c, int(symmetric), seed, C.byref(V),
                             C.byref(E), C.byref(px), C.byref(pa))
     if rc:
         raise ValueError("orc_gen_rmat failed")

@@ -459,12 +459,13 @@ static void keys_to_csr(std::vector<u64>& keys, u32 V, u32** xadj_out, u32** adj
 // Seeded R-MAT (Chakrabarti et al.): raw_edges draws of `scale` quadrant choices each, one 32-bit
 // Philox word per level compared with integer thresholds; ids scrambled; self loops and
 // duplicates removed; adjacency sorted.
-int orc_gen_rmat(u32 scale, u64 raw_edges, double a, double b, double c, int symmetric, u64 seed,
-                 u32* V_out, u64* E_out, u32** xadj_out, u32** adjncy_out) {
+int orc_gen_rmat(u32 scale, u32 num_vertices, u64 raw_edges, double a, double b, double c,
+                 int symmetric, u64 seed, u32* V_out, u64* E_out, u32** xadj_out, u32** adjncy_out) {
   if (scale < 1 || scale > 31) return -1;
   const u32 ta = (u32)std::min(4294967295.0, a * 4294967296.0);
   const u32 tab = (u32)std::min(4294967295.0, (a + b) * 4294967296.0);
   const u32 tabc = (u32)std::min(4294967295.0, (a + b + c) * 4294967296.0);
+  const u32 fold = (num_vertices && num_vertices < (1u << scale)) ? num_vertices : 0;
   const u64 per = symmetric ? 2 : 1;
   std::vector<u64> keys(raw_edges * per);
 #pragma omp parallel for schedule(static)
@@ -481,11 +482,15 @@ int orc_gen_rmat(u32 scale, u64 raw_edges, double a, double b, double c, int sym
     }
     src = scramble(src, scale);
     dst = scramble(dst, scale);
+    if (fold) {
+      src %= fold;
+      dst %= fold;
+    }
     const bool loop = src == dst;  // self loops become a sentinel that sorts last
     keys[e * per] = loop ? ~(u64)0 : (((u64)src << 32) | dst);
     if (symmetric) keys[e * per + 1] = loop ? ~(u64)0 : (((u64)dst << 32) | src);
   }
-  *V_out = 1u << scale;
+  *V_out = fold ? fold : 1u << scale;
   keys_to_csr(keys, *V_out, xadj_out, adjncy_out, E_out);
   return 0;
 }

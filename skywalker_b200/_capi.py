@@ -43,7 +43,7 @@ SIGNATURES = {
     "skw_graph_download": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "skw_graph_device_ptrs": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "skw_graph_free_weights": (C.c_int, [C.c_void_p]),
-    "skw_graph_generate_rmat": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_double, C.c_double, C.c_double,
+    "skw_graph_generate_rmat": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_double, C.c_double, C.c_double,
                                           C.c_int, C.c_uint64, C.c_uint64]),
     "skw_graph_generate_powerlaw": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_double, C.c_double,
                                               C.c_uint32, C.c_uint64, C.c_uint64]),

@@ -99,8 +99,9 @@ class Context:
     def load_gr(self, path, weight_mode=0, weightrange=2, weight_seed=0):
         self._ck(self._lib.skw_graph_load_gr(self._h, path.encode(), weight_mode, weightrange, weight_seed))
 
-    def generate_rmat(self, scale, raw_edges, a=0.57, b=0.19, c=0.19, symmetric=False, graph_seed=1, weight_seed=7):
-        self._ck(self._lib.skw_graph_generate_rmat(self._h, scale, raw_edges, a, b, c, int(symmetric),
+    def generate_rmat(self, scale, raw_edges, a=0.57, b=0.19, c=0.19, symmetric=False, graph_seed=1, weight_seed=7,
+                      num_vertices=0):
+        self._ck(self._lib.skw_graph_generate_rmat(self._h, scale, num_vertices, raw_edges, a, b, c, int(symmetric),
                                                    graph_seed, weight_seed))
 
     def generate_powerlaw(self, V, raw_edges, exponent=2.1, dmin=8.0, cap=33000, graph_seed=1, weight_seed=7):

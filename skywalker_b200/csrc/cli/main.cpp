@@ -209,7 +209,7 @@ int run_device(int dev, Shared& sh, DevResult& out) {
   const bool bias = fb("bias");
   // graph: replicated in this GPU's HBM
   if (fi("rmat_scale") > 0) {
-    rc = skw_graph_generate_rmat(ctx, (uint32_t)fi("rmat_scale"), (uint64_t)fi("rmat_ef") << fi("rmat_scale"), 0.57,
+    rc = skw_graph_generate_rmat(ctx, (uint32_t)fi("rmat_scale"), 0, (uint64_t)fi("rmat_ef") << fi("rmat_scale"), 0.57,
                                  0.19, 0.19, 0, 1, 7);
   } else {
     int mode = 0;

@@ -23,7 +23,8 @@ __device__ __forceinline__ u32 scramble(u32 v, u32 scale) {
 // One raw edge per thread: `scale` quadrant choices, one Philox word each.
 __global__ void __launch_bounds__(256) rmat_keys_kernel(u64* __restrict__ keys, u64 raw_edges,
                                                         u32 scale, u32 ta, u32 tab, u32 tabc,
-                                                        int symmetric, u64 seed, u64 sentinel) {
+                                                        int symmetric, u64 seed, u64 sentinel,
+                                                        u32 fold) {
   for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < raw_edges; e += (u64)gridDim.x * blockDim.x) {
     u32 src = 0, dst = 0;
     Rand4 r{0, 0, 0, 0};
@@ -37,6 +38,10 @@ __global__ void __launch_bounds__(256) rmat_keys_kernel(u64* __restrict__ keys, 
     }
     src = scramble(src, scale);
     dst = scramble(dst, scale);
+    if (fold) {
+      src %= fold;
+      dst %= fold;
+    }
     const bool loop = src == dst;
     if (symmetric) {
       keys[2 * e] = loop ? sentinel : (((u64)src << 32) | dst);
@@ -159,12 +164,16 @@ using namespace skw;
 
 extern "C" {
 
-int skw_graph_generate_rmat(skw_ctx* ctx, uint32_t scale, uint64_t raw_edges, double a, double b,
-                            double c, int symmetric, uint64_t graph_seed, uint64_t weight_seed) {
+int skw_graph_generate_rmat(skw_ctx* ctx, uint32_t scale, uint32_t num_vertices, uint64_t raw_edges,
+                            double a, double b, double c, int symmetric, uint64_t graph_seed,
+                            uint64_t weight_seed) {
   if (!ctx) return SKW_ERR_ARG;
   if (scale < 1 || scale > 31) return fail(ctx, SKW_ERR_ARG, "skw_graph_generate_rmat: scale must be 1..31");
   if (!(a >= 0 && b >= 0 && c >= 0 && a + b + c <= 1.0))
     return fail(ctx, SKW_ERR_ARG, "skw_graph_generate_rmat: need a,b,c >= 0 and a+b+c <= 1");
+  if (num_vertices > (1u << scale) || num_vertices == 1)
+    return fail(ctx, SKW_ERR_ARG, "skw_graph_generate_rmat: num_vertices must be 0 or in 2..2^scale");
+  const u32 fold = (num_vertices && num_vertices < (1u << scale)) ? num_vertices : 0;
   DeviceGuard g(ctx->device);
   const u32 ta = (u32)fmin(4294967295.0, a * 4294967296.0);
   const u32 tab = (u32)fmin(4294967295.0, (a + b) * 4294967296.0);
@@ -176,10 +185,10 @@ int skw_graph_generate_rmat(skw_ctx* ctx, uint32_t scale, uint64_t raw_edges, do
   SKW_CUDA(ctx, cudaMalloc(&alt, sizeof(u64) * (count ? count : 1)));
   if (raw_edges) {
     rmat_keys_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(keys, raw_edges, scale, ta, tab, tabc,
-                                                                 symmetric, graph_seed, sentinel);
+                                                                 symmetric, graph_seed, sentinel, fold);
     ctx->launches++;
   }
-  int rc = keys_to_graph(ctx, keys, alt, count, 1u << scale, 33 + (int)scale, sentinel, weight_seed);
+  int rc = keys_to_graph(ctx, keys, alt, count, fold ? fold : 1u << scale, 33 + (int)scale, sentinel, weight_seed);
   cudaFree(keys);
   cudaFree(alt);
   return rc;

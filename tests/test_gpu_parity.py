@@ -39,6 +39,13 @@ def test_rmat_generator_matches_oracle(ctx, oracle):
         assert np.array_equal(w, oracle.gen_weights(len(oa), 6))
 
 
+def test_rmat_generator_folded_vertex_count(ctx, oracle):
+    ctx.generate_rmat(13, 100000, graph_seed=2, weight_seed=3, num_vertices=5000)
+    x, a, w = ctx.download()
+    ox, oa = oracle.gen_rmat(13, 100000, seed=2, num_vertices=5000)
+    assert len(x) == 5001 and np.array_equal(x, ox) and np.array_equal(a, oa)
+
+
 def test_powerlaw_generator_matches_oracle(ctx, oracle):
     ctx.generate_powerlaw(20000, 300000, 2.1, 4.0, 3000, graph_seed=5, weight_seed=11)
     x, a, w = ctx.download()
