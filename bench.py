@@ -278,7 +278,11 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     ctx = Context(local_rank)
-    stream = torch.cuda.current_stream()
+    # a dedicated stream shared by torch and the library, so that torch's events see the kernels
+    # (handle 0, torch's default stream, means "the context's own stream" to skw_ctx_set_stream)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    assert stream.cuda_stream != 0
     ctx.set_stream(stream.cuda_stream)
 
     t0 = time.perf_counter()
@@ -301,7 +305,7 @@ def main():
     ctx.generate_starts(n_local, START_SEED, starts, id_base=lo)
     torch.cuda.synchronize()
 
-    def step(i, s=starts, r=result, l=lengths):
+    def step(i, s=starts, r=result, l=lengths, enqueue_only=False):
         """One pass over the batch; a new seed (and for k-hop a new batch of seed vertices) every step."""
         if khop:
             if s is starts:
@@ -309,7 +313,8 @@ def main():
             return ctx.sample_khop(s, wl["fanout"], mode=mode, seed=WALK_SEED + i, instance_base=lo, data=r,
                                    sample_lengths=l, n=n_local)
         return ctx.walk(s, hop, app=app_id(wl), mode=mode, tp=wl.get("tp", 0.0), p=wl.get("p", 2.0),
-                        q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, paths=r, lengths=l, n=n_local)
+                        q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, paths=r, lengths=l, n=n_local,
+                        enqueue_only=enqueue_only)
 
     def barrier():
         if dist is not None:
@@ -337,16 +342,23 @@ def main():
     launches0 = ctx.kernel_launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kernel_ms, edges_local = 0.0, 0
+    # offline walks are queued back to back (no host round trip between steps); the online paths
+    # and k-hop return their counters per call
+    queued = (not online) and (not khop)
     ev0.record(stream)
     for i in range(args.steps):
-        _, _, ms, edges = step(100 + i)
-        kernel_ms += ms
-        edges_local += edges
+        _, _, ms, edges = step(100 + i, enqueue_only=queued)
+        if not queued:
+            kernel_ms += ms
+            edges_local += edges
     ev1.record(stream)
     barrier()
     clocks = sampler.stop()
     launches = ctx.kernel_launches - launches0
     span_ms = ev0.elapsed_time(ev1)
+    if queued:
+        edges_local = ctx.take_sampled_edges()
+        kernel_ms = span_ms     # one kernel per step and nothing else on the stream
     mx, sm = combine_over_ranks(dist, [span_ms, kernel_ms, float(edges_local), float(launches)], dev)
     span_ms, kernel_ms = mx[0], mx[1]
     edges_all, launches = sm[2], int(sm[3])

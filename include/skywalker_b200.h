@@ -209,6 +209,12 @@ int skw_walk_records_free(skw_ctx* ctx);
 int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_starts,
                     uint64_t n, uint32_t* d_paths, uint32_t* d_lengths, float* ms,
                     uint64_t* sampled_edges);
+/* Enqueue-only form: when ms and sampled_edges are both NULL, skw_walk_device returns as soon as
+ * the kernels are queued on the context's stream (no synchronisation, no readback), so back to
+ * back calls leave no host gap between kernels.  The sampled edges of such calls add up in the
+ * context; skw_ctx_take_sampled_edges() waits for the stream, reports a device error of any of
+ * them, returns the sum and clears it. */
+int skw_ctx_take_sampled_edges(skw_ctx* ctx, uint64_t* out);
 /* Same with host buffers: copies starts in, runs, copies paths and lengths out. */
 int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
              uint32_t* h_paths, uint32_t* h_lengths, float* ms, uint64_t* sampled_edges);

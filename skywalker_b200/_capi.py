@@ -54,6 +54,7 @@ SIGNATURES = {
     "skw_alias_device_ptrs": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "skw_alias_build_list_static": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_char_p, C.c_size_t]),
+    "skw_ctx_take_sampled_edges": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "skw_walk_records_build": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "skw_walk_records_free": (C.c_int, [C.c_void_p]),
     "skw_walk_device": (C.c_int, [C.c_void_p, C.POINTER(WalkParams), C.c_void_p, C.c_uint64, C.c_void_p,

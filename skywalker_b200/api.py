@@ -167,8 +167,10 @@ class Context:
 
     # -- walks
     def walk(self, starts, hop_num, app=APP_DEEPWALK, mode=MODE_OFFLINE, tp=0.0, p=2.0, q=0.5, seed=42,
-             walker_base=0, paths=None, lengths=None, n=None, walker_stride=1):
-        """Host arrays (numpy) or device buffers.  Returns (paths, lengths, ms, sampled_edges)."""
+             walker_base=0, paths=None, lengths=None, n=None, walker_stride=1, enqueue_only=False):
+        """Host arrays (numpy) or device buffers.  Returns (paths, lengths, ms, sampled_edges).
+        enqueue_only (device buffers only): queue the kernels and return at once with ms = edges = None;
+        collect the edge count later with take_sampled_edges()."""
         prm = WalkParams(app, mode, hop_num, tp, p, q, seed, walker_base, walker_stride)
         ms, edges = C.c_float(), C.c_uint64()
         if _is_device(starts):
@@ -182,9 +184,21 @@ class Context:
             if lengths is None:
                 lengths = np.zeros(n, np.uint32)
             fn = self._lib.skw_walk
+        if enqueue_only:
+            if fn is not self._lib.skw_walk_device:
+                raise ValueError("enqueue_only needs device buffers")
+            self._ck(fn(self._h, C.byref(prm), _ptr(starts) if n else None, n, _ptr(paths) if n else None,
+                        _ptr(lengths) if n else None, None, None))
+            return paths, lengths, None, None
         self._ck(fn(self._h, C.byref(prm), _ptr(starts) if n else None, n, _ptr(paths) if n else None,
                     _ptr(lengths) if n else None, C.byref(ms), C.byref(edges)))
         return paths, lengths, ms.value, edges.value
+
+    def take_sampled_edges(self):
+        """Wait for enqueued walks, raise on a device error of any of them, return their edge count."""
+        v = C.c_uint64()
+        self._ck(self._lib.skw_ctx_take_sampled_edges(self._h, C.byref(v)))
+        return v.value
 
     # -- k-hop
     @staticmethod

@@ -212,6 +212,7 @@ int skw_ctx_create(int device, skw_ctx** out) {
   CK(cudaMemset(ctx->d_err, 0, 4 * sizeof(uint32_t)));
   CK(cudaMallocHost(&ctx->h_err, 4 * sizeof(uint32_t)));
   CK(cudaMalloc(&ctx->d_sum, 2 * sizeof(uint64_t)));
+  CK(cudaMemset(ctx->d_sum, 0, 2 * sizeof(uint64_t)));
   CK(cudaMallocHost(&ctx->h_sum, 2 * sizeof(uint64_t)));
   CK(cudaMalloc(&ctx->cls_counts, 64 * sizeof(uint32_t)));
   CK(cudaMalloc(&ctx->frontier_cls, 64 * sizeof(uint32_t)));

@@ -64,8 +64,22 @@ __device__ __forceinline__ void dev_fail(u32* err, u32 code, u32 a, u32 b, u32 c
   }
 }
 
+// Read-only loads for data that is touched at random and used once.  A plain load that misses L1
+// pulls the whole 128-byte line from DRAM; these ask for the smallest L2 fetch (64 bytes) and do
+// not allocate in L1.  Same access rate on B200, half the DRAM traffic.
+__device__ __forceinline__ u32 ldg_once(const u32* p) {
+  u32 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::64B.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_once(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::64B.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
 __device__ __forceinline__ Slot load_slot(const Slot* p) {
-  const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+  const uint2 v = ldg_once(reinterpret_cast<const uint2*>(p));
   Slot s;
   s.prob = __uint_as_float(v.x);
   s.alias = v.y;

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256) khop_hop_kernel(const KhopArgs a) {
             const Slot sl = load_slot(a.slots + (u64)off + col);
             if (!(sl.prob < 0.0f)) {
               const u32 cand = u01(r.y) < sl.prob ? col : sl.alias;
-              out = __ldg(a.adjncy + (u64)off + cand);
+              out = ldg_once(a.adjncy + (u64)off + cand);
               got = a.fanout;
             }
           }

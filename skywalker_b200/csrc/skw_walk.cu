@@ -77,7 +77,7 @@ __device__ __forceinline__ bool walk_step(const WalkArgs& a, u64 gw, u32 step, u
       const Slot s = load_slot(a.slots + (u64)off + col);
       if (s.prob < 0.0f) return false;  // vertex without usable weight
       const u32 cand = u01(r.y) < s.prob ? col : s.alias;
-      next = __ldg(a.adjncy + (u64)off + cand);
+      next = ldg_once(a.adjncy + (u64)off + cand);
       const float f = next == prev ? a.inv_p : (connected(a.xadj, a.adjncy, prev, next) ? 1.0f : a.inv_q);
       if (__fmul_rn(u01(r.w), a.fmax) < f) break;
       if (++trial == kN2vMaxTrials) break;  // keep the last proposal
@@ -89,7 +89,7 @@ __device__ __forceinline__ bool walk_step(const WalkArgs& a, u64 gw, u32 step, u
   const Slot s = load_slot(a.slots + (u64)off + col);
   if (s.prob < 0.0f) return false;
   const u32 cand = u01(r.y) < s.prob ? col : s.alias;
-  next = __ldg(a.adjncy + (u64)off + cand);
+  next = ldg_once(a.adjncy + (u64)off + cand);
   return true;
 }
 
@@ -185,8 +185,11 @@ struct __align__(32) WalkRecord {
   u32 w[8];
 };
 
+// One 256-bit load.  By default an L1 miss pulls the whole 128-byte line (4 sectors) from DRAM; a
+// record is one sector and is used once, so ask for the smallest L2 fetch (64 bytes) and keep it
+// out of L1.  Measured on B200: same access rate, half the DRAM traffic.
 __device__ __forceinline__ void load_record(const WalkRecord* p, u32 (&w)[8]) {
-  asm volatile("ld.global.nc.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+  asm volatile("ld.global.nc.L1::no_allocate.L2::64B.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
                : "l"(p));
 }
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
       off = 0;
       deg = 0;
     } else {
-      const uint2 vi = __ldg(a.vinfo + cur);
+      const uint2 vi = ldg_once(a.vinfo + cur);
       off = vi.x;
       deg = vi.y;
     }
@@ -362,6 +365,21 @@ int skw_walk_records_build(skw_ctx* ctx, float* ms) {
   return SKW_OK;
 }
 
+int skw_ctx_take_sampled_edges(skw_ctx* ctx, uint64_t* out) {
+  if (!ctx) return SKW_ERR_ARG;
+  DeviceGuard g(ctx->device);
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum + 1, ctx->d_sum + 1, sizeof(uint64_t), cudaMemcpyDeviceToHost, ctx->stream));
+  int rc = err_check(ctx, "enqueued walks");  // synchronises the stream
+  const uint64_t v = ctx->h_sum[1];
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum + 1, 0, sizeof(uint64_t), ctx->stream));
+  if (rc != SKW_OK) {
+    err_reset(ctx);
+    return rc;
+  }
+  if (out) *out = v;
+  return SKW_OK;
+}
+
 int skw_walk_records_free(skw_ctx* ctx) {
   if (!ctx) return SKW_ERR_ARG;
   DeviceGuard g(ctx->device);
@@ -416,9 +434,17 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   a.inv_q = prm->app == SKW_APP_NODE2VEC ? 1.0f / prm->q : 1.0f;
   a.fmax = fmaxf(1.0f, fmaxf(a.inv_p, a.inv_q));
   cudaStream_t st = ctx->stream;
-  if ((rc = err_reset(ctx)) != SKW_OK) return rc;
-  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
-  SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+  // With both result pointers null the call only enqueues work: no reset, no readback, no
+  // synchronisation.  Sampled edges then add up in a second counter and a device error stays
+  // recorded until skw_ctx_take_sampled_edges() (or a later synchronous call) looks at it.
+  const bool enqueue_only = !ms && !sampled_edges;
+  if (enqueue_only) {
+    a.sum = reinterpret_cast<unsigned long long*>(ctx->d_sum) + 1;
+  } else {
+    if ((rc = err_reset(ctx)) != SKW_OK) return rc;
+    SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
+    SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+  }
   if (n) {
     if (!online && ctx->records && prm->app != SKW_APP_NODE2VEC) {
       RecordWalkArgs ra;
@@ -463,6 +489,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
       }
     }
   }
+  if (enqueue_only) return SKW_OK;
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
   SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
   if ((rc = err_check(ctx, "skw_walk")) != SKW_OK) return rc;

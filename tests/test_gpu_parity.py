@@ -241,6 +241,33 @@ def test_walk_sharding_is_invisible(ctx, oracle, rmat12):
     _cmp_walks(np.vstack([a, b]), np.concatenate([al, bl]), full, flen)
 
 
+def test_enqueue_only_walks(ctx, oracle, rmat12):
+    import torch
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    starts = oracle.gen_starts(2000, g.V, 3)
+    ref_p, ref_l, _, ref_e = ctx.walk(starts, 31, app=APP_PPR, tp=0.1, seed=5)
+    d_s = torch.from_numpy(starts.view(np.int32)).cuda()
+    d_p = torch.zeros(2000 * 31, dtype=torch.int32, device="cuda")
+    d_l = torch.zeros(2000, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        _, _, ms, e = ctx.walk(d_s, 31, app=APP_PPR, tp=0.1, seed=5, paths=d_p, lengths=d_l, enqueue_only=True)
+        assert ms is None and e is None
+    assert ctx.take_sampled_edges() == 3 * ref_e
+    assert ctx.take_sampled_edges() == 0
+    _cmp_walks(d_p.cpu().numpy().view(np.uint32).reshape(2000, 31), d_l.cpu().numpy().view(np.uint32), ref_p, ref_l)
+    # a bad start vertex in an enqueued call is reported when the count is taken, and not twice
+    from skywalker_b200.api import SkwError
+    d_s[0] = g.V + 7
+    ctx.walk(d_s, 31, paths=d_p, lengths=d_l, enqueue_only=True)
+    with pytest.raises(SkwError):
+        ctx.take_sampled_edges()
+    d_s[0] = 0
+    ctx.walk(d_s, 31, paths=d_p, lengths=d_l, enqueue_only=True)
+    assert ctx.take_sampled_edges() > 0
+
+
 def test_interleaved_walker_ids(ctx, oracle, rmat12):
     """Reference-style interleaving over 3 'GPUs' (id = dev + i*3) gives the rows of one big call."""
     g = rmat12
