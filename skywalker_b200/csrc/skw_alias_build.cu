@@ -26,7 +26,7 @@
 // Work distribution: vertices are binned by degree into eight classes with warp ballots and
 // shared-memory prefix sums (classify_* kernels); classes of degree <= 32 run one sub-warp
 // group of 4/8/16/32 lanes per vertex entirely in registers; degree <= 256 and <= 1024 one warp
-// per vertex, degree <= 12288 one CTA of 512 threads per vertex, with the two prefix lists in
+// per vertex, degree <= 4096 one CTA of 256 threads per vertex, with the two prefix lists in
 // shared memory; larger vertices one CTA of 1024 threads with the lists in a global scratch slab.
 #include <math_constants.h>
 
@@ -39,12 +39,12 @@
 namespace skw {
 
 // degree classes: groups of 4/8/16/32 lanes; one warp per vertex (two capacities); one CTA of
-// 512 threads with its lists in shared memory; one CTA of 1024 threads with its lists in a
-// global scratch slab
+// 256 threads with its lists in shared memory; one CTA of 1024 threads with its lists in a
+// global scratch slab, merged through shared-memory windows
 enum { K_G4 = 0, K_G8, K_G16, K_G32, K_W256, K_W1K, K_C, K_H, K_CLASSES };
 constexpr u32 kWarpSmallMax = 256;
 constexpr u32 kWarpMax = 1024;
-constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 12288: 12 bytes of list state per edge
+constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 4096: 12 bytes of list state per edge, 4 CTAs per SM
 
 __device__ __forceinline__ float sane_weight(float w) {
   return (w > 0.0f && w < CUDART_INF_F) ? w : 0.0f;
@@ -433,10 +433,82 @@ __device__ __forceinline__ float coop_max(float v, float* s_tmp) {
   return v;
 }
 
-template <int NT, int EPT>
+// Merge phase over one window: nl = Sl + Ll list entries (Sl smalls in sA[0..Sl), Ll larges from
+// the back: large j' at nl-1-j'), positions in sP alike.  dsx_in = deficit of all smalls before
+// the window, next_pos = position of the first large after the window (kNoNext if none).  Thread
+// t emits an equal share of the window's merged order.
+constexpr u32 kNoNext = 0xFFFFFFFFu;
+template <int NT>
+__device__ __forceinline__ void merge_window(u32 t, u32 nl, u32 Sl, const u64* sA, const u32* sP, u64 dsx_in,
+                                             u32 next_pos, u64 C, int B, u32 off, Slot* __restrict__ slots,
+                                             u32 v, u32* err) {
+  const u32 Ll = nl - Sl;
+  const u32 VT = (nl + NT - 1) / NT;
+  const u32 k0 = min(t * VT, nl), k1 = min(k0 + VT, nl);
+  if (k0 >= k1) return;
+  u32 i, j;
+  {
+    u32 lo = k0 > Ll ? k0 - Ll : 0, hi = min(k0, Sl);
+    while (lo < hi) {
+      const u32 mid = (lo + hi) >> 1;
+      const u64 a = mid ? sA[mid - 1] : dsx_in;    // key of small mid
+      const u64 b = sA[nl - 1 - (k0 - 1 - mid)];   // key of large k0-1-mid
+      if (a <= b) lo = mid + 1;
+      else hi = mid;
+    }
+    i = lo;
+    j = k0 - lo;
+  }
+  u64 dsx = i ? sA[i - 1] : dsx_in;  // deficit of the smalls before small i
+  for (u32 k = k0; k < k1; ++k) {
+    Slot out;
+    u32 p;
+    const u64 xl = j < Ll ? sA[nl - 1 - j] : 0;
+    // a small left over after the window's last large belongs to the first large of the next window
+    if (i < Sl && (j >= Ll || dsx <= xl)) {
+      p = sP[i];
+      const u64 dincl = sA[i];
+      u32 donor = j < Ll ? sP[nl - 1 - j] : next_pos;
+      if (donor == kNoNext) {
+        dev_fail(err, DEV_ERR_INTERNAL, v, p, 10);
+        donor = p;
+      }
+      out.alias = donor;
+      out.prob = mass_to_prob_fast(C - (dincl - dsx), B);
+      dsx = dincl;
+      ++i;
+    } else {
+      if (j >= Ll) {  // cannot happen: a window's share of larges is fixed by its boundaries
+        dev_fail(err, DEV_ERR_INTERNAL, v, k, 9);
+        break;
+      }
+      p = sP[nl - 1 - j];
+      if (dsx <= xl) {  // only possible once every small is placed: the large owns one full bucket
+        out.alias = p;
+        out.prob = 1.0f;
+      } else {
+        const u32 nx = j + 1 < Ll ? sP[nl - 2 - j] : next_pos;
+        if (nx == kNoNext) {
+          dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
+          out.alias = p;
+          out.prob = 1.0f;
+        } else {
+          out.alias = nx;
+          out.prob = mass_to_prob_fast(xl + C - dsx, B);
+        }
+      }
+      ++j;
+    }
+    slots[(u64)off + p] = out;
+  }
+}
+
+// WIN == 0: the lists A / P are in shared memory and are merged in place.  WIN > 0: they are in
+// global scratch and win_smem holds WIN * 12 + (NT + 1) * 4 bytes of shared memory for staging.
+template <int NT, int EPT, int WIN>
 __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __restrict__ wgt,
                                    Slot* __restrict__ slots, uint8_t* __restrict__ valid, u64* A,
-                                   u32* P, u64* s_tmp, u32* err) {
+                                   u32* P, u64* s_tmp, unsigned char* win_smem, u32* err) {
   const float* w = wgt + off;
   float wmax = 0.0f;
   for (u32 p = t; p < n; p += NT) wmax = fmaxf(wmax, sane_weight(__ldg(w + p)));
@@ -527,54 +599,51 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
     if (t == 0) valid[v] = 1;
     return;
   }
-  // merge-path partition: this thread emits merged outputs [k0, k1)
-  const u32 VT = (n + NT - 1) / NT;
-  const u32 k0 = min(t * VT, n), k1 = min(k0 + VT, n);
-  u32 i, j;
-  {
-    u32 lo = k0 > L ? k0 - L : 0, hi = min(k0, S);
-    while (lo < hi) {
-      const u32 mid = (lo + hi) >> 1;
-      const u64 a = mid ? A[mid - 1] : 0;         // key of small mid
-      const u64 b = A[n - 1 - (k0 - 1 - mid)];    // key of large k0-1-mid
-      if (a <= b) lo = mid + 1;
-      else hi = mid;
-    }
-    i = lo;
-    j = k0 - lo;
-  }
-  u64 dsx = i ? A[i - 1] : 0;  // deficit of the smalls before small i
-  for (u32 k = k0; k < k1; ++k) {
-    Slot out;
-    u32 p;
-    const u64 xl = j < L ? A[n - 1 - j] : 0;
-    if (i < S && j < L && dsx <= xl) {
-      p = P[i];
-      const u64 dincl = A[i];
-      out.alias = P[n - 1 - j];
-      out.prob = mass_to_prob_fast(C - (dincl - dsx), B);
-      dsx = dincl;
-      ++i;
-    } else {
-      if (j >= L) {  // cannot happen: the last merged element is always the last large
-        dev_fail(err, DEV_ERR_INTERNAL, v, k, 9);
-        break;
+  if constexpr (WIN == 0) {
+    merge_window<NT>(t, n, S, A, P, 0, kNoNext, C, B, off, slots, v, err);
+  } else {
+    // Lists live in global scratch: cut the merged order into windows of WIN outputs, stage each
+    // window's two list slices in shared memory with coalesced copies and merge it from there.
+    u64* sA = reinterpret_cast<u64*>(win_smem);
+    u32* sP = reinterpret_cast<u32*>(sA + WIN);
+    u32* bnd = sP + WIN;  // smalls before the start of each window of one round (NT + 1 entries)
+    const u32 nwin = (n + WIN - 1) / WIN;
+    for (u32 w0 = 0; w0 < nwin; w0 += NT - 1) {  // a round of cnt windows needs cnt + 1 boundaries
+      const u32 cnt = min((u32)NT - 1, nwin - w0);
+      coop_sync<NT>();
+      if (t <= cnt) {  // one bisection per window boundary, all in parallel
+        const u32 k0 = min((w0 + t) * (u32)WIN, n);
+        u32 lo = k0 > L ? k0 - L : 0, hi = min(k0, S);
+        while (lo < hi) {
+          const u32 mid = (lo + hi) >> 1;
+          const u64 a = mid ? A[mid - 1] : 0;
+          const u64 b = A[n - 1 - (k0 - 1 - mid)];
+          if (a <= b) lo = mid + 1;
+          else hi = mid;
+        }
+        bnd[t] = lo;
       }
-      p = P[n - 1 - j];
-      if (dsx <= xl) {  // only possible once every small is placed: the large owns one full bucket
-        out.alias = p;
-        out.prob = 1.0f;
-      } else if (j + 1 < L) {
-        out.alias = P[n - 2 - j];
-        out.prob = mass_to_prob_fast(xl + C - dsx, B);
-      } else {
-        dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
-        out.alias = p;
-        out.prob = 1.0f;
+      coop_sync<NT>();
+      for (u32 wi = 0; wi < cnt; ++wi) {
+        const u32 k0 = (w0 + wi) * (u32)WIN, k1 = min(k0 + (u32)WIN, n);
+        const u32 i0 = bnd[wi], i1 = bnd[wi + 1];
+        const u32 j0 = k0 - i0, j1 = k1 - i1;
+        const u32 Sl = i1 - i0, Ll = j1 - j0, nl = Sl + Ll;
+        for (u32 x = t; x < Sl; x += NT) {
+          sA[x] = A[i0 + x];
+          sP[x] = P[i0 + x];
+        }
+        for (u32 x = t; x < Ll; x += NT) {  // larges j0..j1-1 sit at global n-j1 .. n-j0-1
+          sA[Sl + x] = A[n - j1 + x];
+          sP[Sl + x] = P[n - j1 + x];
+        }
+        const u64 dsx_in = i0 ? A[i0 - 1] : 0;
+        const u32 next_pos = j1 < L ? P[n - 1 - j1] : kNoNext;
+        coop_sync<NT>();
+        merge_window<NT>(t, nl, Sl, sA, sP, dsx_in, next_pos, C, B, off, slots, v, err);
+        coop_sync<NT>();
       }
-      ++j;
     }
-    slots[(u64)off + p] = out;
   }
   if (t == 0) valid[v] = 1;
 }
@@ -602,14 +671,15 @@ __global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* _
       if (lane == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
       continue;
     }
-    build_vertex_merge<32, 4>(lane, v, off, n, wgt, slots, valid, A, P, nullptr, err);
+    build_vertex_merge<32, 4, 0>(lane, v, off, n, wgt, slots, valid, A, P, nullptr, nullptr, err);
     __syncwarp();
   }
 }
 
-// One CTA of NT threads per vertex of degree <= cap; lists in dynamic shared memory, or, when
-// scratch != nullptr, in this CTA's slab of global scratch (cap entries of 12 bytes).
-template <int NT>
+// One CTA of NT threads per vertex of degree <= cap.  WIN == 0: lists in dynamic shared memory.
+// WIN > 0: lists in this CTA's slab of global scratch (cap entries of 12 bytes), merged through
+// windows of WIN outputs staged in dynamic shared memory.
+template <int NT, int WIN>
 __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restrict__ worklist,
                                                              const u32* __restrict__ cls, int k,
                                                              const u32* __restrict__ xadj,
@@ -620,7 +690,7 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
                                                              u64 cap, u32* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ u64 s_tmp[3 * NT / 32];
-  unsigned char* store = scratch ? scratch + (u64)blockIdx.x * cap * 12ull : smem;
+  unsigned char* store = WIN ? scratch + (u64)blockIdx.x * cap * 12ull : smem;
   u64* A = reinterpret_cast<u64*>(store);
   u32* P = reinterpret_cast<u32*>(A + cap);
   const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
@@ -631,7 +701,7 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
       if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)cap);
       continue;
     }
-    build_vertex_merge<NT, 8>(threadIdx.x, v, off, n, wgt, slots, valid, A, P, s_tmp, err);
+    build_vertex_merge<NT, 8, WIN>(threadIdx.x, v, off, n, wgt, slots, valid, A, P, s_tmp, smem, err);
     __syncthreads();
   }
 }
@@ -817,9 +887,12 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
   constexpr int kCtaSmem = kLargeMax * 12;
   constexpr int kW256Smem = 8 * kWarpSmallMax * 12;
   constexpr int kW1KSmem = 8 * kWarpMax * 12;
+  constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
+  constexpr int kWinSmem = kWin * 12 + (1024 + 1) * 4;
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
-    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaSmem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaSmem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_warp_merge_kernel<kWarpMax, 8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kW1KSmem));
     attr_set[ctx->device & 63] = true;
@@ -852,12 +925,12 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
     SKW_LAUNCHED(ctx);
   }
   if (ctx->max_degree > kWarpMax) {
-    build_cta_merge_kernel<512><<<ctx->sm_count, 512, kCtaSmem, st>>>(
+    build_cta_merge_kernel<256, 0><<<ctx->sm_count * 4, 256, kCtaSmem, st>>>(
         worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
     SKW_LAUNCHED(ctx);
   }
   if (slab_elems) {
-    build_cta_merge_kernel<1024><<<gmem_ctas, 1024, 0, st>>>(
+    build_cta_merge_kernel<1024, kWin><<<gmem_ctas, 1024, kWinSmem, st>>>(
         worklist, cls, K_H, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid,
         static_cast<unsigned char*>(ctx->cta_scratch), slab_elems, ctx->d_err);
     SKW_LAUNCHED(ctx);

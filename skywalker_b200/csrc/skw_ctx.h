@@ -16,7 +16,7 @@ namespace skw {
 enum { CLS_G4 = 0, CLS_G8, CLS_G16, CLS_G32, CLS_CTA_SMEM, CLS_CTA_GMEM, CLS_COUNT };
 
 // Largest degree the shared-memory CTA builder takes (12 bytes of list state per edge).
-constexpr uint32_t kCtaSmemMaxDegree = 12288;
+constexpr uint32_t kCtaSmemMaxDegree = 4096;
 
 struct WalkRecord;  // skw_walk.cu
 
