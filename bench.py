@@ -353,12 +353,21 @@ def main():
             edges_local += edges
     ev1.record(stream)
     barrier()
-    clocks = sampler.stop()
     launches = ctx.kernel_launches - launches0
     span_ms = ev0.elapsed_time(ev1)
     if queued:
         edges_local = ctx.take_sampled_edges()
         kernel_ms = span_ms     # one kernel per step and nothing else on the stream
+    # the timed region can be shorter than one nvidia-smi sampling period: keep the same load running
+    # for a moment so that the clock samples are taken under it
+    t_hold = time.perf_counter()
+    while time.perf_counter() - t_hold < 0.7:
+        step(0, enqueue_only=queued)
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    clocks["note"] = "sampled over the timed region and 0.7 s of the same steps repeated after it"
+    if queued:
+        ctx.take_sampled_edges()    # drop the count of the extra steps
     mx, sm = combine_over_ranks(dist, [span_ms, kernel_ms, float(edges_local), float(launches)], dev)
     span_ms, kernel_ms = mx[0], mx[1]
     edges_all, launches = sm[2], int(sm[3])
@@ -395,9 +404,14 @@ def main():
         e_ms, e_edges = m2[0], s2[1]
         e2e = {"value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
                "ms_per_step": e_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
-               "d2h_bytes_per_step": 4 * (result.numel() + lengths.numel()),
-               "note": "host-buffer entry point with pinned memory: start vertices H2D, kernels, full result "
-                       "arrays D2H"}
+               # walks into pinned memory transfer the written cells of each row (length + 1) and the lengths;
+               # k-hop trees are dense and are copied whole
+               "d2h_bytes_per_step": (4 * (result.numel() + lengths.numel()) if khop else
+                                      int(4 * (e_edges / e_steps / world + 2 * n_local))),
+               "note": "host-buffer entry point with pinned memory: start vertices H2D, kernels, then "
+                       + ("the whole result tree D2H" if khop else
+                          "cells 0..length of every path row written into the pinned n x hop_num matrix by a "
+                          "kernel, plus the lengths D2H")}
 
     # NCCL gather of the per-unit lengths to rank 0 (results gather; outside the timed region)
     gather_ms = None

@@ -215,7 +215,11 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
  * context; skw_ctx_take_sampled_edges() waits for the stream, reports a device error of any of
  * them, returns the sum and clears it. */
 int skw_ctx_take_sampled_edges(skw_ctx* ctx, uint64_t* out);
-/* Same with host buffers: copies starts in, runs, copies paths and lengths out. */
+/* Same with host buffers: copies starts in, runs, copies paths and lengths out.  When h_paths is
+ * pinned memory (skw_host_alloc, cudaHostAlloc, cudaHostRegister) only the cells each walk wrote
+ * (0 .. length) are transferred, by a kernel writing into the mapped host matrix; the other cells
+ * keep what the caller had there.  With pageable memory the whole matrix is copied and cells past a
+ * walk's end are unspecified. */
 int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
              uint32_t* h_paths, uint32_t* h_lengths, float* ms, uint64_t* sampled_edges);
 

@@ -309,6 +309,23 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
   add_edges(a.sum, edges);
 }
 
+// Copy the written part of every path row (cells 0..length) from the device matrix into a host
+// matrix that the GPU can address (pinned memory), 8 lanes per row.  For PPR most rows hold a
+// handful of cells, so this moves a few percent of what a copy of the whole matrix would.
+__global__ void __launch_bounds__(256) copy_row_prefixes_kernel(const u32* __restrict__ src,
+                                                                u32* __restrict__ dst,
+                                                                const u32* __restrict__ lengths, u64 n,
+                                                                u32 hop_num) {
+  const u32 sub = threadIdx.x & 7;
+  const u64 rows_per_pass = ((u64)gridDim.x * blockDim.x) >> 3;
+  for (u64 w = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 3; w < n; w += rows_per_pass) {
+    const u32 cells = min(__ldg(lengths + w) + 1u, hop_num);
+    const u32* s = src + w * hop_num;
+    u32* d = dst + w * hop_num;
+    for (u32 c = sub; c < cells; c += 8) d[c] = s[c];
+  }
+}
+
 __global__ void __launch_bounds__(256) generate_starts_kernel(u32* __restrict__ starts, u64 n,
                                                               u64 id_base, u64 seed, u32 V) {
   for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (u64)gridDim.x * blockDim.x) {
@@ -515,7 +532,21 @@ int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts,
                        sampled_edges);
   if (rc != SKW_OK) return rc;
   if (n) {
-    SKW_CUDA(ctx, cudaMemcpyAsync(h_paths, ctx->stage[1], nb * prm->hop_num, cudaMemcpyDeviceToHost, ctx->stream));
+    // Pinned host memory is addressable by the GPU: write only the cells each walk produced.
+    // Pageable memory gets the whole matrix (cells past a walk's end then hold stale values).
+    cudaPointerAttributes at;
+    u32* mapped = nullptr;
+    if (cudaPointerGetAttributes(&at, h_paths) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer)
+      mapped = static_cast<u32*>(at.devicePointer);
+    else
+      cudaGetLastError();
+    if (mapped) {
+      copy_row_prefixes_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(
+          static_cast<const u32*>(ctx->stage[1]), mapped, static_cast<const u32*>(ctx->stage[2]), n, prm->hop_num);
+      SKW_LAUNCHED(ctx);
+    } else {
+      SKW_CUDA(ctx, cudaMemcpyAsync(h_paths, ctx->stage[1], nb * prm->hop_num, cudaMemcpyDeviceToHost, ctx->stream));
+    }
     SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths, ctx->stage[2], nb, cudaMemcpyDeviceToHost, ctx->stream));
   }
   SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

@@ -268,6 +268,25 @@ def test_enqueue_only_walks(ctx, oracle, rmat12):
     assert ctx.take_sampled_edges() > 0
 
 
+def test_walk_into_pinned_host_memory(ctx, oracle, rmat12):
+    """Pinned result buffers receive only the cells each walk wrote; the rest keeps the caller's bytes."""
+    import torch
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    starts = oracle.gen_starts(5000, g.V, 3)
+    ref_p, ref_l, _, ref_e = ctx.walk(starts, 101, app=APP_PPR, tp=0.15, seed=5)
+    pin_p = torch.full((5000, 101), 0x5A5A5A5A, dtype=torch.int32).pin_memory()
+    pin_l = torch.zeros(5000, dtype=torch.int32).pin_memory()
+    p, l, _, e = ctx.walk(starts, 101, app=APP_PPR, tp=0.15, seed=5, paths=pin_p.numpy().view(np.uint32),
+                          lengths=pin_l.numpy().view(np.uint32))
+    assert e == ref_e and np.array_equal(l, ref_l)
+    cols = np.arange(101)[None, :]
+    live = cols <= l[:, None]
+    assert np.array_equal(p[live], ref_p[live])
+    assert (p[~live] == 0x5A5A5A5A).all()
+
+
 def test_interleaved_walker_ids(ctx, oracle, rmat12):
     """Reference-style interleaving over 3 'GPUs' (id = dev + i*3) gives the rows of one big call."""
     g = rmat12
