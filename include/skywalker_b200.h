@@ -187,7 +187,13 @@ typedef struct skw_walk_params {
   uint64_t walker_stride; /* global id of walker i = walker_base + i * walker_stride; 0 means 1. *
                            * The reference interleaves walkers over GPUs (id = dev + i * ngpu,  *
                            * include/sampler.cuh:494-503): stride = ngpu reproduces that.         */
+  uint32_t flags;         /* SKW_WALK_* */
 } skw_walk_params;
+
+/* Online walks: keep the table of a vertex for the rest of the call once it has been built, instead
+ * of rebuilding the frontier's tables at every step (the reference's --cache flag, src/main.cu:74).
+ * The walks are identical; only the amount of build work changes. */
+#define SKW_WALK_CACHE_TABLES 1u
 
 /* Optional wider layout of the same table for offline DeepWalk / PPR.  No counterpart in the
  * reference (whose step reads xadj, prob_array, alias_array and adjncy separately,

@@ -12,13 +12,14 @@ SKW_OK = 0
 APP_DEEPWALK, APP_PPR, APP_NODE2VEC = 0, 1, 2
 MODE_OFFLINE, MODE_ONLINE = 0, 1
 KHOP_TAKE_ALL = 1
+WALK_CACHE_TABLES = 1
 INVALID_VERTEX = 0xFFFFFFFF
 
 
 class WalkParams(C.Structure):
     _fields_ = [("app", C.c_uint32), ("mode", C.c_uint32), ("hop_num", C.c_uint32),
                 ("tp", C.c_float), ("p", C.c_float), ("q", C.c_float),
-                ("seed", C.c_uint64), ("walker_base", C.c_uint64), ("walker_stride", C.c_uint64)]
+                ("seed", C.c_uint64), ("walker_base", C.c_uint64), ("walker_stride", C.c_uint64), ("flags", C.c_uint32)]
 
 
 class KhopParams(C.Structure):

@@ -20,7 +20,7 @@ import numpy as np
 
 from . import _capi
 from ._capi import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, INVALID_VERTEX, KHOP_TAKE_ALL,
-                    MODE_OFFLINE, MODE_ONLINE, KhopParams, WalkParams)
+                    MODE_OFFLINE, MODE_ONLINE, WALK_CACHE_TABLES, KhopParams, WalkParams)
 
 
 class SkwError(RuntimeError):
@@ -167,11 +167,11 @@ class Context:
 
     # -- walks
     def walk(self, starts, hop_num, app=APP_DEEPWALK, mode=MODE_OFFLINE, tp=0.0, p=2.0, q=0.5, seed=42,
-             walker_base=0, paths=None, lengths=None, n=None, walker_stride=1, enqueue_only=False):
+             walker_base=0, paths=None, lengths=None, n=None, walker_stride=1, enqueue_only=False, flags=0):
         """Host arrays (numpy) or device buffers.  Returns (paths, lengths, ms, sampled_edges).
         enqueue_only (device buffers only): queue the kernels and return at once with ms = edges = None;
         collect the edge count later with take_sampled_edges()."""
-        prm = WalkParams(app, mode, hop_num, tp, p, q, seed, walker_base, walker_stride)
+        prm = WalkParams(app, mode, hop_num, tp, p, q, seed, walker_base, walker_stride, flags)
         ms, edges = C.c_float(), C.c_uint64()
         if _is_device(starts):
             n = int(starts.numel()) if n is None else n

@@ -282,6 +282,7 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     p.seed = (uint64_t)fi("seed");
     p.walker_base = id_base;
     p.walker_stride = id_stride;
+    p.flags = fb("cache") ? SKW_WALK_CACHE_TABLES : 0;
     cudaMalloc(&d_data, sizeof(uint32_t) * std::max<long>(n_local, 1) * p.hop_num);
     cudaMalloc(&d_len, sizeof(uint32_t) * std::max<long>(n_local, 1));
     rc = skw_walk_device(ctx, &p, d_starts, n_local, d_data, d_len, &ms, &edges);

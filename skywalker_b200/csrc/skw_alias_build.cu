@@ -23,11 +23,12 @@
 // Every quantity is an integer or a single correctly rounded IEEE operation, so the table is a
 // pure function of the weight list: no atomics on masses, no dependence on scheduling.
 //
-// Work distribution: vertices are binned by degree into eight classes with warp ballots and
+// Work distribution: vertices are binned by degree into nine classes with warp ballots and
 // shared-memory prefix sums (classify_* kernels); classes of degree <= 32 run one sub-warp
 // group of 4/8/16/32 lanes per vertex entirely in registers; degree <= 256 and <= 1024 one warp
-// per vertex, degree <= 4096 one CTA of 256 threads per vertex, with the two prefix lists in
-// shared memory; larger vertices one CTA of 1024 threads with the lists in a global scratch slab.
+// per vertex, degree <= 4096 one CTA of 256 threads and degree <= 16384 one CTA of 1024 threads per
+// vertex, with the two prefix lists in shared memory; larger vertices one CTA of 1024 threads with
+// the lists in a global scratch slab, merged through shared-memory windows.
 #include <math_constants.h>
 
 #include <cstdarg>
@@ -41,10 +42,11 @@ namespace skw {
 // degree classes: groups of 4/8/16/32 lanes; one warp per vertex (two capacities); one CTA of
 // 256 threads with its lists in shared memory; one CTA of 1024 threads with its lists in a
 // global scratch slab, merged through shared-memory windows
-enum { K_G4 = 0, K_G8, K_G16, K_G32, K_W256, K_W1K, K_C, K_H, K_CLASSES };
+enum { K_G4 = 0, K_G8, K_G16, K_G32, K_W256, K_W1K, K_C, K_C2, K_H, K_CLASSES };
 constexpr u32 kWarpSmallMax = 256;
 constexpr u32 kWarpMax = 1024;
 constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 4096: 12 bytes of list state per edge, 4 CTAs per SM
+constexpr u32 kHugeSmemMax = 16384;           // one 1024-thread CTA per SM with 192 KB of lists
 
 __device__ __forceinline__ float sane_weight(float w) {
   return (w > 0.0f && w < CUDART_INF_F) ? w : 0.0f;
@@ -109,6 +111,7 @@ __device__ __forceinline__ int degree_class(u32 deg) {
   if (deg <= kWarpSmallMax) return K_W256;
   if (deg <= kWarpMax) return K_W1K;
   if (deg <= kLargeMax) return K_C;
+  if (deg <= kHugeSmemMax) return K_C2;
   return K_H;
 }
 
@@ -329,7 +332,8 @@ __device__ __forceinline__ void coop_sync() {
   else __syncthreads();
 }
 
-// Exclusive cross-thread prefix and total of one u64 per thread.
+// Exclusive cross-thread prefix and total of one u64 per thread.  In a CTA the warp totals are
+// scanned by the first warp (s_tmp: NT/32 + 1 entries).
 template <int NT>
 __device__ __forceinline__ void coop_scan_u64(u64& v, u64& total, u64* s_tmp) {
   const u32 lane = threadIdx.x & 31;
@@ -343,23 +347,28 @@ __device__ __forceinline__ void coop_scan_u64(u64& v, u64& total, u64* s_tmp) {
     total = __shfl_sync(0xFFFFFFFFu, inc, 31);
     v = inc - v;
   } else {
+    constexpr int NW = NT / 32;
     const u32 warp = threadIdx.x >> 5;
     __syncthreads();
     if (lane == 31) s_tmp[warp] = inc;
     __syncthreads();
-    u64 before = 0, all = 0;
+    if (warp == 0) {
+      u64 x = lane < NW ? s_tmp[lane] : 0, xi = x;
 #pragma unroll
-    for (int w = 0; w < NT / 32; ++w) {
-      const u64 t = s_tmp[w];
-      if ((u32)w < warp) before += t;
-      all += t;
+      for (int o = 1; o < 32; o <<= 1) {
+        const u64 t = __shfl_up_sync(0xFFFFFFFFu, xi, o);
+        if (lane >= (u32)o) xi += t;
+      }
+      if (lane < NW) s_tmp[lane] = xi - x;
+      if (lane == 31) s_tmp[NW] = xi;
     }
-    total = all;
-    v = before + inc - v;
+    __syncthreads();
+    total = s_tmp[NW];
+    v = s_tmp[warp] + inc - v;
   }
 }
-// The same for three values at once (one pair of barriers instead of three).  s_tmp holds
-// 3 * NT/32 entries.
+
+// The same for three values at once (s_tmp: 3 * (NT/32 + 1) entries).
 template <int NT>
 __device__ __forceinline__ void coop_scan3(u64& a, u64& b, u32& c, u64& ta, u64& tb, u32& tc, u64* s_tmp) {
   const u32 lane = threadIdx.x & 31;
@@ -384,36 +393,49 @@ __device__ __forceinline__ void coop_scan3(u64& a, u64& b, u32& c, u64& ta, u64&
     b = ib - b;
     c = ic - c;
   } else {
-    constexpr int NW = NT / 32;
+    constexpr int NW = NT / 32, ST = NW + 1;
     const u32 warp = threadIdx.x >> 5;
     __syncthreads();
     if (lane == 31) {
       s_tmp[warp] = ia;
-      s_tmp[NW + warp] = ib;
-      s_tmp[2 * NW + warp] = ic;
+      s_tmp[ST + warp] = ib;
+      s_tmp[2 * ST + warp] = ic;
     }
     __syncthreads();
-    u64 pa = 0, pb = 0, sa = 0, sb = 0;
-    u32 pc = 0, sc = 0;
+    if (warp == 0) {
+      u64 xa = lane < NW ? s_tmp[lane] : 0, xb = lane < NW ? s_tmp[ST + lane] : 0;
+      u32 xc = lane < NW ? (u32)s_tmp[2 * ST + lane] : 0;
+      u64 ya = xa, yb = xb;
+      u32 yc = xc;
 #pragma unroll
-    for (int w = 0; w < NW; ++w) {
-      const u64 va = s_tmp[w], vb = s_tmp[NW + w];
-      const u32 vc = (u32)s_tmp[2 * NW + w];
-      if ((u32)w < warp) {
-        pa += va;
-        pb += vb;
-        pc += vc;
+      for (int o = 1; o < 32; o <<= 1) {
+        const u64 pa = __shfl_up_sync(0xFFFFFFFFu, ya, o);
+        const u64 pb = __shfl_up_sync(0xFFFFFFFFu, yb, o);
+        const u32 pc = __shfl_up_sync(0xFFFFFFFFu, yc, o);
+        if (lane >= (u32)o) {
+          ya += pa;
+          yb += pb;
+          yc += pc;
+        }
       }
-      sa += va;
-      sb += vb;
-      sc += vc;
+      if (lane < NW) {
+        s_tmp[lane] = ya - xa;
+        s_tmp[ST + lane] = yb - xb;
+        s_tmp[2 * ST + lane] = yc - xc;
+      }
+      if (lane == 31) {
+        s_tmp[NW] = ya;
+        s_tmp[ST + NW] = yb;
+        s_tmp[2 * ST + NW] = yc;
+      }
     }
-    ta = sa;
-    tb = sb;
-    tc = sc;
-    a = pa + ia - a;
-    b = pb + ib - b;
-    c = pc + ic - c;
+    __syncthreads();
+    ta = s_tmp[NW];
+    tb = s_tmp[ST + NW];
+    tc = (u32)s_tmp[2 * ST + NW];
+    a = s_tmp[warp] + ia - a;
+    b = s_tmp[ST + warp] + ib - b;
+    c = (u32)s_tmp[2 * ST + warp] + ic - c;
   }
 }
 
@@ -689,7 +711,7 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
                                                              unsigned char* __restrict__ scratch,
                                                              u64 cap, u32* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ u64 s_tmp[3 * NT / 32];
+  __shared__ u64 s_tmp[3 * (NT / 32 + 1)];
   unsigned char* store = WIN ? scratch + (u64)blockIdx.x * cap * 12ull : smem;
   u64* A = reinterpret_cast<u64*>(store);
   u32* P = reinterpret_cast<u32*>(A + cap);
@@ -885,6 +907,7 @@ __device__ void build_vertex_cta(u32 v, u32 off, u32 n, const float* __restrict_
 static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
   cudaStream_t st = ctx->stream;
   constexpr int kCtaSmem = kLargeMax * 12;
+  constexpr int kCta2Smem = kHugeSmemMax * 12;
   constexpr int kW256Smem = 8 * kWarpSmallMax * 12;
   constexpr int kW1KSmem = 8 * kWarpMax * 12;
   constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
@@ -893,13 +916,14 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
   if (!attr_set[ctx->device & 63]) {
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCta2Smem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_warp_merge_kernel<kWarpMax, 8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kW1KSmem));
     attr_set[ctx->device & 63] = true;
   }
   // slabs of the global-scratch builder: one per CTA, sized by the largest degree
   const int gmem_ctas = ctx->sm_count;
-  const uint64_t slab_elems = ctx->max_degree > kLargeMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
+  const uint64_t slab_elems = ctx->max_degree > kHugeSmemMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
   if (slab_elems) {
     int rc = ensure_bytes(ctx, &ctx->cta_scratch, &ctx->cta_scratch_bytes, slab_elems * 12ull * gmem_ctas);
     if (rc != SKW_OK) return rc;
@@ -927,6 +951,11 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
   if (ctx->max_degree > kWarpMax) {
     build_cta_merge_kernel<256, 0><<<ctx->sm_count * 4, 256, kCtaSmem, st>>>(
         worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->max_degree > kLargeMax) {
+    build_cta_merge_kernel<1024, 0><<<ctx->sm_count, 1024, kCta2Smem, st>>>(
+        worklist, cls, K_C2, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kHugeSmemMax, ctx->d_err);
     SKW_LAUNCHED(ctx);
   }
   if (slab_elems) {
@@ -990,7 +1019,7 @@ __global__ void __launch_bounds__(256) frontier_collect_kernel(
 }
 
 int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 cells, u32 offs,
-                     const u32* alive_lengths) {
+                     const u32* alive_lengths, bool new_round) {
   if (units > 0xFFFFFFFFull) return fail(ctx, SKW_ERR_ARG, "frontier of %llu units is too large",
                                          (unsigned long long)units);
   const u32 cap = (u32)(units < ctx->V ? units : ctx->V);
@@ -1003,7 +1032,9 @@ int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 c
     SKW_CUDA(ctx, cudaMemsetAsync(ctx->stamp, 0, sizeof(u32) * ((size_t)ctx->V + 1), ctx->stream));
     ctx->stamp_round = 0;
   }
-  if (++ctx->stamp_round == 0) {  // wrapped: forget every old claim
+  if (!new_round && ctx->stamp_round != 0) {
+    // keep the round: vertices claimed earlier in this call are not collected (or built) again
+  } else if (++ctx->stamp_round == 0) {  // wrapped: forget every old claim
     SKW_CUDA(ctx, cudaMemsetAsync(ctx->stamp, 0, sizeof(u32) * ((size_t)ctx->V + 1), ctx->stream));
     ctx->stamp_round = 1;
   }

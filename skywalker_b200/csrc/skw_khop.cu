@@ -15,7 +15,7 @@
 namespace skw {
 
 int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 cells, u32 offs,
-                     const u32* alive_lengths);
+                     const u32* alive_lengths, bool new_round);
 
 struct KhopArgs {
   const u32* xadj;
@@ -169,7 +169,7 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
     khop_init_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(d_seeds, n, cells, d_data);
     SKW_LAUNCHED(ctx);
     for (uint32_t h = 0; h < prm->nhops; ++h) {
-      if (online && (rc = frontier_collect(ctx, d_data, n * width[h], width[h], cells, offs[h], nullptr)) != SKW_OK)
+      if (online && (rc = frontier_collect(ctx, d_data, n * width[h], width[h], cells, offs[h], nullptr, true)) != SKW_OK)
         return rc;
       a.offs_parent = offs[h];
       a.offs_child = offs[h + 1];

@@ -18,7 +18,7 @@ namespace skw {
 
 int build_from_worklists(skw_ctx* ctx, const u32* worklist, const u32* cls);
 int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 cells, u32 offs,
-                     const u32* alive_lengths);
+                     const u32* alive_lengths, bool new_round);
 int alloc_table(skw_ctx* ctx);
 
 constexpr u32 kAlive = 0xFFFFFFFFu;
@@ -496,7 +496,8 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
       walk_online_init_kernel<<<grid, 256, 0, st>>>(a);
       SKW_LAUNCHED(ctx);
       for (uint32_t step = 0; step + 1 < prm->hop_num; ++step) {
-        if ((rc = frontier_collect(ctx, d_paths, n, 1, prm->hop_num, step, d_lengths)) != SKW_OK) return rc;
+        if ((rc = frontier_collect(ctx, d_paths, n, 1, prm->hop_num, step, d_lengths,
+                                   step == 0 || !(prm->flags & SKW_WALK_CACHE_TABLES))) != SKW_OK) return rc;
         switch (prm->app) {
           case SKW_APP_DEEPWALK: walk_online_step_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, step); break;
           case SKW_APP_PPR: walk_online_step_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, step); break;

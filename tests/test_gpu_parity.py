@@ -94,7 +94,7 @@ def _star_graph(weights_per_vertex):
 def test_alias_every_degree_class_and_edge_cases(ctx, oracle):
     rng = np.random.default_rng(1)
     lists = []
-    for n in list(range(1, 70)) + [127, 128, 129, 200, 511, 512, 513, 1023, 1024, 1025, 4000, 8191, 8192, 8193, 20000, 70000]:
+    for n in list(range(1, 70)) + [127, 128, 129, 200, 511, 512, 513, 1023, 1024, 1025, 4000, 4096, 4097, 8191, 8192, 8193, 16384, 16385, 20000, 70000]:
         lists.append(rng.uniform(1, 10, n).astype(np.float32))
     lists.append(np.asarray([0.5] * 35 + [2.0] * 5, np.float32))       # reference smoke vector
     lists.append(np.full(40, 3.0, np.float32))                         # uniform
@@ -266,6 +266,21 @@ def test_enqueue_only_walks(ctx, oracle, rmat12):
     d_s[0] = 0
     ctx.walk(d_s, 31, paths=d_p, lengths=d_l, enqueue_only=True)
     assert ctx.take_sampled_edges() > 0
+
+
+def test_online_walk_with_cached_tables(ctx, oracle, plaw):
+    from skywalker_b200 import WALK_CACHE_TABLES
+    g = plaw
+    _upload(ctx, g)
+    starts = oracle.gen_starts(2000, g.V, 7)
+    a, al, _, ae = ctx.walk(starts, 41, app=APP_NODE2VEC, mode=MODE_ONLINE, seed=9)
+    launches = ctx.kernel_launches
+    b, bl, _, be = ctx.walk(starts, 41, app=APP_NODE2VEC, mode=MODE_ONLINE, seed=9, flags=WALK_CACHE_TABLES)
+    _cmp_walks(b, bl, a, al)
+    assert ae == be
+    c, cl, _, _ = ctx.walk(starts, 41, app=APP_NODE2VEC, mode=MODE_ONLINE, seed=10, flags=WALK_CACHE_TABLES)
+    d, dl, _, _ = ctx.walk(starts, 41, app=APP_NODE2VEC, mode=MODE_ONLINE, seed=10)
+    _cmp_walks(c, cl, d, dl)      # a new call starts a new round: nothing stale is reused wrongly
 
 
 def test_walk_into_pinned_host_memory(ctx, oracle, rmat12):
