@@ -445,6 +445,7 @@ int main(int argc, char** argv) {
     sampled += r.sampled;
   }
   const double mseps = max_s > 0 ? sampled / (double)max_s / 1e6 : 0.0;
+  LOGV("sampled_edges %llu\n", (unsigned long long)sampled);  // as src/offline_walk.cu:226 logs it
   if (!sh.gathered_lengths.empty()) {
     uint64_t total = 0;
     for (uint32_t l : sh.gathered_lengths) total += l;

@@ -78,3 +78,27 @@ def test_cli_presets_and_modes(gr_file):
     assert p.returncode == 2 and "outside this build" in p.stderr
     p = _run("--deepwalk", "--input", gr_file + ".missing", check=False)
     assert p.returncode == 2 and "cannot open" in p.stderr
+
+
+def _gpu_count():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+@pytest.mark.gpu
+def test_cli_two_gpus_same_total_as_one(gr_file):
+    """--ngpu 2 shards the walkers (interleaved ids) and gathers the lengths on GPU 0 over NCCL; the
+    walks, hence the sampled-edge total, do not depend on the GPU count."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    args = ["--ppr", "--bias=1", "--ol=0", "-n", "20000", "--input", gr_file, "-v"]
+    one = _run(*args, "--ngpu", "1").stdout
+    two = _run(*args, "--ngpu", "2").stdout
+    e1 = int(re.search(r"sampled_edges (\d+)", one).group(1))
+    e2 = int(re.search(r"sampled_edges (\d+)", two).group(1))
+    m = re.search(r"gathered (\d+) walk lengths on GPU 0 over NCCL, sum (\d+)", two)
+    assert m and int(m.group(1)) == 20000
+    assert e1 == e2 == int(m.group(2)) and e1 > 0

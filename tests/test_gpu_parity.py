@@ -380,3 +380,51 @@ def test_errors_are_reported_not_fatal(ctx, rmat12):
         ctx.alias_build_offline(10, 5)
     paths, lens, _, _ = ctx.walk(np.asarray([1], np.uint32), 5)   # context still usable
     assert paths[0, 0] == 1
+
+
+def test_degenerate_graphs(ctx, oracle):
+    # no edges at all
+    ctx.upload(np.zeros(6, np.uint32), np.zeros(0, np.uint32), np.zeros(0, np.float32))
+    assert ctx.graph_info() == (5, 0, 0)
+    ctx.alias_build_offline()
+    prob, alias, valid = ctx.alias_export()
+    assert len(prob) == 0 and (valid == 0).all()
+    for mode in (MODE_OFFLINE, MODE_ONLINE):
+        paths, lens, _, edges = ctx.walk(np.arange(5, dtype=np.uint32), 4, mode=mode)
+        assert edges == 0 and (lens == 0).all() and list(paths[:, 0]) == [0, 1, 2, 3, 4]
+        data, sl, _, e = ctx.sample_khop(np.arange(5, dtype=np.uint32), [3, 2], mode=mode)
+        assert e == 0 and (sl == 0).all() and (data[:, 1:] == 0xFFFFFFFF).all()
+    # one vertex with a self-contained 2-cycle partner, weights given as None (all ones)
+    ctx.upload(np.asarray([0, 1, 2], np.uint32), np.asarray([1, 0], np.uint32), None)
+    ctx.alias_build_offline()
+    paths, lens, _, edges = ctx.walk(np.asarray([0], np.uint32), 7)
+    assert list(paths[0]) == [0, 1, 0, 1, 0, 1, 0] and edges == 6
+    # bad arguments come back as errors, not faults
+    from skywalker_b200.api import SkwError
+    with pytest.raises(SkwError):
+        ctx.walk(np.asarray([0], np.uint32), 0)
+    with pytest.raises(SkwError):
+        ctx.walk(np.asarray([0], np.uint32), 5, app=APP_PPR, tp=1.5)
+    with pytest.raises(SkwError):
+        ctx.walk(np.asarray([0], np.uint32), 5, app=APP_NODE2VEC, p=0.0)
+    with pytest.raises(SkwError):
+        ctx.sample_khop(np.asarray([0], np.uint32), [3, 0])
+    with pytest.raises(SkwError):
+        ctx.upload(np.asarray([1, 2], np.uint32), np.asarray([0, 0], np.uint32), None)   # xadj[0] != 0
+
+
+def test_offline_table_survives_weight_release(ctx, oracle, rmat12):
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    ctx.free_weights()                                    # src/createTable.cu:175-177
+    starts = oracle.gen_starts(500, g.V, 1)
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    paths, lens, _, _ = ctx.walk(starts, 21, seed=2)
+    op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 21, seed=2)
+    _cmp_walks(paths, lens, op, ol)
+    from skywalker_b200.api import SkwError
+    with pytest.raises(SkwError):
+        ctx.walk(starts, 21, mode=MODE_ONLINE)            # online needs the weights
+    with pytest.raises(SkwError):
+        ctx.alias_build_offline()
