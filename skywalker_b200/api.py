@@ -45,6 +45,16 @@ def _is_device(x):
     return hasattr(x, "data_ptr") and getattr(x, "is_cuda", False)
 
 
+class DeviceArray:
+    """A borrowed 1-D device array, exported through __cuda_array_interface__ (version 2) so that
+    torch / cupy / numba can wrap it without a copy: torch.as_tensor(arr, device="cuda")."""
+
+    def __init__(self, ptr, n, typestr, owner=None):
+        self.ptr, self.n, self.owner = int(ptr or 0), int(n), owner
+        self.__cuda_array_interface__ = {"shape": (self.n,), "typestr": typestr, "data": (self.ptr, False),
+                                         "version": 2, "strides": None}
+
+
 class Context:
     """One GPU.  Owns the resident graph and alias table (reference: gpu_graph + Sampler state)."""
 
@@ -155,6 +165,20 @@ class Context:
         valid = np.ascontiguousarray(valid, np.uint8)
         pad = lambda a: a if a.size else np.zeros(1, a.dtype)
         self._ck(self._lib.skw_alias_import(self._h, _ptr(pad(prob)), _ptr(pad(alias)), _ptr(pad(valid))))
+
+    def alias_device_arrays(self):
+        """(slots as int64[E] -- one packed {f32 prob, u32 alias} per element --, valid as uint8[V]),
+        borrowed from the context: for collectives over table slices (multi-GPU sliced build)."""
+        V, E, _ = self.graph_info()
+        a, b = C.c_void_p(), C.c_void_p()
+        self._ck(self._lib.skw_alias_device_ptrs(self._h, C.byref(a), C.byref(b)))
+        return DeviceArray(a.value, E, "<i8", self), DeviceArray(b.value, V, "|u1", self)
+
+    def download_xadj(self):
+        V, _, _ = self.graph_info()
+        xadj = np.zeros(V + 1, np.uint32)
+        self._ck(self._lib.skw_graph_download(self._h, _ptr(xadj), None, None))
+        return xadj
 
     def walk_records_build(self):
         """Build the fused 32-byte walk records from the alias table; returns milliseconds."""
@@ -301,9 +325,25 @@ class _SampleResult:
         self.data, self.sample_lengths = data, sample_lengths
 
 
+def edge_balanced_ranges(xadj, parts):
+    """Vertex ranges holding ~E/parts edges each, as the reference cuts the table build between GPUs
+    (--edgecut, include/sampler.cuh:151-158): part r starts at the first vertex whose first edge is
+    at or after r * E / parts."""
+    E = int(xadj[-1])
+    V = len(xadj) - 1
+    cuts = [int(np.searchsorted(xadj[:V], E // parts * r, side="left")) for r in range(parts)] + [V]
+    cuts[0] = 0
+    return [(cuts[r], cuts[r + 1]) for r in range(parts)]
+
+
 def ConstructTable(sampler, ngpu=1, index=0):
-    """Build the alias table of every vertex; returns seconds (src/createTable.cu:119-179)."""
-    return sampler.ctx.alias_build_offline() * 1e-3
+    """Build the alias table; returns seconds (src/createTable.cu:119-179).  With ngpu > 1 builds the
+    edge-balanced slice `index` only; the caller assembles the slices (NCCL all-gather of
+    Context.alias_device_arrays() segments, replacing AliasTable::Assemble, include/gpu_graph.cuh:282-291)."""
+    if ngpu <= 1:
+        return sampler.ctx.alias_build_offline() * 1e-3
+    vb, ve = edge_balanced_ranges(sampler.ctx.download_xadj(), ngpu)[index]
+    return sampler.ctx.alias_build_offline(vb, ve) * 1e-3
 
 
 def _walk(walker, mode):

@@ -231,8 +231,58 @@ int run_device(int dev, Shared& sh, DevResult& out) {
   if (!bias) return fail_dev(out, nullptr, SKW_ERR_ARG, "--bias=0 (unbiased sampling) is outside this build");
   if (!online) {
     float ms = 0;
-    rc = skw_alias_build_offline(ctx, 0, V, &ms);
-    if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline");
+    bool sliced = false;
+#ifdef SKW_HAVE_NCCL
+    // More than one GPU: each builds the edge-balanced slice the reference would give it
+    // (--edgecut, include/sampler.cuh:151-158) and the slices are exchanged over NCCL, one broadcast
+    // per slice, straight into every GPU's table (the reference goes through pinned host memory,
+    // include/gpu_graph.cuh:282-291).  --dt=0 (shared host table) has no meaning here.
+    if (sh.ndev > 1 && !sh.comms.empty() && E > 0) {
+      std::vector<uint32_t> xadj((size_t)V + 1);
+      rc = skw_graph_download(ctx, xadj.data(), nullptr, nullptr);
+      if (rc) return fail_dev(out, ctx, rc, "skw_graph_download");
+      std::vector<uint32_t> cut(sh.ndev + 1);
+      for (int r = 0; r < sh.ndev; ++r)
+        cut[r] = r ? (uint32_t)(std::lower_bound(xadj.begin(), xadj.begin() + V, (uint32_t)(E / sh.ndev * r)) - xadj.begin()) : 0;
+      cut[sh.ndev] = V;
+      rc = skw_alias_build_offline(ctx, cut[dev], cut[dev + 1], &ms);
+      if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline (slice)");
+      const void* slots_c = nullptr;
+      const uint8_t* valid_c = nullptr;
+      skw_alias_device_ptrs(ctx, &slots_c, &valid_c);
+      uint64_t* slots = (uint64_t*)slots_c;  // 8-byte {prob, alias} slots
+      uint8_t* valid = (uint8_t*)valid_c;
+      cudaStream_t st;
+      cudaStreamCreate(&st);
+      cudaEvent_t e0, e1;
+      cudaEventCreate(&e0);
+      cudaEventCreate(&e1);
+      cudaEventRecord(e0, st);
+      ncclGroupStart();
+      for (int r = 0; r < sh.ndev; ++r) {
+        const size_t eb = xadj[cut[r]], ee = xadj[cut[r + 1]];
+        if (ee > eb) ncclBroadcast(slots + eb, slots + eb, ee - eb, ncclUint64, r, sh.comms[dev], st);
+        if (cut[r + 1] > cut[r])
+          ncclBroadcast(valid + cut[r], valid + cut[r], cut[r + 1] - cut[r], ncclUint8, r, sh.comms[dev], st);
+      }
+      ncclGroupEnd();
+      cudaEventRecord(e1, st);
+      cudaStreamSynchronize(st);
+      float gms = 0;
+      cudaEventElapsedTime(&gms, e0, e1);
+      LOGV("device %d: slice [%u,%u) built in %.2f ms, table slices exchanged over NCCL in %.2f ms\n", dev, cut[dev],
+           cut[dev + 1], ms, gms);
+      ms += gms;
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+      cudaStreamDestroy(st);
+      sliced = true;
+    }
+#endif
+    if (!sliced) {
+      rc = skw_alias_build_offline(ctx, 0, V, &ms);
+      if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline");
+    }
     out.table_ms = ms;
     if (fb("records") && fb("rw") && !fb("node2vec")) {
       rc = skw_walk_records_build(ctx, &ms);
@@ -414,12 +464,12 @@ int main(int argc, char** argv) {
     else if (!fb("v")) printf("%s\n", token.c_str());
   }
 #ifdef SKW_HAVE_NCCL
-  if (sh.ndev > 1 && fb("gather")) {
+  if (sh.ndev > 1) {
     sh.comms.resize(sh.ndev);
     std::vector<int> devs(sh.ndev);
     for (int i = 0; i < sh.ndev; ++i) devs[i] = i;
     if (ncclCommInitAll(sh.comms.data(), sh.ndev, devs.data()) != ncclSuccess) {
-      fprintf(stderr, "ncclCommInitAll failed; continuing without the result gather\n");
+      fprintf(stderr, "ncclCommInitAll failed; continuing with replicated builds and no result gather\n");
       sh.comms.clear();
     }
   }

@@ -66,3 +66,19 @@ def test_sharded_walks_equal_single_rank(tmp_path, oracle):
     _, lens = oracle.walk(x, a, w, table, starts, 21, app=oracle.PPR, tp=0.15, seed=5)
     assert np.array_equal(got, lens.astype(np.int64))       # the split is invisible in the result
     assert stats[0] == 2.0 and stats[1] == float(lens.sum())  # max over ranks, sum over ranks
+
+
+def test_edge_balanced_ranges_partition_the_vertices(oracle):
+    sys.path.insert(0, ROOT)
+    from skywalker_b200.api import edge_balanced_ranges
+    x, a = oracle.gen_rmat(12, 16 << 12, seed=2)
+    E = int(x[-1])
+    for parts in (1, 2, 3, 8):
+        r = edge_balanced_ranges(x, parts)
+        assert r[0][0] == 0 and r[-1][1] == len(x) - 1
+        assert all(r[i][1] == r[i + 1][0] for i in range(parts - 1))
+        sizes = [int(x[e]) - int(x[b]) for b, e in r]
+        assert sum(sizes) == E
+        assert max(sizes) <= E // parts + int(np.diff(x.astype(np.int64)).max()) + parts
+    # degenerate: empty graph, more parts than vertices
+    assert edge_balanced_ranges(np.zeros(3, np.uint32), 4) == [(0, 0), (0, 0), (0, 0), (0, 2)]
