@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libskywalker_b200.so")
+# SKYWALKER_B200_LIB points at an alternative build of the same library (e.g. a tuning variant)
+LIB_PATH = os.environ.get("SKYWALKER_B200_LIB") or os.path.join(_PKG, "libskywalker_b200.so")
 
 SKW_OK = 0
 APP_DEEPWALK, APP_PPR, APP_NODE2VEC = 0, 1, 2

@@ -79,8 +79,10 @@ static void free_graph(skw_ctx* ctx) {
   cudaFree(ctx->stamp);
   cudaFree(ctx->records);
   cudaFree(ctx->vinfo);
+  cudaFree(ctx->vbits);
   ctx->records = nullptr;
   ctx->vinfo = nullptr;
+  ctx->vbits = nullptr;
   ctx->stamp = nullptr;
   ctx->stamp_round = 0;
   ctx->slots = nullptr;
@@ -149,8 +151,10 @@ void drop_records(skw_ctx* ctx) {
   if (ctx->records || ctx->vinfo) cudaStreamSynchronize(ctx->stream);
   cudaFree(ctx->records);
   cudaFree(ctx->vinfo);
+  cudaFree(ctx->vbits);
   ctx->records = nullptr;
   ctx->vinfo = nullptr;
+  ctx->vbits = nullptr;
 }
 
 int alloc_table(skw_ctx* ctx) {

@@ -48,6 +48,7 @@ struct skw_ctx {
   // optional fused walk records (32 B per edge slot) and per-vertex {offset, usable degree}
   void* records = nullptr;
   void* vinfo = nullptr;
+  void* vbits = nullptr;  // one bit per vertex: usable degree != 0
 
   // device error word (4 x u32) and its pinned host mirror
   uint32_t* d_err = nullptr;

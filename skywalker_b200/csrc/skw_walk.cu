@@ -102,7 +102,7 @@ __device__ __forceinline__ void add_edges(unsigned long long* sum, u64 edges) {
 // All steps of all walkers in one launch.  Each lane owns walkers tid, tid + T, tid + 2T ...;
 // the loop body is one step, so lanes of a warp stay converged although their walkers differ.
 template <int APP>
-__global__ void __launch_bounds__(256, 6) walk_offline_kernel(const WalkArgs a) {
+__global__ void __launch_bounds__(256) walk_offline_kernel(const WalkArgs a) {
   const u64 T = (u64)gridDim.x * blockDim.x;
   u64 w = (u64)blockIdx.x * blockDim.x + threadIdx.x;
   u64 edges = 0;
@@ -194,15 +194,25 @@ __device__ __forceinline__ void load_record(const WalkRecord* p, u32 (&w)[8]) {
                : "l"(p));
 }
 
-// vinfo[v] = {first-edge offset, usable degree}
+// vinfo[v] = {first-edge offset, usable degree}; vbits = one bit per vertex, set when the usable
+// degree is not zero.  The bitmap is V/8 bytes and stays in L2, so a walker that starts on a dead
+// end (most uniformly random starts of a directed R-MAT graph) never touches DRAM for it.
 __global__ void __launch_bounds__(256) vertex_info_kernel(const u32* __restrict__ xadj,
                                                           const Slot* __restrict__ slots, u32 V,
-                                                          uint2* __restrict__ vinfo) {
-  for (u64 v = (u64)blockIdx.x * blockDim.x + threadIdx.x; v < V; v += (u64)gridDim.x * blockDim.x) {
-    const u32 off = xadj[v], deg = xadj[v + 1] - off;
-    u32 eff = deg;
-    if (deg && load_slot(slots + off).prob < 0.0f) eff = 0;
-    vinfo[v] = make_uint2(off, eff);
+                                                          uint2* __restrict__ vinfo, u32* __restrict__ vbits) {
+  const u64 T = (u64)gridDim.x * blockDim.x;
+  const u64 rounds = ((u64)V + T - 1) / T;
+  for (u64 it = 0; it < rounds; ++it) {  // whole warps stay in the loop: the ballot needs them
+    const u64 v = it * T + (u64)blockIdx.x * blockDim.x + threadIdx.x;
+    u32 eff = 0;
+    if (v < V) {
+      const u32 off = xadj[v], deg = xadj[v + 1] - off;
+      eff = deg;
+      if (deg && load_slot(slots + off).prob < 0.0f) eff = 0;
+      vinfo[v] = make_uint2(off, eff);
+    }
+    const u32 word = __ballot_sync(0xFFFFFFFFu, eff != 0);
+    if ((threadIdx.x & 31) == 0 && v < V) vbits[v >> 5] = word;
   }
 }
 
@@ -244,6 +254,7 @@ __global__ void __launch_bounds__(256) walk_records_kernel(const u32* __restrict
 struct RecordWalkArgs {
   const WalkRecord* rec;
   const uint2* vinfo;
+  const u32* vbits;
   const u32* starts;
   u32* paths;
   u32* lengths;
@@ -259,9 +270,8 @@ struct RecordWalkArgs {
 };
 
 // Same lane-owns-a-stride loop as walk_offline_kernel; a step is one record load.
-// 6 resident CTAs per SM: measured best on B200 (more threads in flight lower the DRAM access rate)
 template <int APP>
-__global__ void __launch_bounds__(256, 6) walk_records_walk_kernel(const RecordWalkArgs a) {
+__global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalkArgs a) {
   const u64 T = (u64)gridDim.x * blockDim.x;
   u64 w = (u64)blockIdx.x * blockDim.x + threadIdx.x;
   u64 edges = 0;
@@ -277,10 +287,13 @@ __global__ void __launch_bounds__(256, 6) walk_records_walk_kernel(const RecordW
       dev_fail(a.err, DEV_ERR_INDEX, cur, 0, (u32)w);
       off = 0;
       deg = 0;
-    } else {
+    } else if ((__ldg(a.vbits + (cur >> 5)) >> (cur & 31)) & 1u) {
       const uint2 vi = ldg_once(a.vinfo + cur);
       off = vi.x;
       deg = vi.y;
+    } else {
+      off = 0;
+      deg = 0;
     }
   };
   if (have) begin();
@@ -335,6 +348,14 @@ __global__ void __launch_bounds__(256) generate_starts_kernel(u32* __restrict__ 
   }
 }
 
+// CTAs launched per SM by the all-steps walk kernels (about 5 are resident at a time).  A lane
+// walks its walkers one after another, so a CTA lives as long as its unluckiest lane; many short
+// CTAs keep the SMs evenly loaded to the end.  Measured on B200 at 8 M walkers: fixed-length walks
+// are fastest with one walker per thread (6.8 ms against 10.3 ms at 8 CTAs per SM on scale-26
+// DeepWalk); PPR, where most walkers stop after a few steps, is fastest at about 64 CTAs per SM
+// (1.19 ms against 1.46 ms at 8 and 1.35 ms at one walker per thread).
+static int walk_ctas_per_sm(uint32_t app) { return app == SKW_APP_PPR ? 64 : 1 << 20; }
+
 static int grid_for(const skw_ctx* ctx, u64 n, int per_sm) {
   const u64 want = (n + 255) / 256;
   const u64 cap = (u64)ctx->sm_count * per_sm;
@@ -365,11 +386,13 @@ int skw_walk_records_build(skw_ctx* ctx, float* ms) {
   DeviceGuard g(ctx->device);
   if (!ctx->records) SKW_CUDA(ctx, cudaMalloc(&ctx->records, sizeof(WalkRecord) * (ctx->E ? ctx->E : 1)));
   if (!ctx->vinfo) SKW_CUDA(ctx, cudaMalloc(&ctx->vinfo, sizeof(uint2) * ((size_t)ctx->V + 1)));
+  if (!ctx->vbits) SKW_CUDA(ctx, cudaMalloc(&ctx->vbits, sizeof(u32) * ((size_t)ctx->V / 32 + 1)));
   cudaStream_t st = ctx->stream;
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
   const int grid = ctx->sm_count * 16;
   if (ctx->V) {
-    vertex_info_kernel<<<grid, 256, 0, st>>>(ctx->xadj, ctx->slots, ctx->V, static_cast<uint2*>(ctx->vinfo));
+    vertex_info_kernel<<<grid, 256, 0, st>>>(ctx->xadj, ctx->slots, ctx->V, static_cast<uint2*>(ctx->vinfo),
+                                              static_cast<u32*>(ctx->vbits));
     SKW_LAUNCHED(ctx);
   }
   if (ctx->E) {
@@ -404,8 +427,10 @@ int skw_walk_records_free(skw_ctx* ctx) {
   SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   cudaFree(ctx->records);
   cudaFree(ctx->vinfo);
+  cudaFree(ctx->vbits);
   ctx->records = nullptr;
   ctx->vinfo = nullptr;
+  ctx->vbits = nullptr;
   return SKW_OK;
 }
 
@@ -468,6 +493,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
       RecordWalkArgs ra;
       ra.rec = static_cast<const WalkRecord*>(ctx->records);
       ra.vinfo = static_cast<const uint2*>(ctx->vinfo);
+      ra.vbits = static_cast<const u32*>(ctx->vbits);
       ra.starts = d_starts;
       ra.paths = d_paths;
       ra.lengths = d_lengths;
@@ -480,12 +506,12 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
       ra.V = a.V;
       ra.hop_num = a.hop_num;
       ra.tp = a.tp;
-      const int grid = grid_for(ctx, n, 6);
+      const int grid = grid_for(ctx, n, walk_ctas_per_sm(prm->app));
       if (prm->app == SKW_APP_PPR) walk_records_walk_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(ra);
       else walk_records_walk_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(ra);
       SKW_LAUNCHED(ctx);
     } else if (!online) {
-      const int grid = grid_for(ctx, n, 6);
+      const int grid = grid_for(ctx, n, walk_ctas_per_sm(prm->app));
       switch (prm->app) {
         case SKW_APP_DEEPWALK: walk_offline_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a); break;
         case SKW_APP_PPR: walk_offline_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a); break;
