@@ -476,6 +476,15 @@ def main():
         torch.cuda.synchronize()
         gather_ms = (time.perf_counter() - t0) * 1e3
 
+    # the ceiling the step kernels run against: dependent random 32-byte accesses per second, probed
+    # live on this GPU (footprint 16 GiB, far beyond L2)
+    probe_gacc = None
+    if rank == 0:
+        try:
+            probe_gacc = ctx.probe_random_gather(16 << 30, 128)
+        except Exception:
+            probe_gacc = None
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_leg(ctx, wl, args.cpu_threads)
@@ -521,7 +530,14 @@ def main():
             "online_cached_tables": cached_info,
             "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                         "algorithmic_bytes": bytes_note},
+                         "algorithmic_bytes": bytes_note,
+                         "random_access_probe_gaccess_per_s": probe_gacc,
+                         "sampled_edges_per_probe_access": (edges_per_step_rank / (per_step_ms * 1e-3) / 1e9 / probe_gacc
+                                                            if probe_gacc else None),
+                         "note": "a step is a chain of dependent random accesses; the probe is the rate of such "
+                                 "accesses this GPU sustains whatever their size (8-128 B), so sampled edges per "
+                                 "probe access, not the byte fraction, says how close the step kernel is to the "
+                                 "hardware"},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "result_gather_ms": gather_ms,
         }

@@ -144,6 +144,10 @@ int skw_alias_build_offline(skw_ctx* ctx, uint32_t v_begin, uint32_t v_end, floa
 int skw_alias_export(skw_ctx* ctx, float* h_prob, uint32_t* h_alias, uint8_t* h_valid);
 int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
                      const uint8_t* h_valid);
+/* Checkpoint of the built table in a file (the reference only has the in-process --built flag,
+ * src/main.cu:347).  Loading checks that the file was written for a graph of the same V and E. */
+int skw_alias_save(skw_ctx* ctx, const char* path);
+int skw_alias_load(skw_ctx* ctx, const char* path);
 /* Device address of the packed table: E slots of {float prob; uint32 alias} and V valid bytes. */
 int skw_alias_device_ptrs(const skw_ctx* ctx, const void** d_slots, const uint8_t** d_valid);
 
@@ -258,6 +262,14 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
 int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_seeds, uint64_t n,
                     uint32_t* h_data, uint32_t* h_sample_lengths, float* ms,
                     uint64_t* sampled_edges);
+
+/* Measurement aid, no counterpart in the reference: times a dependent chain of random 32-byte loads
+ * (the access pattern of a walk step, same load instruction as the record walk) over a scratch
+ * buffer of footprint_bytes and reports giga-accesses per second.  This is the ceiling the step
+ * kernels run against; it is far below the streaming bandwidth and does not depend on the bytes
+ * per access.  Allocates and frees the scratch buffer. */
+int skw_probe_random_gather(skw_ctx* ctx, uint64_t footprint_bytes, uint32_t iters,
+                            double* gaccesses_per_s);
 
 /* ---------------------------------------------------------------- host helpers ----------- */
 

@@ -53,6 +53,8 @@ SIGNATURES = {
     "skw_alias_build_offline": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]),
     "skw_alias_export": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "skw_alias_import": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "skw_alias_save": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "skw_alias_load": (C.c_int, [C.c_void_p, C.c_char_p]),
     "skw_alias_device_ptrs": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "skw_alias_build_list_static": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_char_p, C.c_size_t]),
@@ -68,6 +70,7 @@ SIGNATURES = {
                                          C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "skw_sample_khop": (C.c_int, [C.c_void_p, C.POINTER(KhopParams), C.c_void_p, C.c_uint64, C.c_void_p,
                                   C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
+    "skw_probe_random_gather": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.POINTER(C.c_double)]),
     "skw_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "skw_host_free": (None, [C.c_void_p]),
     "skw_version": (C.c_char_p, []),

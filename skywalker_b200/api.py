@@ -166,6 +166,12 @@ class Context:
         pad = lambda a: a if a.size else np.zeros(1, a.dtype)
         self._ck(self._lib.skw_alias_import(self._h, _ptr(pad(prob)), _ptr(pad(alias)), _ptr(pad(valid))))
 
+    def alias_save(self, path):
+        self._ck(self._lib.skw_alias_save(self._h, path.encode()))
+
+    def alias_load(self, path):
+        self._ck(self._lib.skw_alias_load(self._h, path.encode()))
+
     def alias_device_arrays(self):
         """(slots as int64[E] -- one packed {f32 prob, u32 alias} per element --, valid as uint8[V]),
         borrowed from the context: for collectives over table slices (multi-GPU sliced build)."""
@@ -188,6 +194,12 @@ class Context:
 
     def walk_records_free(self):
         self._ck(self._lib.skw_walk_records_free(self._h))
+
+    def probe_random_gather(self, footprint_bytes=16 << 30, iters=128):
+        """Giga random 32-byte accesses per second this GPU sustains (dependent chains, like a walk)."""
+        v = C.c_double()
+        self._ck(self._lib.skw_probe_random_gather(self._h, footprint_bytes, iters, C.byref(v)))
+        return v.value
 
     # -- walks
     def walk(self, starts, hop_num, app=APP_DEEPWALK, mode=MODE_OFFLINE, tp=0.0, p=2.0, q=0.5, seed=42,

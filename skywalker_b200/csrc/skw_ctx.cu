@@ -491,6 +491,80 @@ int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
   return SKW_OK;
 }
 
+// Table checkpoint: 32-byte header {magic "SKWTABLE", V, E, slot bytes} + E packed slots + V valid
+// bytes.  A built table is a pure function of the graph, so a checkpoint saves only the build time.
+static const char kTableMagic[8] = {'S', 'K', 'W', 'T', 'A', 'B', 'L', 'E'};
+
+int skw_alias_save(skw_ctx* ctx, const char* path) {
+  if (!ctx || !path) return SKW_ERR_ARG;
+  if (!ctx->table_ready) return fail(ctx, SKW_ERR_STATE, "skw_alias_save: no table built");
+  DeviceGuard g(ctx->device);
+  FILE* f = fopen(path, "wb");
+  if (!f) return fail(ctx, SKW_ERR_IO, "skw_alias_save: cannot create %s", path);
+  uint64_t hdr[4];
+  memcpy(&hdr[0], kTableMagic, 8);
+  hdr[1] = ctx->V;
+  hdr[2] = ctx->E;
+  hdr[3] = sizeof(Slot);
+  bool ok = fwrite(hdr, 8, 4, f) == 4;
+  const size_t chunk = 64u << 20;  // staged through a bounded host buffer
+  std::vector<unsigned char> buf(chunk);
+  auto dump = [&](const void* dptr, size_t bytes) {
+    for (size_t o = 0; ok && o < bytes; o += chunk) {
+      const size_t nb = bytes - o < chunk ? bytes - o : chunk;
+      if (cudaMemcpyAsync(buf.data(), static_cast<const unsigned char*>(dptr) + o, nb, cudaMemcpyDeviceToHost,
+                          ctx->stream) != cudaSuccess ||
+          cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+        ok = false;
+      else
+        ok = fwrite(buf.data(), 1, nb, f) == nb;
+    }
+  };
+  dump(ctx->slots, sizeof(Slot) * ctx->E);
+  dump(ctx->valid, ctx->V);
+  ok = (fclose(f) == 0) && ok;
+  if (!ok) return fail(ctx, SKW_ERR_IO, "skw_alias_save: write to %s failed", path);
+  return SKW_OK;
+}
+
+int skw_alias_load(skw_ctx* ctx, const char* path) {
+  if (!ctx || !path) return SKW_ERR_ARG;
+  if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_alias_load: no graph resident");
+  DeviceGuard g(ctx->device);
+  FILE* f = fopen(path, "rb");
+  if (!f) return fail(ctx, SKW_ERR_IO, "skw_alias_load: cannot open %s", path);
+  struct Closer {
+    FILE* f;
+    ~Closer() { fclose(f); }
+  } closer{f};
+  uint64_t hdr[4];
+  if (fread(hdr, 8, 4, f) != 4 || memcmp(&hdr[0], kTableMagic, 8) != 0)
+    return fail(ctx, SKW_ERR_IO, "skw_alias_load: %s is not a table checkpoint", path);
+  if (hdr[1] != ctx->V || hdr[2] != ctx->E || hdr[3] != sizeof(Slot))
+    return fail(ctx, SKW_ERR_IO, "skw_alias_load: %s holds a table for V=%llu E=%llu, the resident graph has V=%u E=%llu",
+                path, (unsigned long long)hdr[1], (unsigned long long)hdr[2], ctx->V, (unsigned long long)ctx->E);
+  drop_records(ctx);
+  int rc = alloc_table(ctx);
+  if (rc != SKW_OK) return rc;
+  ctx->table_ready = false;
+  const size_t chunk = 64u << 20;
+  std::vector<unsigned char> buf(chunk);
+  auto fill = [&](void* dptr, size_t bytes) -> int {
+    for (size_t o = 0; o < bytes; o += chunk) {
+      const size_t nb = bytes - o < chunk ? bytes - o : chunk;
+      if (fread(buf.data(), 1, nb, f) != nb) return fail(ctx, SKW_ERR_IO, "skw_alias_load: %s is truncated", path);
+      SKW_CUDA(ctx, cudaMemcpyAsync(static_cast<unsigned char*>(dptr) + o, buf.data(), nb, cudaMemcpyHostToDevice,
+                                    ctx->stream));
+      SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    return SKW_OK;
+  };
+  if ((rc = fill(ctx->slots, sizeof(Slot) * ctx->E)) != SKW_OK) return rc;
+  if ((rc = fill(ctx->valid, ctx->V)) != SKW_OK) return rc;
+  ctx->table_ready = true;
+  return SKW_OK;
+}
+
 int skw_alias_device_ptrs(const skw_ctx* ctx, const void** d_slots, const uint8_t** d_valid) {
   if (!ctx) return SKW_ERR_ARG;
   if (d_slots) *d_slots = ctx->slots;

@@ -356,6 +356,27 @@ __global__ void __launch_bounds__(256) generate_starts_kernel(u32* __restrict__ 
 // (1.19 ms against 1.46 ms at 8 and 1.35 ms at one walker per thread).
 static int walk_ctas_per_sm(uint32_t app) { return app == SKW_APP_PPR ? 64 : 1 << 20; }
 
+// Measurement aid: a dependent chain of random 32-byte record loads, the memory behaviour of a walk
+// stripped of everything else.  Every thread follows `iters` pseudo-random hops through `nrec`
+// records with the same load instruction the record walk uses.
+__global__ void __launch_bounds__(256) probe_gather_kernel(const WalkRecord* __restrict__ rec, u64 nrec,
+                                                           u32 iters, unsigned long long* __restrict__ sink) {
+  const u64 tid = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+  u64 cur = (tid * 0x9E3779B97F4A7C15ull) % nrec;
+  u32 acc = 0;
+  for (u32 it = 0; it < iters; ++it) {
+    u32 w[8];
+    load_record(rec + cur, w);
+    acc += w[0];
+    u64 x = cur * 31 + w[7] + it + tid;
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdull;
+    x ^= x >> 33;
+    cur = x % nrec;
+  }
+  if (acc == 0x12345677u) atomicAdd(sink, 1ull);  // keeps the loads alive
+}
+
 static int grid_for(const skw_ctx* ctx, u64 n, int per_sm) {
   const u64 want = (n + 255) / 256;
   const u64 cap = (u64)ctx->sm_count * per_sm;
@@ -418,6 +439,34 @@ int skw_ctx_take_sampled_edges(skw_ctx* ctx, uint64_t* out) {
     return rc;
   }
   if (out) *out = v;
+  return SKW_OK;
+}
+
+int skw_probe_random_gather(skw_ctx* ctx, uint64_t footprint_bytes, uint32_t iters, double* gaccesses_per_s) {
+  if (!ctx || !gaccesses_per_s) return SKW_ERR_ARG;
+  if (footprint_bytes < (1ull << 20) || iters == 0)
+    return fail(ctx, SKW_ERR_ARG, "skw_probe_random_gather: need a footprint of at least 1 MiB and iters > 0");
+  DeviceGuard g(ctx->device);
+  const u64 nrec = footprint_bytes / sizeof(WalkRecord);
+  WalkRecord* buf = nullptr;
+  SKW_CUDA(ctx, cudaMalloc(&buf, nrec * sizeof(WalkRecord)));
+  cudaStream_t st = ctx->stream;
+  cudaError_t e = cudaMemsetAsync(buf, 1, nrec * sizeof(WalkRecord), st);
+  const int grid = ctx->sm_count * 8;
+  unsigned long long* sink = reinterpret_cast<unsigned long long*>(ctx->d_sum) + 1;
+  float ms = 0;
+  if (e == cudaSuccess) {
+    probe_gather_kernel<<<grid, 256, 0, st>>>(buf, nrec, 8, sink);  // warm-up
+    cudaEventRecord(ctx->ev0, st);
+    probe_gather_kernel<<<grid, 256, 0, st>>>(buf, nrec, iters, sink);
+    cudaEventRecord(ctx->ev1, st);
+    ctx->launches += 2;
+    e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1);
+  }
+  cudaFree(buf);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "skw_probe_random_gather", __FILE__, __LINE__);
+  *gaccesses_per_s = (double)grid * 256.0 * iters / (ms * 1e-3) / 1e9;
   return SKW_OK;
 }
 

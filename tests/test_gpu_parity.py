@@ -428,3 +428,34 @@ def test_offline_table_survives_weight_release(ctx, oracle, rmat12):
         ctx.walk(starts, 21, mode=MODE_ONLINE)            # online needs the weights
     with pytest.raises(SkwError):
         ctx.alias_build_offline()
+
+
+def test_random_gather_probe(ctx):
+    g = ctx.probe_random_gather(1 << 30, 32)
+    assert 5.0 < g < 500.0          # giga-accesses/s; ~40 on B200 beyond L2
+
+
+def test_table_checkpoint(ctx, oracle, rmat12, plaw, tmp_path):
+    from skywalker_b200.api import SkwError
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    want = ctx.alias_export()
+    path = str(tmp_path / "table.skw")
+    ctx.alias_save(path)
+    _upload(ctx, g)                       # fresh graph, no table
+    with pytest.raises(SkwError):
+        ctx.walk(np.zeros(2, np.uint32), 3)
+    ctx.alias_load(path)
+    got = ctx.alias_export()
+    assert all(np.array_equal(a.view(np.uint8), b.view(np.uint8)) for a, b in zip(got, want))
+    starts = oracle.gen_starts(300, g.V, 4)
+    p1, l1, _, _ = ctx.walk(starts, 11, seed=6)
+    op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, oracle.alias_build(g.xadj, g.adjwgt), starts, 11, seed=6)
+    _cmp_walks(p1, l1, op, ol)
+    _upload(ctx, plaw)                    # a different graph must refuse the file
+    with pytest.raises(SkwError):
+        ctx.alias_load(path)
+    (tmp_path / "bad.skw").write_bytes(b"not a table")
+    with pytest.raises(SkwError):
+        ctx.alias_load(str(tmp_path / "bad.skw"))
