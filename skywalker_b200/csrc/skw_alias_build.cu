@@ -115,7 +115,8 @@ __device__ __forceinline__ int degree_class(u32 deg) {
   return K_H;
 }
 
-// cls[0..K) counts, cls[K..2K) fill cursors, cls[2K..3K) bases of the classes in the work list.
+// cls[0..K) counts, cls[K..2K) fill cursors, cls[2K..3K) bases of the classes in the work list,
+// cls[3K..4K) cursors from which the builder kernels take their next vertex.
 __global__ void __launch_bounds__(256) classify_count_kernel(const u32* __restrict__ xadj,
                                                              u32 v_begin, u32 v_end,
                                                              u32* __restrict__ cls,
@@ -545,12 +546,11 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
   const int sh = weight_shift(wmax, B);
   u64 W = 0;
   {
-    u64 acc = 0, dummy;
+    u64 acc = 0;
     for (u32 p = t; p < n; p += NT) acc += quantise_bits(sane_weight(__ldg(w + p)), sh);
     // total only: the exclusive prefix is not needed here
     u64 x = acc;
     coop_scan_u64<NT>(x, W, s_tmp);
-    (void)dummy;
   }
   const u64 nC = (u64)n << B;
   const double K = mass_factor(n, B, W);
@@ -674,7 +674,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
 // (12 bytes per edge per warp).
 template <int CAP, int WPB>
 __global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* __restrict__ worklist,
-                                                                    const u32* __restrict__ cls, int k,
+                                                                    u32* __restrict__ cls, int k,
                                                                     const u32* __restrict__ xadj,
                                                                     const float* __restrict__ wgt,
                                                                     Slot* __restrict__ slots,
@@ -685,8 +685,14 @@ __global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* _
   const u32 lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   u64* A = reinterpret_cast<u64*>(smem) + (size_t)wib * CAP;
   u32* P = reinterpret_cast<u32*>(reinterpret_cast<u64*>(smem) + (size_t)WPB * CAP) + (size_t)wib * CAP;
-  const u32 warp = blockIdx.x * WPB + wib, nwarps = gridDim.x * WPB;
-  for (u32 it = warp; it < count; it += nwarps) {
+  u32* cursor = cls + 3 * K_CLASSES + k;
+  // vertices are handed out by an atomic cursor: their cost varies with the degree, so a fixed
+  // stride would leave the slowest warp running alone at the end
+  for (;;) {
+    u32 it = 0;
+    if (lane == 0) it = atomicAdd(cursor, 1u);
+    it = __shfl_sync(0xFFFFFFFFu, it, 0);
+    if (it >= count) break;
     const u32 v = worklist[base + it];
     const u32 off = xadj[v], n = xadj[v + 1] - off;
     if (n > CAP) {
@@ -703,7 +709,7 @@ __global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* _
 // windows of WIN outputs staged in dynamic shared memory.
 template <int NT, int WIN>
 __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restrict__ worklist,
-                                                             const u32* __restrict__ cls, int k,
+                                                             u32* __restrict__ cls, int k,
                                                              const u32* __restrict__ xadj,
                                                              const float* __restrict__ wgt,
                                                              Slot* __restrict__ slots,
@@ -716,7 +722,13 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
   u64* A = reinterpret_cast<u64*>(store);
   u32* P = reinterpret_cast<u32*>(A + cap);
   const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
-  for (u32 it = blockIdx.x; it < count; it += gridDim.x) {
+  __shared__ u32 s_it;
+  for (;;) {  // next vertex from the class's atomic cursor (degrees, hence costs, vary widely)
+    if (threadIdx.x == 0) s_it = atomicAdd(cls + 3 * K_CLASSES + k, 1u);
+    __syncthreads();
+    const u32 it = s_it;
+    __syncthreads();
+    if (it >= count) break;
     const u32 v = worklist[base + it];
     const u32 off = xadj[v], n = xadj[v + 1] - off;
     if (n > cap) {
@@ -904,7 +916,7 @@ __device__ void build_vertex_cta(u32 v, u32 off, u32 n, const float* __restrict_
 
 // Launch the class builders over work lists laid out as cls describes (counts at [k],
 // bases at [2K + k]).
-static int launch_builders(skw_ctx* ctx, const u32* worklist, const u32* cls) {
+static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   cudaStream_t st = ctx->stream;
   constexpr int kCtaSmem = kLargeMax * 12;
   constexpr int kCta2Smem = kHugeSmemMax * 12;
@@ -978,6 +990,7 @@ __global__ void frontier_reset_kernel(u32* __restrict__ cls, u32 cap) {
     cls[threadIdx.x] = 0;
     cls[K_CLASSES + threadIdx.x] = 0;
     cls[2 * K_CLASSES + threadIdx.x] = threadIdx.x * cap;
+    cls[3 * K_CLASSES + threadIdx.x] = 0;
   }
 }
 
@@ -1076,7 +1089,7 @@ extern "C" int skw_alias_build_offline(skw_ctx* ctx, uint32_t v_begin, uint32_t 
   rc = err_reset(ctx);
   if (rc != SKW_OK) return rc;
   cudaStream_t st = ctx->stream;
-  SKW_CUDA(ctx, cudaMemsetAsync(ctx->cls_counts, 0, 3 * K_CLASSES * sizeof(uint32_t), st));
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->cls_counts, 0, 4 * K_CLASSES * sizeof(uint32_t), st));
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
   if (v_end > v_begin) {
     const int cgrid = ctx->sm_count * 8;

@@ -11,14 +11,8 @@
 
 namespace skw {
 
-// Degree classes of the offline builder: a group of 4/8/16/32 lanes per vertex, then one CTA per
-// vertex with its arrays in shared memory, then one CTA per vertex with arrays in global scratch.
-enum { CLS_G4 = 0, CLS_G8, CLS_G16, CLS_G32, CLS_CTA_SMEM, CLS_CTA_GMEM, CLS_COUNT };
-
 // Largest degree the shared-memory CTA builder takes (12 bytes of list state per edge).
 constexpr uint32_t kCtaSmemMaxDegree = 4096;
-
-struct WalkRecord;  // skw_walk.cu
 
 }  // namespace skw
 
@@ -60,7 +54,7 @@ struct skw_ctx {
   // builder scratch, grown on demand
   uint32_t* worklist = nullptr;      // V entries, vertices grouped by degree class
   size_t worklist_cap = 0;
-  uint32_t* cls_counts = nullptr;    // CLS_COUNT counters + CLS_COUNT cursors + CLS_COUNT bases
+  uint32_t* cls_counts = nullptr;    // per degree class: count, fill cursor, base in the work list
   void* cta_scratch = nullptr;       // slabs of the global-memory CTA builder
   size_t cta_scratch_bytes = 0;
 

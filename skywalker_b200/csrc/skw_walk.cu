@@ -16,11 +16,8 @@
 
 namespace skw {
 
-int build_from_worklists(skw_ctx* ctx, const u32* worklist, const u32* cls);
 int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 cells, u32 offs,
                      const u32* alive_lengths, bool new_round);
-int alloc_table(skw_ctx* ctx);
-
 constexpr u32 kAlive = 0xFFFFFFFFu;
 constexpr u32 kNoVertex = 0xFFFFFFFFu;
 constexpr u32 kN2vMaxTrials = 64;
