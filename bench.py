@@ -5,7 +5,7 @@
                     [--impl ours|reference]
 
 One "step" is one pass of the hot path over one batch: all walkers of the workload (walks) or one
-batch of seed vertices (k-hop).  Default workload: BASELINE config 5 -- biased offline PPR
+batch of seed vertices (k-hop).  Default workload: benchmark configuration 5 -- biased offline PPR
 (tp 0.15, max length 100) on a seeded R-MAT scale-26 graph (~1.8 G directed edges), 8 M walkers
 sharded evenly over the N GPUs, graph and tables replicated per GPU.  Rank 0 prints ONE JSON line.
 
@@ -29,21 +29,21 @@ if ROOT not in sys.path:
 WORKLOADS = {
     "c1": dict(graph="rmat", scale=16, edge_factor=16, kind="walk", mode="offline", units=4096, length=80,
                app="deepwalk", tp=0.0,
-               desc="BASELINE config 1: biased offline DeepWalk, R-MAT scale 16, 4,096 walkers x 80"),
+               desc="benchmark configuration 1: biased offline DeepWalk, R-MAT scale 16, 4,096 walkers x 80"),
     "c2": dict(graph="rmat", scale=22, edge_factor=16, kind="walk", mode="offline", units=40000, length=80,
                app="deepwalk", tp=0.0,
-               desc="BASELINE config 2: biased offline DeepWalk, R-MAT scale 22, 40,000 walkers x 80"),
+               desc="benchmark configuration 2: biased offline DeepWalk, R-MAT scale 22, 40,000 walkers x 80"),
     "c3": dict(graph="plaw", V=3070000, raw_edges=117000000, exponent=2.1, dmin=12.0, cap=33000, kind="walk",
                mode="online", units=40000, length=80, app="node2vec", tp=0.0, p=2.0, q=0.5,
-               desc="BASELINE config 3: online biased node2vec p=2 q=0.5 (rejection), undirected power-law graph "
+               desc="benchmark configuration 3: online biased node2vec p=2 q=0.5 (rejection), undirected power-law graph "
                     "3.07M vertices / 117M undirected edges, degree ~ Zipf 2.1 capped at 33k, 40,000 walkers x 80"),
     "c4": dict(graph="rmat", scale=23, V=4850000, raw_edges=72000000, kind="khop", mode="online", units=65536,
                fanout=[25, 10],
-               desc="BASELINE config 4: online biased 2-hop sampling, fan-out 25 then 10 with replacement, "
+               desc="benchmark configuration 4: online biased 2-hop sampling, fan-out 25 then 10 with replacement, "
                     "R-MAT-like directed graph 4.85M vertices / ~69M edges, batches of 65,536 random seeds"),
     "c5": dict(graph="rmat", scale=26, edge_factor=28, kind="walk", mode="offline", units=8000000, length=100,
                app="ppr", tp=0.15,
-               desc="BASELINE config 5: biased offline PPR tp=0.15 max length 100, R-MAT scale 26 "
+               desc="benchmark configuration 5: biased offline PPR tp=0.15 max length 100, R-MAT scale 26 "
                     "(~1.8G directed edges), 8M walkers sharded over the GPUs"),
     "dw26": dict(graph="rmat", scale=26, edge_factor=28, kind="walk", mode="offline", units=8000000, length=80,
                  app="deepwalk", tp=0.0,
@@ -54,6 +54,11 @@ WORKLOADS = {
 GRAPH_SEED, WEIGHT_SEED, START_SEED, WALK_SEED = 1, 7, 42, 42
 ALG_BYTES_PER_EDGE = 24        # offline step: 8 offsets + 8 slot + 4 neighbour + 4 path store
 ALG_BYTES_PER_BUILD_EDGE = 12  # offline build: 4 weight + 8 slot
+# DRAM bytes per sampled edge, (dram__bytes_read.sum + dram__bytes_write.sum) / sampled edges of one
+# launch, from ncu captures of the reduced PPR workload "c5s" (same kernels, scale 22, 1 M walkers;
+# summary in profiles/walk_kernels_ppr_rmat22_1Mwalkers.md).  Traffic grows in proportion to walkers
+# and steps, so roofline.traffic = this figure x the sampled edges of a full launch.
+DRAM_BYTES_PER_SAMPLED_EDGE = {"walk_records_walk_kernel": 105.2, "walk_offline_kernel": 162.9}
 
 
 def measured_peak():
@@ -503,15 +508,8 @@ def main():
             bytes_note = "24 bytes per sampled edge"
             achieved = edges_per_step_rank * ALG_BYTES_PER_EDGE / (per_step_ms * 1e-3) / 1e9
             kernel_name = "walk_records_walk_kernel" if use_records else "walk_offline_kernel"
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tpath):
-            try:
-                tj = json.load(open(tpath)).get(kernel_name)
-                if tj:
-                    traffic = tj["dram_bytes_per_sampled_edge"] * edges_per_step_rank
-            except Exception:
-                traffic = None
+        per_edge = DRAM_BYTES_PER_SAMPLED_EDGE.get(kernel_name)
+        traffic = per_edge * edges_per_step_rank if per_edge else None
         build_gbs = E * ALG_BYTES_PER_BUILD_EDGE / (build_best * 1e-3) / 1e9
         out = {
             "metric": "sampled edges/s", "value": value, "unit": "sampled edges/s", "n_gpus": world,

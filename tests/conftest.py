@@ -47,7 +47,7 @@ def oracle():
 
 @pytest.fixture(scope="session")
 def rmat16(oracle):
-    """BASELINE config 1: R-MAT scale 16, edge factor 16, weights in [1,10)."""
+    """benchmark configuration 1: R-MAT scale 16, edge factor 16, weights in [1,10)."""
     x, a = oracle.gen_rmat(16, 16 << 16, 0.57, 0.19, 0.19, False, seed=1)
     return SynthGraph(x, a, oracle.gen_weights(len(a), 7))
 

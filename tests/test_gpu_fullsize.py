@@ -1,4 +1,4 @@
-"""Properties that hold at any size, checked at BASELINE config 2's size (R-MAT scale 22, ~65 M edges)
+"""Properties that hold at any size, checked at benchmark configuration 2's size (R-MAT scale 22, ~65 M edges)
 where a bit-for-bit CPU walk of every configuration would be slow: reconstruction of the edge
 probabilities, every step is an edge, determinism, invisibility of sharding, agreement of the two
 table layouts, PPR length statistics, k-hop children are neighbours of their parent."""

@@ -136,7 +136,7 @@ def test_alias_import_export(ctx, oracle, rmat12):
 
 
 def test_config1_deepwalk_bit_exact(ctx, oracle, rmat16):
-    """BASELINE config 1: 4,096 walkers, length 80, seed 42, tables from the oracle."""
+    """benchmark configuration 1: 4,096 walkers, length 80, seed 42, tables from the oracle."""
     g = rmat16
     _upload(ctx, g)
     table = oracle.alias_build(g.xadj, g.adjwgt)
