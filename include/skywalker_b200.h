@@ -271,6 +271,12 @@ int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_
 int skw_probe_random_gather(skw_ctx* ctx, uint64_t footprint_bytes, uint32_t iters,
                             double* gaccesses_per_s);
 
+/* Self-test of the kernels' bounded waits, no counterpart in the reference (whose block-level
+ * constructor can spin forever, include/alias_table_new.cuh:637-708): launches a kernel that waits
+ * on a barrier nothing signals; the wait must run out after its poll limit (about a millisecond)
+ * and the call must return SKW_ERR_DEVICE ("bounded wait ran out") with the context still usable. */
+int skw_selftest_bounded_wait(skw_ctx* ctx);
+
 /* ---------------------------------------------------------------- host helpers ----------- */
 
 /* Pinned host memory for the h_* buffers (optional; any host pointer is accepted). */

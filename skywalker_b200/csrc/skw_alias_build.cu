@@ -310,6 +310,40 @@ __global__ void __launch_bounds__(256) build_group_kernel(const u32* __restrict_
   }
 }
 
+// ------------------------------------------------------------------ bulk copy (TMA unit) ---
+// Untiled cp.async.bulk global -> shared with completion on an mbarrier.  Both addresses must be
+// 16-byte aligned and the size a multiple of 16 bytes; the caller rounds the window inwards and
+// fetches ragged ends with plain loads.  No multicast, local memory only.
+__device__ __forceinline__ u32 smem_addr(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(u64* bar, u32 arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
+  // order earlier generic-proxy accesses of the destination before the async-proxy writes
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_addr(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+// Poll (without blocking) for the phase with the given parity, at most `limit` times with a short
+// sleep in between: a few milliseconds in total.  Returns false if the copy did not complete.
+__device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 limit) {
+  for (u32 i = 0; i < limit; ++i) {
+    u32 done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+    __nanosleep(32);
+  }
+  return false;
+}
+
 // ------------------------------------------------------------------ merge-path builders ----
 // NT cooperating threads (one warp, or a CTA) build one vertex.
 //
@@ -528,13 +562,14 @@ __device__ __forceinline__ void merge_window(u32 t, u32 nl, u32 Sl, const u64* s
 
 // WIN == 0: the lists A / P are in shared memory and are merged in place.  WIN > 0: they are in
 // global scratch and win_smem holds WIN * 12 + (NT + 1) * 4 bytes of shared memory for staging.
-template <int NT, int EPT, int WIN>
-__device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __restrict__ wgt,
+// STAGED: w points at a copy of the weight list in shared memory, else at the list in global memory.
+template <int NT, int EPT, int WIN, bool STAGED>
+__device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
                                    Slot* __restrict__ slots, uint8_t* __restrict__ valid, u64* A,
                                    u32* P, u64* s_tmp, unsigned char* win_smem, u32* err) {
-  const float* w = wgt + off;
+  auto weight = [&](u32 p) { return sane_weight(STAGED ? w[p] : __ldg(w + p)); };
   float wmax = 0.0f;
-  for (u32 p = t; p < n; p += NT) wmax = fmaxf(wmax, sane_weight(__ldg(w + p)));
+  for (u32 p = t; p < n; p += NT) wmax = fmaxf(wmax, weight(p));
   wmax = coop_max<NT>(wmax, reinterpret_cast<float*>(s_tmp));
   if (!(wmax > 0.0f)) {
     for (u32 p = t; p < n; p += NT) slots[(u64)off + p] = Slot{-1.0f, p};
@@ -547,7 +582,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
   u64 W = 0;
   {
     u64 acc = 0;
-    for (u32 p = t; p < n; p += NT) acc += quantise_bits(sane_weight(__ldg(w + p)), sh);
+    for (u32 p = t; p < n; p += NT) acc += quantise_bits(weight(p), sh);
     // total only: the exclusive prefix is not needed here
     u64 x = acc;
     coop_scan_u64<NT>(x, W, s_tmp);
@@ -563,7 +598,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* __
     u64 Qex = 0;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
-      m[k] = p0 + k < n ? quantise_bits(sane_weight(__ldg(w + p0 + k)), sh) : 0;
+      m[k] = p0 + k < n ? quantise_bits(weight(p0 + k), sh) : 0;
       Qex += m[k];
     }
     u64 tq;
@@ -699,7 +734,7 @@ __global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* _
       if (lane == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
       continue;
     }
-    build_vertex_merge<32, 4, 0>(lane, v, off, n, wgt, slots, valid, A, P, nullptr, nullptr, err);
+    build_vertex_merge<32, 4, 0, false>(lane, v, off, n, wgt + off, slots, valid, A, P, nullptr, nullptr, err);
     __syncwarp();
   }
 }
@@ -735,7 +770,76 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
       if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)cap);
       continue;
     }
-    build_vertex_merge<NT, 8, WIN>(threadIdx.x, v, off, n, wgt, slots, valid, A, P, s_tmp, smem, err);
+    build_vertex_merge<NT, 8, WIN, false>(threadIdx.x, v, off, n, wgt + off, slots, valid, A, P, s_tmp, smem, err);
+    __syncthreads();
+  }
+}
+
+// The 1025..CAP class with the weight list staged in shared memory by the bulk-copy engine: one
+// cp.async.bulk per vertex brings the 16-byte-aligned middle of the list (the up to 3 floats
+// before the first and after the last boundary come with plain loads), the three passes over the
+// weights then read shared memory.  Lists (12 B/edge) follow the weights in dynamic shared memory.
+template <int NT, int CAP>
+__global__ void __launch_bounds__(NT) build_cta_staged_kernel(const u32* __restrict__ worklist,
+                                                              u32* __restrict__ cls, int k,
+                                                              const u32* __restrict__ xadj,
+                                                              const float* __restrict__ wgt,
+                                                              Slot* __restrict__ slots,
+                                                              uint8_t* __restrict__ valid,
+                                                              u32* __restrict__ err) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ u64 s_tmp[3 * (NT / 32 + 1)];
+  __shared__ __align__(8) u64 s_bar;
+  __shared__ u32 s_it;
+  u64* A = reinterpret_cast<u64*>(smem);
+  u32* P = reinterpret_cast<u32*>(A + CAP);
+  float* sW = reinterpret_cast<float*>(P + CAP);  // CAP + 8 floats, 16-byte aligned
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  if (threadIdx.x == 0) mbar_init(&s_bar, 1);
+  __syncthreads();
+  u32 parity = 0;
+  for (;;) {
+    if (threadIdx.x == 0) s_it = atomicAdd(cls + 3 * K_CLASSES + k, 1u);
+    __syncthreads();
+    const u32 it = s_it;
+    __syncthreads();
+    if (it >= count) break;
+    const u32 v = worklist[base + it];
+    const u32 off = xadj[v], n = xadj[v + 1] - off;
+    if (n > (u32)CAP) {
+      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
+      continue;
+    }
+    const float* w = wgt + off;
+    const u32 head = (u32)((reinterpret_cast<uintptr_t>(w) & 15u) >> 2);            // floats before w in its 16-byte group
+    const float* first = w - head;                                                 // aligned start
+    const u32 body = ((head + n) & ~3u);                                           // floats up to the last boundary
+    const u32 lead = head ? 4 - head : 0;                                          // list elements before the first boundary
+    // elements [lead_start .. ) layout in sW: element i of the list lives at sW[head + i]
+    bool mine_ok = true;
+    const u32 skip = head ? 4u : 0u;  // floats from `first` to the first boundary inside the list
+    const bool bulk = body > skip;
+    if (bulk) {
+      // whole 16-byte groups that lie inside the list: [first + skip, first + body)
+      if (threadIdx.x == 0) bulk_copy_g2s(sW + skip, first + skip, (body - skip) * 4u, &s_bar);
+      // ragged ends by plain loads
+      if (threadIdx.x < lead) sW[head + threadIdx.x] = __ldg(w + threadIdx.x);
+      const u32 tail = head + n - body;  // elements after the last boundary
+      if (threadIdx.x < tail) sW[body + threadIdx.x] = __ldg(first + body + threadIdx.x);
+      mine_ok = mbar_wait(&s_bar, parity, 1u << 16);
+    } else {
+      for (u32 i = threadIdx.x; i < n; i += NT) sW[head + i] = __ldg(w + i);
+    }
+    // the same verdict in every thread (and the barrier that publishes the plain stores)
+    if (!__syncthreads_and(mine_ok ? 1 : 0)) {
+      // the copy did not report completion in time: record it, give it one more bounded chance to
+      // land so that nothing still writes this CTA's shared memory when it leaves, and stop
+      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_WAIT, v, n, 12);
+      if (!mine_ok) mbar_wait(&s_bar, parity, 1u << 16);
+      break;
+    }
+    if (bulk) parity ^= 1u;
+    build_vertex_merge<NT, 8, 0, true>(threadIdx.x, v, off, n, sW + head, slots, valid, A, P, s_tmp, nullptr, err);
     __syncthreads();
   }
 }
@@ -920,6 +1024,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   cudaStream_t st = ctx->stream;
   constexpr int kCtaSmem = kLargeMax * 12;
   constexpr int kCta2Smem = kHugeSmemMax * 12;
+  constexpr int kCtaStagedSmem = kLargeMax * 12 + (kLargeMax + 8) * 4;
   constexpr int kW256Smem = 8 * kWarpSmallMax * 12;
   constexpr int kW1KSmem = 8 * kWarpMax * 12;
   constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
@@ -929,6 +1034,8 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCta2Smem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_staged_kernel<256, kLargeMax>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaStagedSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_warp_merge_kernel<kWarpMax, 8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kW1KSmem));
     attr_set[ctx->device & 63] = true;
@@ -961,8 +1068,13 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
     SKW_LAUNCHED(ctx);
   }
   if (ctx->max_degree > kWarpMax) {
-    build_cta_merge_kernel<256, 0><<<ctx->sm_count * 4, 256, kCtaSmem, st>>>(
-        worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
+    if ((reinterpret_cast<uintptr_t>(ctx->adjwgt) & 15u) == 0) {
+      build_cta_staged_kernel<256, kLargeMax><<<ctx->sm_count * 3, 256, kCtaStagedSmem, st>>>(
+          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+    } else {  // a borrowed weight array that is not 16-byte aligned cannot be bulk-copied
+      build_cta_merge_kernel<256, 0><<<ctx->sm_count * 4, 256, kCtaSmem, st>>>(
+          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
+    }
     SKW_LAUNCHED(ctx);
   }
   if (ctx->max_degree > kLargeMax) {
@@ -1070,6 +1182,26 @@ int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 c
 }  // namespace skw
 
 using namespace skw;
+
+// Self-test of the bounded wait: an mbarrier that nothing ever signals.  The kernel must give up
+// after its poll limit, record DEV_ERR_WAIT and return normally.
+__global__ void selftest_wait_kernel(u32 limit, u32* err) {
+  __shared__ __align__(8) u64 bar;
+  if (threadIdx.x == 0) mbar_init(&bar, 1);
+  __syncthreads();
+  const bool done = mbar_wait(&bar, 0, limit);
+  if (!__syncthreads_and(done ? 1 : 0) && threadIdx.x == 0) dev_fail(err, DEV_ERR_WAIT, limit, 0, 99);
+}
+
+extern "C" int skw_selftest_bounded_wait(skw_ctx* ctx) {
+  if (!ctx) return SKW_ERR_ARG;
+  DeviceGuard g(ctx->device);
+  int rc = err_reset(ctx);
+  if (rc != SKW_OK) return rc;
+  selftest_wait_kernel<<<1, 64, 0, ctx->stream>>>(1u << 10, ctx->d_err);
+  SKW_LAUNCHED(ctx);
+  return err_check(ctx, "skw_selftest_bounded_wait");
+}
 
 extern "C" int skw_alias_build_offline(skw_ctx* ctx, uint32_t v_begin, uint32_t v_end, float* ms) {
   if (!ctx) return SKW_ERR_ARG;

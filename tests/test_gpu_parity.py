@@ -459,3 +459,13 @@ def test_table_checkpoint(ctx, oracle, rmat12, plaw, tmp_path):
     (tmp_path / "bad.skw").write_bytes(b"not a table")
     with pytest.raises(SkwError):
         ctx.alias_load(str(tmp_path / "bad.skw"))
+
+
+def test_bounded_wait_runs_out_cleanly(ctx, rmat12):
+    """A wait on a barrier nobody signals ends by itself with an error record; nothing hangs or faults."""
+    lib = ctx._lib
+    rc = lib.skw_selftest_bounded_wait(ctx._h)
+    assert rc == -4 and b"bounded wait ran out" in lib.skw_last_error(ctx._h)
+    _upload(ctx, rmat12)                     # the context keeps working
+    ctx.alias_build_offline()
+    assert ctx.walk(np.asarray([1, 2], np.uint32), 4)[0][0, 0] == 1
