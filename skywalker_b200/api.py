@@ -239,6 +239,8 @@ class Context:
     # -- k-hop
     @staticmethod
     def khop_layout(fanout):
+        if not 1 <= len(fanout) <= 4:
+            raise SkwError(-1, "k-hop sampling takes 1 to 4 hops, got %d" % len(fanout))
         prm = KhopParams(0, len(fanout), (C.c_uint32 * 4)(*(list(fanout) + [0] * (4 - len(fanout)))), 0, 0, 0, 1)
         cells, lens = C.c_uint32(), C.c_uint32()
         rc = _capi.load().skw_khop_layout(C.byref(prm), C.byref(cells), C.byref(lens))

@@ -102,3 +102,24 @@ def test_cli_two_gpus_same_total_as_one(gr_file):
     m = re.search(r"gathered (\d+) walk lengths on GPU 0 over NCCL, sum (\d+)", two)
     assert m and int(m.group(1)) == 20000
     assert e1 == e2 == int(m.group(2)) and e1 > 0
+
+
+@pytest.mark.gpu
+def test_cli_start_vertex_conventions(oracle, rmat12, gr_file):
+    """--itl (default) and --itl=0 give walker g the start vertex g either way on one GPU; --full walks
+    from every vertex; --randstart draws the starts from the seeded stream."""
+    g = rmat12
+    w = np.floor(g.adjwgt).astype(np.float32)
+    table = oracle.alias_build(g.xadj, w)
+    base = ["--deepwalk", "--d", "6", "--bias=1", "--ol=0", "--input", gr_file, "--printresult"]
+    a = _paths_from_printresult(_run(*base, "-n", "32").stdout)
+    b = _paths_from_printresult(_run(*base, "-n", "32", "--itl=0").stdout)
+    assert a == b and [r[1][0] for r in a] == [0, 1, 2]
+    full = _run(*base, "--full", "-v").stdout
+    _, olens = oracle.walk(g.xadj, g.adjncy, w, table, np.arange(g.V, dtype=np.uint32), 7, seed=42)
+    assert int(re.search(r"sampled_edges (\d+)", full).group(1)) == int(olens.sum())
+    r = _paths_from_printresult(_run(*base, "-n", "32", "--randstart", "--seed", "9").stdout)
+    starts = oracle.gen_starts(32, g.V, 9)
+    assert [row[1][0] for row in r] == [int(x) for x in starts[:3]]
+    op, ol = oracle.walk(g.xadj, g.adjncy, w, table, starts, 7, seed=9)
+    assert [row[1] for row in r] == [list(op[j, :ol[j] + 1]) for j in range(3)]

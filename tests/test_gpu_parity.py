@@ -469,3 +469,35 @@ def test_bounded_wait_runs_out_cleanly(ctx, rmat12):
     _upload(ctx, rmat12)                     # the context keeps working
     ctx.alias_build_offline()
     assert ctx.walk(np.asarray([1, 2], np.uint32), 4)[0][0, 0] == 1
+
+
+def test_walker_ids_beyond_32_bits(ctx, oracle, rmat12):
+    """Global walker ids use both counter words: a base above 2^32 gives the oracle's rows."""
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    starts = oracle.gen_starts(700, g.V, 5)
+    base = (1 << 40) + 12345
+    p, l, _, _ = ctx.walk(starts, 31, app=APP_PPR, tp=0.05, seed=(1 << 50) + 7, walker_base=base)
+    op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 31, app=APP_PPR, tp=0.05, seed=(1 << 50) + 7,
+                         walker_base=base)
+    _cmp_walks(p, l, op, ol)
+    low, ll, _, _ = ctx.walk(starts, 31, app=APP_PPR, tp=0.05, seed=(1 << 50) + 7, walker_base=12345)
+    assert not np.array_equal(ll, l)          # the high word matters
+
+
+@pytest.mark.parametrize("fanout", [[7], [2, 3, 2, 2]])
+def test_khop_one_and_four_hops(ctx, oracle, rmat12, fanout):
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    seeds = oracle.gen_starts(300, g.V, 8)
+    for mode in (MODE_OFFLINE, MODE_ONLINE):
+        data, sl, _, e = ctx.sample_khop(seeds, fanout, mode=mode, seed=3, instance_base=1 << 33)
+        odata, osl = oracle.khop(g.xadj, g.adjncy, g.adjwgt, table, seeds, fanout, seed=3, instance_base=1 << 33)
+        assert np.array_equal(data, odata) and np.array_equal(sl, osl) and e == int(osl.sum())
+    from skywalker_b200.api import SkwError
+    with pytest.raises(SkwError):
+        ctx.sample_khop(seeds, [2, 2, 2, 2, 2])      # more than 4 hops
