@@ -1041,8 +1041,14 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
     attr_set[ctx->device & 63] = true;
   }
   // slabs of the global-scratch builder: one per CTA, sized by the largest degree
-  const int gmem_ctas = ctx->sm_count;
+  // one slab per CTA of the scratch class, sized by the largest degree; fewer CTAs when a giant
+  // hub would make the slabs exceed 4 GB in total
   const uint64_t slab_elems = ctx->max_degree > kHugeSmemMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
+  int gmem_ctas = ctx->sm_count;
+  if (slab_elems) {
+    const uint64_t fit = (4ull << 30) / (slab_elems * 12ull);
+    if (fit < (uint64_t)gmem_ctas) gmem_ctas = (int)(fit < 8 ? 8 : fit);
+  }
   if (slab_elems) {
     int rc = ensure_bytes(ctx, &ctx->cta_scratch, &ctx->cta_scratch_bytes, slab_elems * 12ull * gmem_ctas);
     if (rc != SKW_OK) return rc;

@@ -501,3 +501,23 @@ def test_khop_one_and_four_hops(ctx, oracle, rmat12, fanout):
     from skywalker_b200.api import SkwError
     with pytest.raises(SkwError):
         ctx.sample_khop(seeds, [2, 2, 2, 2, 2])      # more than 4 hops
+
+
+def test_alias_giant_vertex(ctx, oracle):
+    """One vertex with 8.6 M edges: bucket width drops below 40 bits, the scratch class needs more than
+    one round of 1023 windows; still bit for bit the sequential sweep."""
+    rng = np.random.default_rng(5)
+    n = 8_600_000
+    w = rng.uniform(1, 10, n).astype(np.float32)
+    w[::1000] = 0.0
+    xadj = np.asarray([0, n, n], np.uint32)
+    adj = np.ones(n, np.uint32)
+    ctx.upload(xadj, adj, w)
+    ctx.alias_build_offline()
+    prob, alias, valid = ctx.alias_export()
+    oprob, oalias, ok = oracle.alias_vertex(w)
+    assert ok and valid[0] == 1
+    assert np.array_equal(alias, oalias)
+    assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
+    M, B = oracle.alias_vertex_masses(w)
+    assert B == 38
