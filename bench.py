@@ -157,7 +157,9 @@ def cpu_leg(ctx, wl, threads, want_seconds=12.0):
     from oracle import oracle as O
     V, E, _ = ctx.graph_info()
     xadj, adjncy, wgt = ctx.download()
-    threads = threads or O.num_threads()
+    # all host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which must not shrink the
+    # CPU arm to one thread)
+    threads = threads or len(os.sched_getaffinity(0)) or O.num_threads()
     online = wl["mode"] == "online"
     target = min(E, max(1 << 20, E // 16))
     v_end = max(1, min(V, int(np.searchsorted(xadj, target, side="left"))))
@@ -492,8 +494,12 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_leg(ctx, wl, args.cpu_threads)
-        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample", "alias_build_edges_per_s")}
+        try:
+            cpu = cpu_leg(ctx, wl, args.cpu_threads)
+            cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample", "alias_build_edges_per_s")}
+        except MemoryError as e:   # the host copy of graph + table needs ~4 x E x 4 bytes
+            cpu = {"value": None, "unit": "sampled edges/s", "cores": 0, "kind": "port",
+                   "sample": "unavailable: host memory too small for the graph copy (%s)" % e}
 
     if rank == 0:
         per_step_ms = kernel_ms / args.steps

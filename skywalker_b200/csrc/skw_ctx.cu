@@ -442,13 +442,17 @@ int skw_alias_export(skw_ctx* ctx, float* h_prob, uint32_t* h_alias, uint8_t* h_
   if (!ctx->table_ready) return fail(ctx, SKW_ERR_STATE, "skw_alias_export: no table built");
   DeviceGuard g(ctx->device);
   if ((h_prob || h_alias) && ctx->E) {
-    std::vector<Slot> tmp(ctx->E);
-    SKW_CUDA(ctx, cudaMemcpyAsync(tmp.data(), ctx->slots, sizeof(Slot) * ctx->E,
-                                  cudaMemcpyDeviceToHost, ctx->stream));
-    SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    for (uint64_t i = 0; i < ctx->E; ++i) {
-      if (h_prob) h_prob[i] = tmp[i].prob < 0.0f ? 1.0f : tmp[i].prob;  // -1 marks "no usable weight"
-      if (h_alias) h_alias[i] = tmp[i].alias;
+    const uint64_t chunk = 32u << 20;  // slots per staging round (256 MB of host memory)
+    std::vector<Slot> tmp(ctx->E < chunk ? ctx->E : chunk);
+    for (uint64_t o = 0; o < ctx->E; o += chunk) {
+      const uint64_t cnt = ctx->E - o < chunk ? ctx->E - o : chunk;
+      SKW_CUDA(ctx, cudaMemcpyAsync(tmp.data(), ctx->slots + o, sizeof(Slot) * cnt, cudaMemcpyDeviceToHost,
+                                    ctx->stream));
+      SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      for (uint64_t i = 0; i < cnt; ++i) {
+        if (h_prob) h_prob[o + i] = tmp[i].prob < 0.0f ? 1.0f : tmp[i].prob;  // -1 marks "no usable weight"
+        if (h_alias) h_alias[o + i] = tmp[i].alias;
+      }
     }
   }
   if (h_valid && ctx->V) {
