@@ -345,33 +345,17 @@ __global__ void __launch_bounds__(256) generate_starts_kernel(u32* __restrict__ 
   }
 }
 
-// CTAs launched per SM by the all-steps walk kernels (about 5 are resident at a time).  A lane
-// walks its walkers one after another, so a CTA lives as long as its unluckiest lane; many short
-// CTAs keep the SMs evenly loaded to the end.  Measured on B200 at 8 M walkers: fixed-length walks
-// are fastest with one walker per thread (6.8 ms against 10.3 ms at 8 CTAs per SM on scale-26
-// DeepWalk); PPR, where most walkers stop after a few steps, is fastest at about 64 CTAs per SM
-// (1.19 ms against 1.46 ms at 8 and 1.35 ms at one walker per thread).
-static int walk_ctas_per_sm(uint32_t app) { return app == SKW_APP_PPR ? 64 : 1 << 20; }
-
-// Measurement aid: a dependent chain of random 32-byte record loads, the memory behaviour of a walk
-// stripped of everything else.  Every thread follows `iters` pseudo-random hops through `nrec`
-// records with the same load instruction the record walk uses.
-__global__ void __launch_bounds__(256) probe_gather_kernel(const WalkRecord* __restrict__ rec, u64 nrec,
-                                                           u32 iters, unsigned long long* __restrict__ sink) {
-  const u64 tid = (u64)blockIdx.x * blockDim.x + threadIdx.x;
-  u64 cur = (tid * 0x9E3779B97F4A7C15ull) % nrec;
-  u32 acc = 0;
-  for (u32 it = 0; it < iters; ++it) {
-    u32 w[8];
-    load_record(rec + cur, w);
-    acc += w[0];
-    u64 x = cur * 31 + w[7] + it + tid;
-    x ^= x >> 33;
-    x *= 0xff51afd7ed558ccdull;
-    x ^= x >> 33;
-    cur = x % nrec;
-  }
-  if (acc == 0x12345677u) atomicAdd(sink, 1ull);  // keeps the loads alive
+// Grid of the all-steps walk kernels.  A lane walks its walkers one after another, so a CTA lives
+// as long as its unluckiest lane; many short CTAs (about 5 are resident per SM at a time) keep the
+// SMs evenly loaded to the end.  Measured on B200 for 1, 2, 4 and 8 M walkers alike: fixed-length
+// walks are fastest with one walker per thread (8 M walkers, scale-26 DeepWalk: 6.8 ms against
+// 7.4 at three per thread and 10.3 at 8 CTAs per SM); PPR, where most walkers stop after a few
+// steps, with three walkers per thread (1.19 ms against 1.35 at one per thread and 1.46 at 8 CTAs
+// per SM).
+static int walk_grid(uint32_t app, u64 n) {
+  const u64 per_cta = 256ull * (app == SKW_APP_PPR ? 3 : 1);
+  const u64 b = (n + per_cta - 1) / per_cta;
+  return (int)(b ? (b < 0x7FFFFFFFull ? b : 0x7FFFFFFFull) : 1);
 }
 
 static int grid_for(const skw_ctx* ctx, u64 n, int per_sm) {
@@ -552,12 +536,12 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
       ra.V = a.V;
       ra.hop_num = a.hop_num;
       ra.tp = a.tp;
-      const int grid = grid_for(ctx, n, walk_ctas_per_sm(prm->app));
+      const int grid = walk_grid(prm->app, n);
       if (prm->app == SKW_APP_PPR) walk_records_walk_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(ra);
       else walk_records_walk_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(ra);
       SKW_LAUNCHED(ctx);
     } else if (!online) {
-      const int grid = grid_for(ctx, n, walk_ctas_per_sm(prm->app));
+      const int grid = walk_grid(prm->app, n);
       switch (prm->app) {
         case SKW_APP_DEEPWALK: walk_offline_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a); break;
         case SKW_APP_PPR: walk_offline_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a); break;
