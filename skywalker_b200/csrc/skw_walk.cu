@@ -358,6 +358,27 @@ static int walk_grid(uint32_t app, u64 n) {
   return (int)(b ? (b < 0x7FFFFFFFull ? b : 0x7FFFFFFFull) : 1);
 }
 
+// Measurement aid: a dependent chain of random 32-byte record loads, the memory behaviour of a walk
+// stripped of everything else.  Every thread follows `iters` pseudo-random hops through `nrec`
+// records with the same load instruction the record walk uses.
+__global__ void __launch_bounds__(256) probe_gather_kernel(const WalkRecord* __restrict__ rec, u64 nrec,
+                                                           u32 iters, unsigned long long* __restrict__ sink) {
+  const u64 tid = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+  u64 cur = (tid * 0x9E3779B97F4A7C15ull) % nrec;
+  u32 acc = 0;
+  for (u32 it = 0; it < iters; ++it) {
+    u32 w[8];
+    load_record(rec + cur, w);
+    acc += w[0];
+    u64 x = cur * 31 + w[7] + it + tid;
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdull;
+    x ^= x >> 33;
+    cur = x % nrec;
+  }
+  if (acc == 0x12345677u) atomicAdd(sink, 1ull);  // keeps the loads alive
+}
+
 static int grid_for(const skw_ctx* ctx, u64 n, int per_sm) {
   const u64 want = (n + 255) / 256;
   const u64 cap = (u64)ctx->sm_count * per_sm;
