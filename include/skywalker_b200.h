@@ -148,7 +148,9 @@ int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
  * src/main.cu:347).  Loading checks that the file was written for a graph of the same V and E. */
 int skw_alias_save(skw_ctx* ctx, const char* path);
 int skw_alias_load(skw_ctx* ctx, const char* path);
-/* Device address of the packed table: E slots of {float prob; uint32 alias} and V valid bytes. */
+/* Device address of the packed table: E slots of {float prob; uint32 alias} and V valid bytes.  The
+ * slot array is allocated with 1024 spare entries past E, so that ranks of a multi-GPU job can
+ * all-gather it in place in equal chunks of ceil(E / ranks) slots. */
 int skw_alias_device_ptrs(const skw_ctx* ctx, const void** d_slots, const uint8_t** d_valid);
 
 /* Alias table of ONE weight list without any allocation.  No counterpart in the reference (its

@@ -172,13 +172,17 @@ class Context:
     def alias_load(self, path):
         self._ck(self._lib.skw_alias_load(self._h, path.encode()))
 
-    def alias_device_arrays(self):
+    SLOT_SLACK = 1024   # spare slots allocated past E (see skw_alias_device_ptrs)
+
+    def alias_device_arrays(self, padded=False):
         """(slots as int64[E] -- one packed {f32 prob, u32 alias} per element --, valid as uint8[V]),
-        borrowed from the context: for collectives over table slices (multi-GPU sliced build)."""
+        borrowed from the context: for collectives over table slices (multi-GPU sliced build).
+        padded=True exposes the E + SLOT_SLACK allocated slots (in-place equal-chunk all-gather)."""
         V, E, _ = self.graph_info()
         a, b = C.c_void_p(), C.c_void_p()
         self._ck(self._lib.skw_alias_device_ptrs(self._h, C.byref(a), C.byref(b)))
-        return DeviceArray(a.value, E, "<i8", self), DeviceArray(b.value, V, "|u1", self)
+        return (DeviceArray(a.value, E + (self.SLOT_SLACK if padded else 0), "<i8", self),
+                DeviceArray(b.value, V, "|u1", self))
 
     def download_xadj(self):
         V, _, _ = self.graph_info()
@@ -348,6 +352,32 @@ def edge_balanced_ranges(xadj, parts):
     cuts = [int(np.searchsorted(xadj[:V], E // parts * r, side="left")) for r in range(parts)] + [V]
     cuts[0] = 0
     return [(cuts[r], cuts[r + 1]) for r in range(parts)]
+
+
+def edge_chunk_ranges(xadj, parts):
+    """For an in-place all-gather of the table in equal chunks of S = ceil(E / parts) slots: part r owns
+    slots [r*S, (r+1)*S) and must build every vertex that overlaps them, so a vertex straddling a chunk
+    boundary is built by both neighbours (same bits either way).  Returns (S, [(v_begin, v_end), ...]);
+    the ranges cover every vertex, also those without edges."""
+    E = int(xadj[-1])
+    V = len(xadj) - 1
+    S = max(1, -(-E // parts))
+    out = []
+    for r in range(parts):
+        lo, hi = min(r * S, E), min((r + 1) * S, E)
+        if hi > lo:
+            vb = int(np.searchsorted(xadj, lo, side="right")) - 1
+            ve = int(np.searchsorted(xadj, hi - 1, side="right"))
+        else:
+            vb = ve = V
+        out.append([vb, ve])
+    out[0][0] = 0
+    out[-1][1] = V
+    for r in range(parts - 1):     # vertices without edges between two chunks go to the earlier part
+        out[r][1] = max(out[r][1], min(out[r + 1][0], V))
+        if out[r][0] > out[r][1]:
+            out[r][0] = out[r][1]
+    return S, [tuple(x) for x in out]
 
 
 def ConstructTable(sampler, ngpu=1, index=0):

@@ -158,7 +158,8 @@ void drop_records(skw_ctx* ctx) {
 }
 
 int alloc_table(skw_ctx* ctx) {
-  if (!ctx->slots) SKW_CUDA(ctx, cudaMalloc(&ctx->slots, sizeof(Slot) * (ctx->E ? ctx->E : 1)));
+  // kSlotSlack spare entries let a multi-GPU caller all-gather the table in equal chunks in place
+  if (!ctx->slots) SKW_CUDA(ctx, cudaMalloc(&ctx->slots, sizeof(Slot) * (ctx->E + kSlotSlack)));
   if (!ctx->valid) {
     SKW_CUDA(ctx, cudaMalloc(&ctx->valid, ctx->V ? ctx->V : 1));
     SKW_CUDA(ctx, cudaMemsetAsync(ctx->valid, 0, ctx->V ? ctx->V : 1, ctx->stream));

@@ -11,6 +11,10 @@
 
 namespace skw {
 
+// Spare slots allocated past the table's E entries (room for the padded last chunk of an in-place
+// all-gather over up to 1024 ranks).
+constexpr uint32_t kSlotSlack = 1024;
+
 // Largest degree the shared-memory CTA builder takes (12 bytes of list state per edge).
 constexpr uint32_t kCtaSmemMaxDegree = 4096;
 

@@ -82,3 +82,23 @@ def test_edge_balanced_ranges_partition_the_vertices(oracle):
         assert max(sizes) <= E // parts + int(np.diff(x.astype(np.int64)).max()) + parts
     # degenerate: empty graph, more parts than vertices
     assert edge_balanced_ranges(np.zeros(3, np.uint32), 4) == [(0, 0), (0, 0), (0, 0), (0, 2)]
+
+
+def test_edge_chunk_ranges_cover_every_chunk(oracle):
+    sys.path.insert(0, ROOT)
+    from skywalker_b200.api import edge_chunk_ranges
+    x, a = oracle.gen_rmat(12, 16 << 12, seed=2)
+    E, V = int(x[-1]), len(x) - 1
+    for parts in (1, 2, 3, 8):
+        S, r = edge_chunk_ranges(x, parts)
+        assert S * parts >= E and S * (parts - 1) < E + S
+        assert r[0][0] == 0 and r[-1][1] == V
+        covered = np.zeros(V, bool)
+        for k, (vb, ve) in enumerate(r):
+            covered[vb:ve] = True
+            lo, hi = min(k * S, E), min((k + 1) * S, E)
+            if hi > lo:     # every slot of the chunk belongs to a vertex of the range
+                assert int(x[vb]) <= lo and int(x[ve]) >= hi
+        assert covered.all()
+    S, r = edge_chunk_ranges(np.zeros(5, np.uint32), 3)
+    assert r[0][0] == 0 and r[-1][1] == 4 and all(b <= e for b, e in r)
