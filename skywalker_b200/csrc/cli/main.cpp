@@ -233,45 +233,65 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     float ms = 0;
     bool sliced = false;
 #ifdef SKW_HAVE_NCCL
-    // More than one GPU: each builds the edge-balanced slice the reference would give it
-    // (--edgecut, include/sampler.cuh:151-158) and the slices are exchanged over NCCL, one broadcast
-    // per slice, straight into every GPU's table (the reference goes through pinned host memory,
-    // include/gpu_graph.cuh:282-291).  --dt=0 (shared host table) has no meaning here.
+    // More than one GPU: the slot array is cut into ndev equal chunks of S = ceil(E / ndev) slots;
+    // every GPU builds the vertices that overlap its chunk (a vertex straddling a boundary is built
+    // by both neighbours, with identical bits) and one in-place NCCL all-gather completes every
+    // GPU's table (the reference assembles edge-balanced slices through pinned host memory,
+    // include/sampler.cuh:151-158, include/gpu_graph.cuh:282-291).  --dt=0 (one shared host table)
+    // has no meaning here.
     if (sh.ndev > 1 && !sh.comms.empty() && E > 0) {
       std::vector<uint32_t> xadj((size_t)V + 1);
       rc = skw_graph_download(ctx, xadj.data(), nullptr, nullptr);
       if (rc) return fail_dev(out, ctx, rc, "skw_graph_download");
-      std::vector<uint32_t> cut(sh.ndev + 1);
-      for (int r = 0; r < sh.ndev; ++r)
-        cut[r] = r ? (uint32_t)(std::lower_bound(xadj.begin(), xadj.begin() + V, (uint32_t)(E / sh.ndev * r)) - xadj.begin()) : 0;
-      cut[sh.ndev] = V;
-      rc = skw_alias_build_offline(ctx, cut[dev], cut[dev + 1], &ms);
+      const uint64_t S = (E + sh.ndev - 1) / sh.ndev;
+      std::vector<uint32_t> vb(sh.ndev), ve(sh.ndev);
+      for (int r = 0; r < sh.ndev; ++r) {
+        const uint64_t lo = std::min<uint64_t>((uint64_t)r * S, E), hi = std::min<uint64_t>((uint64_t)(r + 1) * S, E);
+        if (hi > lo) {
+          vb[r] = (uint32_t)(std::upper_bound(xadj.begin(), xadj.end(), (uint32_t)lo) - xadj.begin()) - 1;
+          ve[r] = (uint32_t)(std::upper_bound(xadj.begin(), xadj.end(), (uint32_t)(hi - 1)) - xadj.begin());
+        } else {
+          vb[r] = ve[r] = V;
+        }
+      }
+      vb[0] = 0;
+      ve[sh.ndev - 1] = V;
+      for (int r = 0; r + 1 < sh.ndev; ++r) {  // vertices without edges between two chunks
+        ve[r] = std::max(ve[r], std::min(vb[r + 1], V));
+        if (vb[r] > ve[r]) vb[r] = ve[r];
+      }
+      rc = skw_alias_build_offline(ctx, vb[dev], ve[dev], &ms);
       if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline (slice)");
       const void* slots_c = nullptr;
       const uint8_t* valid_c = nullptr;
       skw_alias_device_ptrs(ctx, &slots_c, &valid_c);
-      uint64_t* slots = (uint64_t*)slots_c;  // 8-byte {prob, alias} slots
+      uint64_t* slots = (uint64_t*)slots_c;  // 8-byte {prob, alias} slots, 1024 spare entries past E
       uint8_t* valid = (uint8_t*)valid_c;
       cudaStream_t st;
       cudaStreamCreate(&st);
       cudaEvent_t e0, e1;
       cudaEventCreate(&e0);
       cudaEventCreate(&e1);
+      {  // the first collective of a communicator pays its connection set-up: keep that out of the table time
+        uint32_t* d_one = nullptr;
+        cudaMalloc(&d_one, sizeof(uint32_t));
+        cudaMemsetAsync(d_one, 0, sizeof(uint32_t), st);
+        ncclAllReduce(d_one, d_one, 1, ncclUint32, ncclSum, sh.comms[dev], st);
+        cudaStreamSynchronize(st);
+        cudaFree(d_one);
+      }
       cudaEventRecord(e0, st);
       ncclGroupStart();
-      for (int r = 0; r < sh.ndev; ++r) {
-        const size_t eb = xadj[cut[r]], ee = xadj[cut[r + 1]];
-        if (ee > eb) ncclBroadcast(slots + eb, slots + eb, ee - eb, ncclUint64, r, sh.comms[dev], st);
-        if (cut[r + 1] > cut[r])
-          ncclBroadcast(valid + cut[r], valid + cut[r], cut[r + 1] - cut[r], ncclUint8, r, sh.comms[dev], st);
-      }
+      ncclAllGather(slots + (size_t)dev * S, slots, S, ncclUint64, sh.comms[dev], st);
+      for (int r = 0; r < sh.ndev; ++r)
+        if (ve[r] > vb[r]) ncclBroadcast(valid + vb[r], valid + vb[r], ve[r] - vb[r], ncclUint8, r, sh.comms[dev], st);
       ncclGroupEnd();
       cudaEventRecord(e1, st);
       cudaStreamSynchronize(st);
       float gms = 0;
       cudaEventElapsedTime(&gms, e0, e1);
-      LOGV("device %d: slice [%u,%u) built in %.2f ms, table slices exchanged over NCCL in %.2f ms\n", dev, cut[dev],
-           cut[dev + 1], ms, gms);
+      LOGV("device %d: vertices [%u,%u) built in %.2f ms, table all-gathered over NCCL in %.2f ms\n", dev, vb[dev],
+           ve[dev], ms, gms);
       ms += gms;
       cudaEventDestroy(e0);
       cudaEventDestroy(e1);
