@@ -65,6 +65,9 @@ typedef enum skw_mode {
 #define SKW_KHOP_TAKE_ALL 1u /* reference behaviour (src/offline_sample.cu:120-128): when the  *
                               * fan-out is >= degree copy every neighbour instead of drawing  */
 
+#define SKW_KHOP_UNBIASED 2u /* uniform draws with replacement, no table (--bias=0,            *
+                              * src/unbiased_sample.cu:28-36); `mode` is ignored               */
+
 #define SKW_INVALID_VERTEX 0xFFFFFFFFu /* written into k-hop cells that hold no sample */
 
 /* ---------------------------------------------------------------- context ---------------- */
@@ -200,6 +203,10 @@ typedef struct skw_walk_params {
  * of rebuilding the frontier's tables at every step (the reference's --cache flag, src/main.cu:74).
  * The walks are identical; only the amount of build work changes. */
 #define SKW_WALK_CACHE_TABLES 1u
+/* Unbiased walk (the reference's --bias=0, src/unbiased_walk.cu:102-124): the neighbour is drawn
+ * uniformly, no alias table is read or built and `mode` is ignored; with SKW_APP_NODE2VEC this is
+ * the reference's unweighted rejection walk (src/unbiased_walk.cu:14-61). */
+#define SKW_WALK_UNBIASED 2u
 
 /* Optional wider layout of the same table for offline DeepWalk / PPR.  No counterpart in the
  * reference (whose step reads xadj, prob_array, alias_array and adjncy separately,

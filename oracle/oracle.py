@@ -44,7 +44,7 @@ def lib():
         L.orc_alias_build.argtypes = [C.c_uint32, C.c_uint32, u32p, f32p, f32p, u32p, u8p, C.c_int]
         L.orc_alias_reconstruct_maxrel.argtypes = [C.c_uint32, u32p, f32p, f32p, u32p, u8p]
         L.orc_alias_reconstruct_maxrel.restype = C.c_double
-        L.orc_walk.argtypes = [u32p, u32p, f32p, f32p, u32p, u8p, C.c_int, C.c_int, C.c_uint32,
+        L.orc_walk.argtypes = [u32p, u32p, f32p, f32p, u32p, u8p, C.c_int, C.c_int, C.c_int, C.c_uint32,
                                C.c_float, C.c_float, C.c_float, C.c_uint64, C.c_uint64, C.c_uint64, u32p,
                                C.c_uint64, u32p, u32p, C.c_int]
         L.orc_khop.argtypes = [u32p, u32p, f32p, f32p, u32p, u8p, C.c_int, C.c_uint32, u32p,
@@ -171,7 +171,7 @@ DEEPWALK, PPR, NODE2VEC = 0, 1, 2
 
 
 def walk(xadj, adjncy, adjwgt, table, starts, hop_num, app=DEEPWALK, online=False, tp=0.0,
-         p=2.0, q=0.5, seed=42, walker_base=0, threads=0, fill=0xFFFFFFFF, walker_stride=1):
+         p=2.0, q=0.5, seed=42, walker_base=0, threads=0, fill=0xFFFFFFFF, walker_stride=1, unbiased=False):
     """table = (prob, alias, valid) or None for online.  Returns (paths[n, hop_num], lengths[n]);
     cells after the walk's end keep `fill`."""
     n = len(starts)
@@ -183,7 +183,7 @@ def walk(xadj, adjncy, adjwgt, table, starts, hop_num, app=DEEPWALK, online=Fals
     paths = np.full((n, hop_num), fill, np.uint32)
     lengths = np.zeros(n, np.uint32)
     lib().orc_walk(xadj, _nz(adjncy, np.uint32), _nz(adjwgt, np.float32), _nz(prob, np.float32),
-                   _nz(alias, np.uint32), valid, int(online), app, hop_num, tp, p, q, seed,
+                   _nz(alias, np.uint32), valid, int(online), int(unbiased), app, hop_num, tp, p, q, seed,
                    walker_base, walker_stride, _nz(starts, np.uint32), n, paths.reshape(-1) if n else np.zeros(1, np.uint32),
                    _nz(lengths, np.uint32) if n else np.zeros(1, np.uint32), threads)
     return paths, lengths

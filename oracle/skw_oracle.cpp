@@ -277,8 +277,10 @@ enum { N2V_MAX_TRIALS = 64 };
 // f / max(1/p, 1, 1/q), f = 1/p back to the previous vertex, 1 to a neighbour of it, 1/q else.
 // online != 0 rebuilds the table of the current vertex from its weights at every step, as
 // OnlineWalkKernel does (src/online_walk.cu:10-40), instead of reading the stored one.
+// unbiased != 0: the neighbour is drawn uniformly (column only, no table), as UnbiasedWalkKernelStatic
+// does (src/unbiased_walk.cu:102-124); node2vec then is exactly Node2vecKernelStaticBuffer.
 static void walk_one(const u32* xadj, const u32* adjncy, const float* adjwgt, const float* prob,
-                     const u32* alias, const uint8_t* valid, int online, int app, u32 hop_num,
+                     const u32* alias, const uint8_t* valid, int online, int unbiased, int app, u32 hop_num,
                      float tp, float inv_p, float inv_q, u64 seed, u64 gw, u32 start, u32* row,
                      u32* length, std::vector<float>& tprob, std::vector<u32>& talias) {
   const float fmax = std::max(1.0f, std::max(inv_p, inv_q));
@@ -291,9 +293,10 @@ static void walk_one(const u32* xadj, const u32* adjncy, const float* adjwgt, co
     if (app == APP_PPR && u01(r[2]) < tp) break;
     const u32 off = xadj[cur], deg = xadj[cur + 1] - off;
     if (deg == 0) break;
-    const float* vp;
-    const u32* va;
-    if (online) {
+    const float* vp = nullptr;
+    const u32* va = nullptr;
+    if (unbiased) {
+    } else if (online) {
       tprob.resize(deg);
       talias.resize(deg);
       if (!alias_vertex(deg, adjwgt + off, tprob.data(), talias.data())) break;
@@ -308,7 +311,7 @@ static void walk_one(const u32* xadj, const u32* adjncy, const float* adjwgt, co
     if (app == APP_NODE2VEC && prev != 0xFFFFFFFFu) {
       u32 trial = 0;
       for (;;) {
-        const u32 cand = deg == 1 ? 0 : alias_draw(vp, va, deg, r[0], r[1]);
+        const u32 cand = unbiased ? mulhi32(r[0], deg) : (deg == 1 ? 0 : alias_draw(vp, va, deg, r[0], r[1]));
         next = adjncy[off + cand];
         const float f = next == prev ? inv_p : (connected(xadj, adjncy, prev, next) ? 1.0f : inv_q);
         if (u01(r[3]) * fmax < f) break;
@@ -316,7 +319,7 @@ static void walk_one(const u32* xadj, const u32* adjncy, const float* adjwgt, co
         philox_tagged(seed, TAG_WALK, gw, step, trial, r);
       }
     } else {
-      const u32 cand = deg == 1 ? 0 : alias_draw(vp, va, deg, r[0], r[1]);
+      const u32 cand = unbiased ? mulhi32(r[0], deg) : (deg == 1 ? 0 : alias_draw(vp, va, deg, r[0], r[1]));
       next = adjncy[off + cand];
     }
     row[step + 1] = next;
@@ -329,7 +332,7 @@ static void walk_one(const u32* xadj, const u32* adjncy, const float* adjwgt, co
 // n walkers; paths[w * hop_num + s], lengths[w] (include/sampler_result.cuh:607-612).
 // Cells after paths[w*hop_num + lengths[w]] are left untouched.
 void orc_walk(const u32* xadj, const u32* adjncy, const float* adjwgt, const float* prob,
-              const u32* alias, const uint8_t* valid, int online, int app, u32 hop_num, float tp,
+              const u32* alias, const uint8_t* valid, int online, int unbiased, int app, u32 hop_num, float tp,
               float p, float q, u64 seed, u64 walker_base, u64 walker_stride, const u32* starts, u64 n,
               u32* paths, u32* lengths, int threads) {
   const float inv_p = 1.0f / p, inv_q = 1.0f / q;
@@ -339,7 +342,7 @@ void orc_walk(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
     std::vector<u32> talias;
 #pragma omp for schedule(dynamic, 64)
     for (long long w = 0; w < (long long)n; ++w)
-      walk_one(xadj, adjncy, adjwgt, prob, alias, valid, online, app, hop_num, tp, inv_p, inv_q,
+      walk_one(xadj, adjncy, adjwgt, prob, alias, valid, online, unbiased, app, hop_num, tp, inv_p, inv_q,
                seed, walker_base + (u64)w * walker_stride, starts[w], paths + (u64)w * hop_num, lengths + w, tprob,
                talias);
   }
@@ -393,6 +396,13 @@ void orc_khop(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
             if ((flags & 1u) && f >= deg) {
               for (u32 j = 0; j < deg; ++j) child[j] = adjncy[off + j];
               got = deg;
+            } else if (flags & 2u) {  // unbiased: uniform column, no table (src/unbiased_sample.cu:28-36)
+              for (u32 j = 0; j < f; ++j) {
+                u32 r[4];
+                philox_tagged(seed, TAG_KHOP, gi, idx * f + j, h + 1, r);
+                child[j] = adjncy[off + mulhi32(r[0], deg)];
+              }
+              got = f;
             } else {
               if (online) {
                 tprob.resize(deg);

@@ -14,6 +14,8 @@ APP_DEEPWALK, APP_PPR, APP_NODE2VEC = 0, 1, 2
 MODE_OFFLINE, MODE_ONLINE = 0, 1
 KHOP_TAKE_ALL = 1
 WALK_CACHE_TABLES = 1
+WALK_UNBIASED = 2
+KHOP_UNBIASED = 2
 INVALID_VERTEX = 0xFFFFFFFF
 
 

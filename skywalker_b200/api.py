@@ -20,7 +20,8 @@ import numpy as np
 
 from . import _capi
 from ._capi import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, INVALID_VERTEX, KHOP_TAKE_ALL,
-                    MODE_OFFLINE, MODE_ONLINE, WALK_CACHE_TABLES, KhopParams, WalkParams)
+                    MODE_OFFLINE, MODE_ONLINE, WALK_CACHE_TABLES, WALK_UNBIASED, KHOP_UNBIASED, KhopParams,
+                    WalkParams)
 
 
 class SkwError(RuntimeError):
@@ -390,10 +391,10 @@ def ConstructTable(sampler, ngpu=1, index=0):
     return sampler.ctx.alias_build_offline(vb, ve) * 1e-3
 
 
-def _walk(walker, mode):
+def _walk(walker, mode, flags=0):
     paths, lengths, ms, edges = walker.ctx.walk(walker.starts, walker.hop_num, app=walker.app, mode=mode,
                                                 tp=walker.tp, p=walker.p, q=walker.q, seed=walker.seed,
-                                                walker_base=walker.walker_base)
+                                                walker_base=walker.walker_base, flags=flags)
     walker.result = _WalkResult(paths, lengths)
     walker.sampled_edges = edges
     return ms * 1e-3
@@ -412,8 +413,14 @@ def OnlineWalkShMem(walker):
 OnlineWalkGMem = OnlineWalkShMem  # same result; the reference differs only in scratch placement
 
 
-def _sample(sampler, mode):
-    data, lens, ms, edges = sampler.ctx.sample_khop(sampler.seeds, sampler.hops[1:], mode=mode, flags=sampler.flags,
+def UnbiasedWalk(walker):
+    """Uniform neighbour choice, no table (src/unbiased_walk.cu:194-247)."""
+    return _walk(walker, MODE_OFFLINE, WALK_UNBIASED)
+
+
+def _sample(sampler, mode, flags=0):
+    data, lens, ms, edges = sampler.ctx.sample_khop(sampler.seeds, sampler.hops[1:], mode=mode,
+                                                    flags=sampler.flags | flags,
                                                     seed=sampler.seed, instance_base=sampler.instance_base)
     sampler.result = _SampleResult(data, lens)
     sampler.sampled_edges = edges
@@ -428,3 +435,8 @@ def OfflineSample(sampler):
 def OnlineGBSampleNew(sampler):
     """src/online_sample_new.cu:459-547."""
     return _sample(sampler, MODE_ONLINE)
+
+
+def UnbiasedSample(sampler):
+    """Uniform draws with replacement, no table (src/unbiased_sample.cu:322-384)."""
+    return _sample(sampler, MODE_OFFLINE, KHOP_UNBIASED)

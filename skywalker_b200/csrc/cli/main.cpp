@@ -14,11 +14,13 @@
 // --d is honoured when given explicitly together with --deepwalk / --ppr / --node2vec (the
 // reference overrides it with 100).
 #include <algorithm>
+#include <condition_variable>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <thread>
 #include <vector>
@@ -179,7 +181,42 @@ struct DevResult {
   std::string err;
 };
 
+// Host-side agreement of the device threads before a collective: a thread that failed earlier must
+// never leave its peers waiting inside an NCCL kernel, so each thread reports its status here and
+// enters the collective only when every thread is present and healthy.
+struct Rendezvous {
+  std::mutex m;
+  std::condition_variable cv;
+  int ndev = 1, arrived = 0, gone = 0;
+  uint64_t gen = 0;
+  bool ok = true, verdict = true;
+  void release() {  // caller holds m
+    verdict = ok && gone == 0;
+    arrived = 0;
+    ok = true;
+    ++gen;
+    cv.notify_all();
+  }
+  bool agree(bool mine) {
+    std::unique_lock<std::mutex> l(m);
+    ok = ok && mine;
+    const uint64_t g = gen;
+    if (++arrived + gone >= ndev) {
+      release();
+      return verdict;
+    }
+    cv.wait(l, [&] { return gen != g; });
+    return verdict;
+  }
+  void leave() {  // a thread that ends (for whatever reason) takes part in no later agreement
+    std::lock_guard<std::mutex> l(m);
+    ++gone;
+    if (arrived && arrived + gone >= ndev) release();
+  }
+};
+
 struct Shared {
+  Rendezvous rv;
   int ndev;
   uint32_t V = 0;
   uint64_t E = 0;
@@ -228,8 +265,7 @@ int run_device(int dev, Shared& sh, DevResult& out) {
   }
   LOGV("device %d: %u nodes, %llu edges, max degree %u\n", dev, V, (unsigned long long)E, maxdeg);
   const bool online = fb("ol");
-  if (!bias) return fail_dev(out, nullptr, SKW_ERR_ARG, "--bias=0 (unbiased sampling) is outside this build");
-  if (!online) {
+  if (bias && !online) {
     float ms = 0;
     bool sliced = false;
 #ifdef SKW_HAVE_NCCL
@@ -242,7 +278,7 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     if (sh.ndev > 1 && !sh.comms.empty() && E > 0) {
       std::vector<uint32_t> xadj((size_t)V + 1);
       rc = skw_graph_download(ctx, xadj.data(), nullptr, nullptr);
-      if (rc) return fail_dev(out, ctx, rc, "skw_graph_download");
+      if (rc) return fail_dev(out, ctx, rc, "skw_graph_download");  // the others learn of it in agree() below
       const uint64_t S = (E + sh.ndev - 1) / sh.ndev;
       std::vector<uint32_t> vb(sh.ndev), ve(sh.ndev);
       for (int r = 0; r < sh.ndev; ++r) {
@@ -261,7 +297,12 @@ int run_device(int dev, Shared& sh, DevResult& out) {
         if (vb[r] > ve[r]) vb[r] = ve[r];
       }
       rc = skw_alias_build_offline(ctx, vb[dev], ve[dev], &ms);
-      if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline (slice)");
+      if (!sh.rv.agree(rc == 0)) {
+        if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline (slice)");
+        out.rc = SKW_ERR_STATE;
+        out.err = "another device failed before the table all-gather";
+        return out.rc;
+      }
       const void* slots_c = nullptr;
       const uint8_t* valid_c = nullptr;
       skw_alias_device_ptrs(ctx, &slots_c, &valid_c);
@@ -352,7 +393,7 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     p.seed = (uint64_t)fi("seed");
     p.walker_base = id_base;
     p.walker_stride = id_stride;
-    p.flags = fb("cache") ? SKW_WALK_CACHE_TABLES : 0;
+    p.flags = (fb("cache") ? SKW_WALK_CACHE_TABLES : 0) | (bias ? 0 : SKW_WALK_UNBIASED);
     cudaMalloc(&d_data, sizeof(uint32_t) * std::max<long>(n_local, 1) * p.hop_num);
     cudaMalloc(&d_len, sizeof(uint32_t) * std::max<long>(n_local, 1));
     rc = skw_walk_device(ctx, &p, d_starts, n_local, d_data, d_len, &ms, &edges);
@@ -376,7 +417,8 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     p.nhops = (uint32_t)sh.depth;
     if (p.nhops > 4) return fail_dev(out, nullptr, SKW_ERR_ARG, "k-hop sampling supports --d up to 4");
     for (uint32_t h = 0; h < p.nhops; ++h) p.fanout[h] = sh.hops[h + 1];
-    p.flags = SKW_KHOP_TAKE_ALL;  // the reference copies all neighbours when fan-out >= degree
+    // the reference copies all neighbours when fan-out >= degree; --bias=0 draws uniformly
+    p.flags = SKW_KHOP_TAKE_ALL | (bias ? 0 : SKW_KHOP_UNBIASED);
     p.seed = (uint64_t)fi("seed");
     uint32_t cells, lens;
     if (skw_khop_layout(&p, &cells, &lens)) return fail_dev(out, nullptr, SKW_ERR_ARG, "bad --k/--d for k-hop sampling");
@@ -414,7 +456,7 @@ int run_device(int dev, Shared& sh, DevResult& out) {
 #ifdef SKW_HAVE_NCCL
   // results stay on the GPU that produced them (as in the reference); with --gather the per-walker
   // lengths are collected on GPU 0 over NCCL
-  if (sh.ndev > 1 && fb("gather") && fb("rw") && !sh.comms.empty()) {
+  if (sh.ndev > 1 && fb("gather") && fb("rw") && !sh.comms.empty() && sh.rv.agree(true)) {
     const size_t cnt = (size_t)std::max<long>(n_local, 1);
     uint32_t* d_all = nullptr;
     if (dev == 0) cudaMalloc(&d_all, sizeof(uint32_t) * cnt * sh.ndev);
@@ -496,7 +538,12 @@ int main(int argc, char** argv) {
 #endif
   std::vector<DevResult> res(sh.ndev);
   std::vector<std::thread> th;
-  for (int dev = 0; dev < sh.ndev; ++dev) th.emplace_back([&, dev] { run_device(dev, sh, res[dev]); });
+  sh.rv.ndev = sh.ndev;
+  for (int dev = 0; dev < sh.ndev; ++dev)
+    th.emplace_back([&, dev] {
+      run_device(dev, sh, res[dev]);
+      sh.rv.leave();
+    });
   for (auto& t : th) t.join();
 #ifdef SKW_HAVE_NCCL
   for (auto c : sh.comms) ncclCommDestroy(c);

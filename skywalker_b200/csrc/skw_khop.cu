@@ -63,6 +63,11 @@ __global__ void __launch_bounds__(256) khop_hop_kernel(const KhopArgs a) {
           } else {
             const Rand4 r = philox_tagged(a.seed, TAG_KHOP, a.instance_base + s * a.instance_stride, rem, a.hop);
             const u32 col = __umulhi(r.x, deg);
+            if (a.flags & SKW_KHOP_UNBIASED) {
+              out = ldg_once(a.adjncy + (u64)off + col);
+              got = a.fanout;
+              goto store;
+            }
             const Slot sl = load_slot(a.slots + (u64)off + col);
             if (!(sl.prob < 0.0f)) {
               const u32 cand = u01(r.y) < sl.prob ? col : sl.alias;
@@ -73,6 +78,7 @@ __global__ void __launch_bounds__(256) khop_hop_kernel(const KhopArgs a) {
         }
       }
     }
+  store:
     row[a.offs_child + rem] = out;
     if (j == 0) {
       a.lens[s * a.lens_per + a.offs_parent + idx] = got;
@@ -127,8 +133,9 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
   if (rc != SKW_OK) return rc;
   if (n && (!d_seeds || !d_data || !d_sample_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: null buffer");
   if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: no graph resident");
-  const bool online = prm->mode == SKW_MODE_ONLINE;
-  if (!online && !ctx->table_ready)
+  const bool unbiased = (prm->flags & SKW_KHOP_UNBIASED) != 0;
+  const bool online = prm->mode == SKW_MODE_ONLINE && !unbiased;
+  if (!online && !unbiased && !ctx->table_ready)
     return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: offline mode needs skw_alias_build_offline or skw_alias_import first");
   if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: online mode needs the edge weights");
   DeviceGuard g(ctx->device);

@@ -37,6 +37,7 @@ struct WalkArgs {
   u64 walker_stride;
   u32 V;
   u32 hop_num;
+  u32 unbiased;  // uniform neighbour choice: no table is read
   float tp, inv_p, inv_q, fmax;
 };
 
@@ -71,9 +72,12 @@ __device__ __forceinline__ bool walk_step(const WalkArgs& a, u64 gw, u32 step, u
   if (APP == SKW_APP_NODE2VEC && prev != kNoVertex) {
     for (u32 trial = 0;;) {
       const u32 col = __umulhi(r.x, deg);
-      const Slot s = load_slot(a.slots + (u64)off + col);
-      if (s.prob < 0.0f) return false;  // vertex without usable weight
-      const u32 cand = u01(r.y) < s.prob ? col : s.alias;
+      u32 cand = col;
+      if (!a.unbiased) {
+        const Slot s = load_slot(a.slots + (u64)off + col);
+        if (s.prob < 0.0f) return false;  // vertex without usable weight
+        cand = u01(r.y) < s.prob ? col : s.alias;
+      }
       next = ldg_once(a.adjncy + (u64)off + cand);
       const float f = next == prev ? a.inv_p : (connected(a.xadj, a.adjncy, prev, next) ? 1.0f : a.inv_q);
       if (__fmul_rn(u01(r.w), a.fmax) < f) break;
@@ -83,9 +87,12 @@ __device__ __forceinline__ bool walk_step(const WalkArgs& a, u64 gw, u32 step, u
     return true;
   }
   const u32 col = __umulhi(r.x, deg);
-  const Slot s = load_slot(a.slots + (u64)off + col);
-  if (s.prob < 0.0f) return false;
-  const u32 cand = u01(r.y) < s.prob ? col : s.alias;
+  u32 cand = col;
+  if (!a.unbiased) {
+    const Slot s = load_slot(a.slots + (u64)off + col);
+    if (s.prob < 0.0f) return false;
+    cand = u01(r.y) < s.prob ? col : s.alias;
+  }
   next = ldg_once(a.adjncy + (u64)off + cand);
   return true;
 }
@@ -498,8 +505,9 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   if (prm->app == SKW_APP_NODE2VEC && !(prm->p > 0.0f && prm->q > 0.0f))
     return fail(ctx, SKW_ERR_ARG, "skw_walk: p and q must be positive");
   if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_walk: no graph resident");
-  const bool online = prm->mode == SKW_MODE_ONLINE;
-  if (!online && !ctx->table_ready)
+  const bool unbiased = (prm->flags & SKW_WALK_UNBIASED) != 0;
+  const bool online = prm->mode == SKW_MODE_ONLINE && !unbiased;
+  if (!online && !unbiased && !ctx->table_ready)
     return fail(ctx, SKW_ERR_STATE, "skw_walk: offline mode needs skw_alias_build_offline or skw_alias_import first");
   if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_walk: online mode needs the edge weights");
   DeviceGuard g(ctx->device);
@@ -523,6 +531,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   a.walker_stride = prm->walker_stride ? prm->walker_stride : 1;
   a.V = ctx->V;
   a.hop_num = prm->hop_num;
+  a.unbiased = unbiased ? 1u : 0u;
   a.tp = prm->tp;
   a.inv_p = prm->app == SKW_APP_NODE2VEC ? 1.0f / prm->p : 1.0f;
   a.inv_q = prm->app == SKW_APP_NODE2VEC ? 1.0f / prm->q : 1.0f;
@@ -540,7 +549,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
     SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
   }
   if (n) {
-    if (!online && ctx->records && prm->app != SKW_APP_NODE2VEC) {
+    if (!online && !unbiased && ctx->records && prm->app != SKW_APP_NODE2VEC) {
       RecordWalkArgs ra;
       ra.rec = static_cast<const WalkRecord*>(ctx->records);
       ra.vinfo = static_cast<const uint2*>(ctx->vinfo);

@@ -74,8 +74,6 @@ def test_cli_presets_and_modes(gr_file):
         out = _run(*args, "--bias=1", "-n", "256", "--input", gr_file).stdout
         mseps = float(out.strip().split("\n")[-1])
         assert mseps > 0
-    p = _run("--bias=0", "--deepwalk", "--input", gr_file, check=False)
-    assert p.returncode == 2 and "outside this build" in p.stderr
     p = _run("--deepwalk", "--input", gr_file + ".missing", check=False)
     assert p.returncode == 2 and "cannot open" in p.stderr
 
@@ -123,3 +121,20 @@ def test_cli_start_vertex_conventions(oracle, rmat12, gr_file):
     assert [row[1][0] for row in r] == [int(x) for x in starts[:3]]
     op, ol = oracle.walk(g.xadj, g.adjncy, w, table, starts, 7, seed=9)
     assert [row[1] for row in r] == [list(op[j, :ol[j] + 1]) for j in range(3)]
+
+
+@pytest.mark.gpu
+def test_cli_unbiased_modes(oracle, rmat12, gr_file):
+    # --bias=0: uniform neighbour choice, no table row (src/main.cu:408-419 prints it only with --bias)
+    g = rmat12
+    out = _run("--deepwalk", "--d", "10", "--bias=0", "-n", "64", "--input", gr_file, "--printresult").stdout
+    assert len(re.findall(r"^([\d.]+)\t$", out, re.M)) == 2
+    starts = np.arange(64, dtype=np.uint32)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, None, None, starts, 11, seed=42, unbiased=True)
+    shown = _paths_from_printresult(out)
+    assert len(shown) == 3
+    for j, (length, row) in enumerate(shown):
+        assert length == olens[j] and row == list(opaths[j, :length + 1])
+    for args in (["--ppr"], ["--sage"], ["--node2vec", "--d", "8"]):
+        out = _run(*args, "--bias=0", "-n", "256", "--input", gr_file).stdout
+        assert float(out.strip().split("\n")[-1]) > 0

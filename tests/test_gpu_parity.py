@@ -7,7 +7,8 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-from skywalker_b200 import APP_DEEPWALK, APP_NODE2VEC, APP_PPR, KHOP_TAKE_ALL, MODE_OFFLINE, MODE_ONLINE
+from skywalker_b200 import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, KHOP_TAKE_ALL, KHOP_UNBIASED, MODE_OFFLINE,
+                            MODE_ONLINE, WALK_UNBIASED)
 
 
 def _upload(ctx, g):
@@ -521,3 +522,37 @@ def test_alias_giant_vertex(ctx, oracle):
     assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
     M, B = oracle.alias_vertex_masses(w)
     assert B == 38
+
+
+@pytest.mark.parametrize("app,kw", [(APP_DEEPWALK, {}), (APP_PPR, {"tp": 0.15}), (APP_NODE2VEC, {"p": 2.0, "q": 0.5})])
+def test_unbiased_walks_bit_exact(ctx, oracle, plaw, app, kw):
+    # uniform neighbour choice: no table needed, neither weights (the graph goes up without them)
+    g = plaw
+    ctx.upload(g.xadj, g.adjncy, None)
+    starts = oracle.gen_starts(3000, g.V, 7)
+    hop = 41 if app != APP_PPR else 101
+    paths, lens, ms, edges = ctx.walk(starts, hop, app=app, seed=5, walker_base=17, flags=WALK_UNBIASED, **kw)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, None, None, starts, hop, app=app, seed=5, walker_base=17,
+                                unbiased=True, **kw)
+    _cmp_walks(paths, lens, opaths, olens)
+    assert edges == int(olens.sum())
+    # a resident table and walk records change nothing about an unbiased walk
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    ctx.walk_records_build()
+    paths2, lens2, _, _ = ctx.walk(starts, hop, app=app, mode=MODE_ONLINE, seed=5, walker_base=17,
+                                   flags=WALK_UNBIASED, **kw)
+    assert np.array_equal(lens2, lens) and np.array_equal(paths2, paths)
+
+
+@pytest.mark.parametrize("flags", [0, KHOP_TAKE_ALL])
+def test_unbiased_khop_bit_exact(ctx, oracle, rmat16, flags):
+    g = rmat16
+    ctx.upload(g.xadj, g.adjncy, None)
+    seeds = oracle.gen_starts(2048, g.V, 11)
+    data, sl, ms, edges = ctx.sample_khop(seeds, [25, 10], flags=flags | KHOP_UNBIASED, seed=77, instance_base=3)
+    odata, osl = oracle.khop(g.xadj, g.adjncy, None, None, seeds, [25, 10], flags=flags | 2, seed=77,
+                             instance_base=3)
+    assert np.array_equal(sl, osl)
+    assert np.array_equal(data, odata)
+    assert edges == int(osl.sum())

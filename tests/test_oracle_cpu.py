@@ -171,3 +171,34 @@ def test_chi_square_transition_frequencies(oracle):
     wf = w.astype(np.float64)
     chi, pval = stats.chisquare(counts, f_exp=wf / wf.sum() * counts.sum())
     assert pval > 0.01
+
+
+def test_unbiased_walks_and_samples_ignore_weights(oracle, rmat12):
+    g = rmat12
+    starts = oracle.gen_starts(4000, g.V, 3)
+    paths, lens = oracle.walk(g.xadj, g.adjncy, None, None, starts, 21, seed=8, unbiased=True)
+    # every step follows an edge; lengths end only at dead ends
+    for w in range(0, 4000, 97):
+        for s in range(lens[w]):
+            u, v = paths[w, s], paths[w, s + 1]
+            assert v in g.adjncy[g.xadj[u]:g.xadj[u + 1]]
+        if lens[w] < 20:
+            u = paths[w, lens[w]]
+            assert g.xadj[u + 1] == g.xadj[u]
+    # first-step frequencies from one vertex are uniform over its columns (chi-square, 64 columns)
+    deg = np.diff(g.xadj.astype(np.int64))
+    v = int(np.argmax(deg >= 64))
+    n = 200 * int(deg[v])
+    p1, l1 = oracle.walk(g.xadj, g.adjncy, None, None, np.full(n, v, np.uint32), 2, seed=1, unbiased=True)
+    nbrs = g.adjncy[g.xadj[v]:g.xadj[v + 1]]
+    uniq, mult = np.unique(nbrs, return_counts=True)
+    got = np.array([(p1[:, 1] == u).sum() for u in uniq], np.float64)
+    exp = mult.astype(np.float64) / mult.sum() * n
+    chi2 = ((got - exp) ** 2 / exp).sum()
+    assert chi2 < len(uniq) + 6 * np.sqrt(2 * len(uniq))
+    # k-hop: uniform draws need no table; TAKE_ALL still copies whole neighbour lists
+    seeds = oracle.gen_starts(256, g.V, 5)
+    data, sl = oracle.khop(g.xadj, g.adjncy, None, None, seeds, [6, 3], flags=1 | 2, seed=4)
+    for s in range(0, 256, 17):
+        d = int(deg[seeds[s]])
+        assert sl[s, 0] == (min(d, 6) if d else 0)
