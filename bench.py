@@ -450,27 +450,47 @@ def main():
         np_s, np_r, np_l = (t.numpy().view(np.uint32) for t in (h_starts, h_res, h_len))
         if khop:
             np_r, np_l = np_r.reshape(nl, -1), np_l.reshape(nl, -1)
-        step(0, np_s, np_r, np_l)
-        barrier()
         e_steps = max(1, min(args.steps, 5))
-        t0 = time.perf_counter()
-        e_edges = 0
-        for i in range(e_steps):
-            e_edges += step(100 + i, np_s, np_r, np_l)[3]
-        barrier()
-        e_ms = (time.perf_counter() - t0) * 1e3
-        m2, s2 = combine_over_ranks(dist, [e_ms, float(e_edges)], dev)
-        e_ms, e_edges = m2[0], s2[1]
-        e2e = {"value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
-               "ms_per_step": e_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
-               # walks into pinned memory transfer the written cells of each row (length + 1) and the lengths;
-               # k-hop trees are dense and are copied whole
-               "d2h_bytes_per_step": (4 * (result.numel() + lengths.numel()) if khop else
-                                      int(4 * (e_edges / e_steps / world + 2 * n_local))),
-               "note": "host-buffer entry point with pinned memory: start vertices H2D, kernels, then "
-                       + ("the whole result tree D2H" if khop else
-                          "cells 0..length of every path row written into the pinned n x hop_num matrix by a "
-                          "kernel, plus the lengths D2H")}
+
+        def timed_host_calls(call):
+            call(0)
+            barrier()
+            t0 = time.perf_counter()
+            edges = 0
+            for i in range(e_steps):
+                edges += call(100 + i)
+            barrier()
+            ms_ = (time.perf_counter() - t0) * 1e3
+            m2, s2 = combine_over_ranks(dist, [ms_, float(edges)], dev)
+            return m2[0], s2[1]
+
+        e_ms, e_edges = timed_host_calls(lambda i: step(i, np_s, np_r, np_l)[3])
+        rows = {"value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+                "ms_per_step": e_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
+                # walks into pinned memory transfer the written cells of each row (length + 1) and the lengths;
+                # k-hop trees are dense and are copied whole
+                "d2h_bytes_per_step": (4 * (result.numel() + lengths.numel()) if khop else
+                                       int(4 * (e_edges / e_steps / world + 2 * n_local))),
+                "note": "host-buffer entry point with pinned memory: start vertices H2D, kernels, then "
+                        + ("the whole result tree D2H" if khop else
+                           "cells 0..length of every path row written into the pinned n x hop_num matrix by a "
+                           "kernel, plus the lengths D2H")}
+        e2e = rows
+        if not khop:
+            # the same walks returned packed (lengths + the walks back to back): only result cells cross
+            # the bus, as one contiguous stream instead of one small write per row
+            def packed_call(i):
+                return ctx.walk_packed(np_s, hop, app=app_id(wl), mode=mode, tp=wl.get("tp", 0.0), p=wl.get("p", 2.0),
+                                       q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, packed=np_r,
+                                       lengths=np_l, n=n_local)[4]
+            p_ms, p_edges = timed_host_calls(packed_call)
+            e2e = {"value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+                   "ms_per_step": p_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
+                   "d2h_bytes_per_step": int(4 * (p_edges / e_steps / world + 2 * n_local)),
+                   "note": "host-buffer entry point skw_walk_packed with pinned memory: start vertices H2D, walk "
+                           "kernel, prefix sum of the lengths, pack kernel writing lengths[w] + 1 vertices per walk "
+                           "back to back into the pinned result buffer, lengths D2H",
+                   "row_layout": rows}
 
     # NCCL gather of the per-unit lengths to rank 0 (results gather; outside the timed region)
     gather_ms = None

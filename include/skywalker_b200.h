@@ -241,6 +241,18 @@ int skw_ctx_take_sampled_edges(skw_ctx* ctx, uint64_t* out);
  * walk's end are unspecified. */
 int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
              uint32_t* h_paths, uint32_t* h_lengths, float* ms, uint64_t* sampled_edges);
+/* Host buffers, packed result.  No counterpart in the reference, which leaves results on the
+ * device (include/sampler_result.cuh:571-612).  h_lengths[w] as in skw_walk; h_packed receives the
+ * walks back to back in walker order, walk w holding lengths[w] + 1 vertices (its start first)
+ * from cell sum_{u<w}(lengths[u] + 1) on -- the same values the row layout holds in
+ * paths[w * hop_num + 0 .. lengths[w]].  *cells = cells the result needs (= sampled edges + n).
+ * When capacity_cells is smaller (or h_packed is NULL) the call fills h_lengths and *cells, writes
+ * nothing to h_packed and returns SKW_ERR_ARG; the same call with a buffer of *cells cells then
+ * returns the same walks.  Rows are packed on the device and leave in one contiguous copy, so
+ * only cells that hold a result cross the bus (fastest with pinned h_packed / h_lengths). */
+int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+                    uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_lengths, uint64_t* cells,
+                    float* ms, uint64_t* sampled_edges);
 
 /* ---------------------------------------------------------------- k-hop sampling --------- */
 

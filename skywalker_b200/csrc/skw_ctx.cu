@@ -210,6 +210,7 @@ int skw_ctx_create(int device, skw_ctx** out) {
   CK(cudaGetDeviceProperties(&prop, device));
   ctx->sm_count = prop.multiProcessorCount;
   CK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
+  CK(cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
   ctx->stream = ctx->own_stream;
   CK(cudaEventCreate(&ctx->ev0));
   CK(cudaEventCreate(&ctx->ev1));
@@ -240,10 +241,11 @@ void skw_ctx_destroy(skw_ctx* ctx) {
   cudaFree(ctx->cta_scratch);
   cudaFree(ctx->frontier_lists);
   cudaFree(ctx->frontier_cls);
-  for (int i = 0; i < 4; ++i) cudaFree(ctx->stage[i]);
+  for (int i = 0; i < 6; ++i) cudaFree(ctx->stage[i]);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+  if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
   delete ctx;
 }
 

@@ -25,6 +25,7 @@ struct skw_ctx {
   int sm_count = 0;
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
+  cudaStream_t side_stream = nullptr;  // result copies that overlap kernels of `stream`
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::string err;
   uint64_t launches = 0;
@@ -71,8 +72,8 @@ struct skw_ctx {
   uint32_t stamp_round = 0;
 
   // staging buffers of the host-pointer entry points, grown on demand
-  void* stage[4] = {nullptr, nullptr, nullptr, nullptr};
-  size_t stage_bytes[4] = {0, 0, 0, 0};
+  void* stage[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t stage_bytes[6] = {0, 0, 0, 0, 0, 0};
 };
 
 namespace skw {

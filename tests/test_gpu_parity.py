@@ -556,3 +556,42 @@ def test_unbiased_khop_bit_exact(ctx, oracle, rmat16, flags):
     assert np.array_equal(sl, osl)
     assert np.array_equal(data, odata)
     assert edges == int(osl.sum())
+
+
+@pytest.mark.parametrize("pinned", [False, True])
+def test_packed_host_result_matches_rows(ctx, oracle, plaw, pinned):
+    import torch
+    from skywalker_b200.api import SkwError
+    g = plaw
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    starts = oracle.gen_starts(5000, g.V, 21)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 101, app=APP_PPR, tp=0.15, seed=13)
+    want = np.concatenate([opaths[w, :olens[w] + 1] for w in range(len(starts))])
+    cap = len(want) + 7
+    if pinned:
+        buf = torch.empty(cap, dtype=torch.int32).pin_memory()
+        packed = buf.numpy().view(np.uint32)
+    else:
+        packed = np.zeros(cap, np.uint32)
+    packed[:] = 0xABCDEF01
+    out, lens, cells, ms, edges = ctx.walk_packed(starts, 101, app=APP_PPR, tp=0.15, seed=13, packed=packed)
+    assert cells == len(want) == edges + len(starts)
+    assert np.array_equal(lens, olens)
+    assert np.array_equal(out[:cells], want)
+    assert (out[cells:] == 0xABCDEF01).all()              # nothing written past the result
+    # a buffer that is too small: lengths and the needed size come back, nothing is written, the context lives on
+    small = np.full(cells - 1, 0xABCDEF01, np.uint32)
+    lens2 = np.zeros(len(starts), np.uint32)
+    with pytest.raises(SkwError) as e:
+        ctx.walk_packed(starts, 101, app=APP_PPR, tp=0.15, seed=13, packed=small, lengths=lens2)
+    assert str(cells) in str(e.value)
+    assert np.array_equal(lens2, olens) and (small == 0xABCDEF01).all()
+    # no walkers
+    _, _, cells0, _, edges0 = ctx.walk_packed(np.zeros(0, np.uint32), 101, app=APP_PPR, tp=0.15, seed=13)
+    assert cells0 == 0 and edges0 == 0
+    # fixed-length walks fill whole rows
+    out3, lens3, cells3, _, _ = ctx.walk_packed(starts[:100], 11, seed=3)
+    p3, l3 = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts[:100], 11, seed=3)
+    assert np.array_equal(out3[:cells3], np.concatenate([p3[w, :l3[w] + 1] for w in range(100)]))
