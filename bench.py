@@ -456,16 +456,18 @@ def main():
             call(0)
             barrier()
             t0 = time.perf_counter()
-            edges = 0
+            edges, per_call = 0, []
             for i in range(e_steps):
+                t1 = time.perf_counter()
                 edges += call(100 + i)
+                per_call.append(round((time.perf_counter() - t1) * 1e3, 3))
             barrier()
             ms_ = (time.perf_counter() - t0) * 1e3
             m2, s2 = combine_over_ranks(dist, [ms_, float(edges)], dev)
-            return m2[0], s2[1]
+            return m2[0], s2[1], per_call
 
-        e_ms, e_edges = timed_host_calls(lambda i: step(i, np_s, np_r, np_l)[3])
-        rows = {"value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+        e_ms, e_edges, e_calls = timed_host_calls(lambda i: step(i, np_s, np_r, np_l)[3])
+        rows = {"ms_per_call_this_rank": e_calls, "value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
                 "ms_per_step": e_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
                 # walks into pinned memory transfer the written cells of each row (length + 1) and the lengths;
                 # k-hop trees are dense and are copied whole
@@ -483,8 +485,8 @@ def main():
                 return ctx.walk_packed(np_s, hop, app=app_id(wl), mode=mode, tp=wl.get("tp", 0.0), p=wl.get("p", 2.0),
                                        q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, packed=np_r,
                                        lengths=np_l, n=n_local)[4]
-            p_ms, p_edges = timed_host_calls(packed_call)
-            e2e = {"value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+            p_ms, p_edges, p_calls = timed_host_calls(packed_call)
+            e2e = {"ms_per_call_this_rank": p_calls, "value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
                    "ms_per_step": p_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
                    "d2h_bytes_per_step": int(4 * (p_edges / e_steps / world + 2 * n_local)),
                    "note": "host-buffer entry point skw_walk_packed with pinned memory: start vertices H2D, walk "

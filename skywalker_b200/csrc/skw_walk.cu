@@ -12,6 +12,8 @@
 // Randomness: Philox4x32-10, counter (walker id low, high, step, trial), key seed ^ TAG_WALK;
 // word x -> column (multiply-high by the degree), y -> acceptance uniform, z -> PPR stop test,
 // w -> node2vec rejection uniform.
+#include <algorithm>
+
 #include <cub/device/device_scan.cuh>
 #include <cub/iterator/transform_input_iterator.cuh>
 
@@ -703,8 +705,15 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
   const bool fits = *cells <= capacity_cells && h_packed;
   if (fits) {
     if ((rc = ensure_bytes(ctx, &ctx->stage[3], &ctx->stage_bytes[3], offs_bytes + tmp_bytes)) != SKW_OK) return rc;
-    if ((rc = ensure_bytes(ctx, &ctx->stage[4], &ctx->stage_bytes[4], sizeof(u32) * (size_t)*cells)) != SKW_OK)
-      return rc;
+    // The size of the result changes from call to call (another seed, other lengths).  When the
+    // buffer has to grow it grows by an eighth more than needed (capped by the row matrix), so that
+    // later calls do not reallocate: a free and an allocation between two calls cost milliseconds
+    // and at times far more.
+    const size_t need = sizeof(u32) * (size_t)*cells;
+    if (ctx->stage_bytes[4] < need || !ctx->stage[4]) {
+      const size_t roomy = std::min<size_t>(need + (need >> 3) + 4096, nb * prm->hop_num);
+      if ((rc = ensure_bytes(ctx, &ctx->stage[4], &ctx->stage_bytes[4], roomy)) != SKW_OK) return rc;
+    }
   }
   // the walk has completed (skw_walk_device waited for it): the lengths go home on the side stream
   // while the rows are packed
