@@ -58,7 +58,8 @@ ALG_BYTES_PER_BUILD_EDGE = 12  # offline build: 4 weight + 8 slot
 # launch, from ncu captures of the reduced PPR workload "c5s" (same kernels, scale 22, 1 M walkers;
 # summary in profiles/walk_kernels_ppr_rmat22_1Mwalkers.md).  Traffic grows in proportion to walkers
 # and steps, so roofline.traffic = this figure x the sampled edges of a full launch.
-DRAM_BYTES_PER_SAMPLED_EDGE = {"walk_records_walk_kernel": 105.2, "walk_offline_kernel": 162.9}
+DRAM_BYTES_PER_SAMPLED_EDGE = {"walk_records_ppr_kernel": 101.5, "walk_records_walk_kernel": 105.2,
+                               "walk_offline_kernel": 162.9}
 
 
 def measured_peak():
@@ -535,7 +536,8 @@ def main():
         else:
             bytes_note = "24 bytes per sampled edge"
             achieved = edges_per_step_rank * ALG_BYTES_PER_EDGE / (per_step_ms * 1e-3) / 1e9
-            kernel_name = "walk_records_walk_kernel" if use_records else "walk_offline_kernel"
+            kernel_name = (("walk_records_ppr_kernel" if wl.get("app") == "ppr" else "walk_records_walk_kernel")
+                           if use_records else "walk_offline_kernel")
         per_edge = DRAM_BYTES_PER_SAMPLED_EDGE.get(kernel_name)
         traffic = per_edge * edges_per_step_rank if per_edge else None
         build_gbs = E * ALG_BYTES_PER_BUILD_EDGE / (build_best * 1e-3) / 1e9
