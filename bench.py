@@ -531,8 +531,10 @@ def main():
             bytes_note = ("16 + 4*deg(v) bytes per walk step" if not khop else
                           "8 + 4*deg(v) per frontier vertex + 8 per sample") + ", summed over the last step's frontier"
             achieved = online_bytes / (per_step_ms * 1e-3) / 1e9 * (edges_per_step_rank / max(last_edges, 1.0))
-            kernel_name = "frontier_collect + degree-class builders + " + ("khop_hop_kernel" if khop else
-                                                                          "walk_online_step_kernel")
+            direct = (not khop) and n_local * max_deg <= 8 * E   # the library's own rule (skw_walk_device)
+            kernel_name = ("walk_online_direct_kernel" if direct else
+                           "frontier_collect + degree-class builders + " + ("khop_hop_kernel" if khop else
+                                                                            "walk_online_step_kernel"))
         else:
             bytes_note = "24 bytes per sampled edge"
             achieved = edges_per_step_rank * ALG_BYTES_PER_EDGE / (per_step_ms * 1e-3) / 1e9

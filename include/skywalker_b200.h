@@ -207,6 +207,15 @@ typedef struct skw_walk_params {
  * uniformly, no alias table is read or built and `mode` is ignored; with SKW_APP_NODE2VEC this is
  * the reference's unweighted rejection walk (src/unbiased_walk.cu:14-61). */
 #define SKW_WALK_UNBIASED 2u
+/* Online mode only: how the slot a walker draws is obtained.  BUILD_TABLES: the alias tables of all
+ * distinct frontier vertices are built at every step, as OnlineWalkShMem does
+ * (src/online_walk.cu:82-166), and the walkers draw from them.  DIRECT_SLOTS: every walker computes
+ * the one slot it draws straight from the weight list of its vertex (one warp per walker, all steps
+ * in one launch, no table memory touched) -- the same (prob, alias) bits a built table holds, so
+ * the walks are identical.  With neither flag the library picks: direct when few walkers share a
+ * vertex (n * max_degree <= 8 * E), tables otherwise.  SKW_WALK_CACHE_TABLES implies BUILD_TABLES. */
+#define SKW_WALK_BUILD_TABLES 4u
+#define SKW_WALK_DIRECT_SLOTS 8u
 
 /* Optional wider layout of the same table for offline DeepWalk / PPR.  No counterpart in the
  * reference (whose step reads xadj, prob_array, alias_array and adjncy separately,

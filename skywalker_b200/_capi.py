@@ -15,6 +15,8 @@ MODE_OFFLINE, MODE_ONLINE = 0, 1
 KHOP_TAKE_ALL = 1
 WALK_CACHE_TABLES = 1
 WALK_UNBIASED = 2
+WALK_BUILD_TABLES = 4
+WALK_DIRECT_SLOTS = 8
 KHOP_UNBIASED = 2
 INVALID_VERTEX = 0xFFFFFFFF
 

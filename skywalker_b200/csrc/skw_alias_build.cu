@@ -35,6 +35,7 @@
 #include <cstdio>
 #include <mutex>
 
+#include "skw_alias_math.cuh"
 #include "skw_ctx.h"
 
 namespace skw {
@@ -47,61 +48,6 @@ constexpr u32 kWarpSmallMax = 256;
 constexpr u32 kWarpMax = 1024;
 constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 4096: 12 bytes of list state per edge, 4 CTAs per SM
 constexpr u32 kHugeSmemMax = 16384;           // one 1024-thread CTA per SM with 192 KB of lists
-
-__device__ __forceinline__ float sane_weight(float w) {
-  return (w > 0.0f && w < CUDART_INF_F) ? w : 0.0f;
-}
-__device__ __forceinline__ int bucket_bits(u32 n) {
-  const int L = n <= 1 ? 0 : 32 - __clz((int)(n - 1));
-  return min(40, 62 - L);
-}
-__device__ __forceinline__ double pow2d(int e) {
-  return __longlong_as_double((long long)(e + 1023) << 52);
-}
-// 2^(B-1-e), e = exponent of the largest weight.
-__device__ __forceinline__ double weight_scale(float wmax, int B) {
-  const int e = (int)((__double_as_longlong((double)wmax) >> 52) & 0x7FF) - 1023;
-  return pow2d(B - 1 - e);
-}
-__device__ __forceinline__ u64 quantise(float w, double scale) {
-  return __double2ull_rz(__dmul_rn((double)w, scale));
-}
-// The same value as quantise(w, 2^s) from the bits of w (w > 0 finite or 0), without the
-// fp64 conversions: trunc(w * 2^s) = mantissa shifted by (exponent + s).
-__device__ __forceinline__ u64 quantise_bits(float w, int s) {
-  const u32 b = __float_as_uint(w);
-  const u32 ew = b >> 23;
-  const u32 mant = b & 0x7FFFFFu;
-  const u64 M = ew ? (u64)(mant | 0x800000u) : (u64)mant;
-  const int sh = s + (ew ? (int)ew - 150 : -149);
-  if (sh >= 0) return sh < 64 ? M << sh : 0;  // sh < 40 by construction
-  return sh > -64 ? M >> (-sh) : 0;
-}
-// s of quantise_bits for the largest weight wmax (> 0): B - 1 - floor(log2 wmax)
-__device__ __forceinline__ int weight_shift(float wmax, int B) {
-  const u32 b = __float_as_uint(wmax);
-  const u32 ew = b >> 23;
-  const int e = ew ? (int)ew - 127 : (31 - __clz((int)(b & 0x7FFFFFu))) - 149;
-  return B - 1 - e;
-}
-__device__ __forceinline__ float mass_to_prob_fast(u64 m, int B) {
-  // one rounding (u64 -> fp32, nearest even) then an exact power-of-two scale: the same bits as
-  // rounding the exact quotient m / 2^B once
-  return __ull2float_rn(m) * __uint_as_float((u32)(127 - B) << 23);
-}
-
-__device__ __forceinline__ double mass_factor(u32 n, int B, u64 W) {
-  return __ddiv_rn(__ull2double_rn((u64)n << B), __ull2double_rn(W));
-}
-// g(Q): cumulative mass up to cumulative quantised weight Q.
-__device__ __forceinline__ u64 cum_mass(u64 Q, u64 W, u64 nC, double K) {
-  if (Q == W) return nC;
-  const u64 g = __double2ull_rz(__dmul_rn(__ull2double_rn(Q), K));
-  return g < nC ? g : nC;
-}
-__device__ __forceinline__ float mass_to_prob(u64 m, int B) {
-  return __double2float_rn(__dmul_rn(__ull2double_rn(m), pow2d(-B)));
-}
 
 __device__ __forceinline__ int degree_class(u32 deg) {
   if (deg <= 4) return K_G4;
@@ -1053,46 +999,66 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
     int rc = ensure_bytes(ctx, &ctx->cta_scratch, &ctx->cta_scratch_bytes, slab_elems * 12ull * gmem_ctas);
     if (rc != SKW_OK) return rc;
   }
-  const int ggrid = ctx->sm_count * 8;
-#define GROUP(GSZ, KCLS)                                                                          \
-  build_group_kernel<GSZ><<<ggrid, 256, 0, st>>>(worklist, cls, KCLS, ctx->xadj, ctx->adjwgt,     \
-                                                 ctx->slots, ctx->valid, ctx->d_err);             \
-  SKW_LAUNCHED(ctx)
-  GROUP(4, K_G4);
-  GROUP(8, K_G8);
-  GROUP(16, K_G16);
-  GROUP(32, K_G32);
-#undef GROUP
+  // The classes are independent and each kernel drains its own work list through an atomic cursor,
+  // so they run side by side: the large classes (few, long-running CTAs, whose last vertices would
+  // otherwise leave most SMs idle) start first on streams of their own, the small classes fill in
+  // on the caller's stream.
+  const bool fork = !getenv("SKW_TMP_SERIAL_BUILD") && ctx->max_degree > kWarpSmallMax;
+  cudaStream_t s_w1k = st, s_c = st, s_c2 = st, s_h = st;
+  if (fork) {
+    SKW_CUDA(ctx, cudaEventRecord(ctx->bfork, st));
+    for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) SKW_CUDA(ctx, cudaStreamWaitEvent(ctx->bstream[i], ctx->bfork, 0));
+    s_h = ctx->bstream[0];
+    s_c2 = ctx->bstream[1];
+    s_c = ctx->bstream[2];
+    s_w1k = ctx->bstream[3];
+  }
+  if (slab_elems) {
+    build_cta_merge_kernel<1024, kWin><<<gmem_ctas, 1024, kWinSmem, s_h>>>(
+        worklist, cls, K_H, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid,
+        static_cast<unsigned char*>(ctx->cta_scratch), slab_elems, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->max_degree > kLargeMax) {
+    build_cta_merge_kernel<1024, 0><<<ctx->sm_count, 1024, kCta2Smem, s_c2>>>(
+        worklist, cls, K_C2, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kHugeSmemMax, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->max_degree > kWarpMax) {
+    if ((reinterpret_cast<uintptr_t>(ctx->adjwgt) & 15u) == 0) {
+      build_cta_staged_kernel<256, kLargeMax><<<ctx->sm_count * 3, 256, kCtaStagedSmem, s_c>>>(
+          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+    } else {  // a borrowed weight array that is not 16-byte aligned cannot be bulk-copied
+      build_cta_merge_kernel<256, 0><<<ctx->sm_count * 4, 256, kCtaSmem, s_c>>>(
+          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
+    }
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->max_degree > kWarpSmallMax) {
+    build_warp_merge_kernel<kWarpMax, 8><<<ctx->sm_count * 2, 256, kW1KSmem, s_w1k>>>(
+        worklist, cls, K_W1K, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
   if (ctx->max_degree > 32) {
     build_warp_merge_kernel<kWarpSmallMax, 8><<<ctx->sm_count * 8, 256, kW256Smem, st>>>(
         worklist, cls, K_W256, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
     SKW_LAUNCHED(ctx);
   }
-  if (ctx->max_degree > kWarpSmallMax) {
-    build_warp_merge_kernel<kWarpMax, 8><<<ctx->sm_count * 2, 256, kW1KSmem, st>>>(
-        worklist, cls, K_W1K, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
-    SKW_LAUNCHED(ctx);
-  }
-  if (ctx->max_degree > kWarpMax) {
-    if ((reinterpret_cast<uintptr_t>(ctx->adjwgt) & 15u) == 0) {
-      build_cta_staged_kernel<256, kLargeMax><<<ctx->sm_count * 3, 256, kCtaStagedSmem, st>>>(
-          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
-    } else {  // a borrowed weight array that is not 16-byte aligned cannot be bulk-copied
-      build_cta_merge_kernel<256, 0><<<ctx->sm_count * 4, 256, kCtaSmem, st>>>(
-          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
+  const int ggrid = ctx->sm_count * 8;
+#define GROUP(GSZ, KCLS)                                                                          \
+  build_group_kernel<GSZ><<<ggrid, 256, 0, st>>>(worklist, cls, KCLS, ctx->xadj, ctx->adjwgt,     \
+                                                 ctx->slots, ctx->valid, ctx->d_err);             \
+  SKW_LAUNCHED(ctx)
+  GROUP(32, K_G32);
+  GROUP(16, K_G16);
+  GROUP(8, K_G8);
+  GROUP(4, K_G4);
+#undef GROUP
+  if (fork) {
+    for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) {
+      SKW_CUDA(ctx, cudaEventRecord(ctx->bjoin[i], ctx->bstream[i]));
+      SKW_CUDA(ctx, cudaStreamWaitEvent(st, ctx->bjoin[i], 0));
     }
-    SKW_LAUNCHED(ctx);
-  }
-  if (ctx->max_degree > kLargeMax) {
-    build_cta_merge_kernel<1024, 0><<<ctx->sm_count, 1024, kCta2Smem, st>>>(
-        worklist, cls, K_C2, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kHugeSmemMax, ctx->d_err);
-    SKW_LAUNCHED(ctx);
-  }
-  if (slab_elems) {
-    build_cta_merge_kernel<1024, kWin><<<gmem_ctas, 1024, kWinSmem, st>>>(
-        worklist, cls, K_H, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid,
-        static_cast<unsigned char*>(ctx->cta_scratch), slab_elems, ctx->d_err);
-    SKW_LAUNCHED(ctx);
   }
   return SKW_OK;
 }

@@ -212,6 +212,11 @@ int skw_ctx_create(int device, skw_ctx** out) {
   CK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
   CK(cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
   ctx->stream = ctx->own_stream;
+  for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) {
+    CK(cudaStreamCreateWithFlags(&ctx->bstream[i], cudaStreamNonBlocking));
+    CK(cudaEventCreateWithFlags(&ctx->bjoin[i], cudaEventDisableTiming));
+  }
+  CK(cudaEventCreateWithFlags(&ctx->bfork, cudaEventDisableTiming));
   CK(cudaEventCreate(&ctx->ev0));
   CK(cudaEventCreate(&ctx->ev1));
   CK(cudaMalloc(&ctx->d_err, 4 * sizeof(uint32_t)));
@@ -246,6 +251,11 @@ void skw_ctx_destroy(skw_ctx* ctx) {
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
+  for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) {
+    if (ctx->bstream[i]) cudaStreamDestroy(ctx->bstream[i]);
+    if (ctx->bjoin[i]) cudaEventDestroy(ctx->bjoin[i]);
+  }
+  if (ctx->bfork) cudaEventDestroy(ctx->bfork);
   delete ctx;
 }
 

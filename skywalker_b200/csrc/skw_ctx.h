@@ -27,6 +27,11 @@ struct skw_ctx {
   cudaStream_t stream = nullptr;
   cudaStream_t side_stream = nullptr;  // result copies that overlap kernels of `stream`
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // the degree-class builders of one build run side by side: classes 257+ on streams of their own,
+  // forked from and joined back into `stream` by events
+  static constexpr int kBuilderStreams = 4;
+  cudaStream_t bstream[kBuilderStreams] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t bfork = nullptr, bjoin[kBuilderStreams] = {nullptr, nullptr, nullptr, nullptr};
   std::string err;
   uint64_t launches = 0;
 

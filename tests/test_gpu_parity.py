@@ -155,8 +155,10 @@ def test_config1_deepwalk_bit_exact(ctx, oracle, rmat16):
 
 @pytest.mark.parametrize("app,kw", [(APP_DEEPWALK, {}), (APP_PPR, {"tp": 0.15}), (APP_NODE2VEC, {"p": 2.0, "q": 0.5}),
                                     (APP_NODE2VEC, {"p": 0.25, "q": 4.0})])
-@pytest.mark.parametrize("mode", [MODE_OFFLINE, MODE_ONLINE])
-def test_walks_bit_exact(ctx, oracle, plaw, app, kw, mode):
+@pytest.mark.parametrize("mode,flags", [(MODE_OFFLINE, 0), (MODE_ONLINE, 0), (MODE_ONLINE, 4), (MODE_ONLINE, 8)])
+def test_walks_bit_exact(ctx, oracle, plaw, app, kw, mode, flags):
+    # online: flags 4 (WALK_BUILD_TABLES) builds the tables of the frontier at every step, 8
+    # (WALK_DIRECT_SLOTS) evaluates every drawn slot straight from the weights, 0 lets the library pick
     g = plaw
     _upload(ctx, g)
     table = oracle.alias_build(g.xadj, g.adjwgt)
@@ -164,7 +166,7 @@ def test_walks_bit_exact(ctx, oracle, plaw, app, kw, mode):
         ctx.alias_build_offline()
     starts = oracle.gen_starts(3000, g.V, 7)
     hop = 41 if app != APP_PPR else 101
-    paths, lens, ms, edges = ctx.walk(starts, hop, app=app, mode=mode, seed=99, walker_base=1000, **kw)
+    paths, lens, ms, edges = ctx.walk(starts, hop, app=app, mode=mode, seed=99, walker_base=1000, flags=flags, **kw)
     opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, hop, app=app, seed=99, walker_base=1000,
                                 online=False, **kw)
     _cmp_walks(paths, lens, opaths, olens)
@@ -595,3 +597,29 @@ def test_packed_host_result_matches_rows(ctx, oracle, plaw, pinned):
     out3, lens3, cells3, _, _ = ctx.walk_packed(starts[:100], 11, seed=3)
     p3, l3 = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts[:100], 11, seed=3)
     assert np.array_equal(out3[:cells3], np.concatenate([p3[w, :l3[w] + 1] for w in range(100)]))
+
+
+def test_online_direct_slots_every_degree_class(ctx, oracle):
+    """The online walk computes the slot it draws without a table: one step from every list of the
+    degree-class zoo, enough walkers per list to draw most columns, against the oracle's built tables."""
+    rng = np.random.default_rng(5)
+    lists = []
+    for n in [1, 2, 3, 4, 5, 31, 32, 33, 127, 128, 129, 255, 256, 257, 1000, 4097, 20000, 70000]:
+        lists.append(rng.uniform(1, 10, n).astype(np.float32))
+    lists.append(np.asarray([0.5] * 35 + [2.0] * 5, np.float32))
+    lists.append(np.full(130, 3.0, np.float32))                        # uniform: every slot is its own bucket
+    lists.append(np.asarray([1e-3] * 300 + [1000.0], np.float32))      # one dominant weight at the end
+    lists.append(np.asarray([1000.0] + [1e-3] * 300, np.float32))      # ... and at the start
+    lists.append(np.zeros(100, np.float32))                            # no usable weight: the walk ends
+    lists.append(np.asarray([0, 1, 2, 0, 5] * 40, np.float32))         # zeros inside
+    lists.append(np.asarray([np.nan, -1, np.inf, 2, 3], np.float32))
+    lists.append(rng.uniform(0, 1, 3000).astype(np.float32) ** 8)      # skewed, many tiny
+    xadj, adj, w = _star_graph(lists)
+    ctx.upload(xadj, adj, w)
+    starts = np.concatenate([np.full(min(4 * len(l), 6000), i, np.uint32) for i, l in enumerate(lists)])
+    paths, lens, _, edges = ctx.walk(starts, 3, mode=MODE_ONLINE, seed=31, flags=8)
+    opaths, olens = oracle.walk(xadj, adj, w, None, starts, 3, online=True, seed=31)
+    _cmp_walks(paths, lens, opaths, olens)
+    assert edges == int(olens.sum())
+    built, blens, _, _ = ctx.walk(starts, 3, mode=MODE_ONLINE, seed=31, flags=4)
+    _cmp_walks(built, blens, opaths, olens)
