@@ -1003,7 +1003,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   // so they run side by side: the large classes (few, long-running CTAs, whose last vertices would
   // otherwise leave most SMs idle) start first on streams of their own, the small classes fill in
   // on the caller's stream.
-  const bool fork = !getenv("SKW_TMP_SERIAL_BUILD") && ctx->max_degree > kWarpSmallMax;
+  const bool fork = ctx->max_degree > kWarpSmallMax;
   cudaStream_t s_w1k = st, s_c = st, s_c2 = st, s_h = st;
   if (fork) {
     SKW_CUDA(ctx, cudaEventRecord(ctx->bfork, st));
