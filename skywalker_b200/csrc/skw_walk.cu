@@ -546,6 +546,7 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
   bool have = w < a.n;
   u32 off = 0, deg = 0, step = 0;
   u32* row = nullptr;
+  Rand4 r{0, 0, 0, 0};  // random words of the walker's current step
   auto begin = [&]() {
     const u32 cur = __ldg(a.starts + w);
     row = a.paths + w * a.hop_num;
@@ -563,23 +564,24 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
       off = 0;
       deg = 0;
     }
+    r = philox_tagged(a.seed, TAG_WALK, a.walker_base + w * a.walker_stride, 0, 0);
   };
   if (have) begin();
   while (have) {
     bool go = step + 1 < a.hop_num && deg != 0;
-    Rand4 r{0, 0, 0, 0};
-    if (go) {
-      r = philox_tagged(a.seed, TAG_WALK, a.walker_base + w * a.walker_stride, step, 0);
-      if (APP == SKW_APP_PPR && u01(r.z) < a.tp) go = false;
-    }
+    if (APP == SKW_APP_PPR && go && u01(r.z) < a.tp) go = false;
     if (go) {
       u32 rw[8];
       load_record(a.rec + (u64)off + __umulhi(r.x, deg), rw);
+      // the next step's random words do not depend on the record: computing them here overlaps the
+      // load's latency (what a walk is made of when few walkers are in flight)
+      const Rand4 rn = philox_tagged(a.seed, TAG_WALK, a.walker_base + w * a.walker_stride, step + 1, 0);
       const bool keep = u01(r.y) < __uint_as_float(rw[0]);
       ++step;
       row[step] = keep ? rw[1] : rw[4];
       off = keep ? rw[2] : rw[5];
       deg = keep ? rw[3] : rw[6];
+      r = rn;
     } else {
       a.lengths[w] = step;
       edges += step;

@@ -623,3 +623,24 @@ def test_online_direct_slots_every_degree_class(ctx, oracle):
     assert edges == int(olens.sum())
     built, blens, _, _ = ctx.walk(starts, 3, mode=MODE_ONLINE, seed=31, flags=4)
     _cmp_walks(built, blens, opaths, olens)
+
+
+def test_ppr_records_chunk_edges_and_long_rows(ctx, oracle, rmat12):
+    """The chunked PPR kernel: walker counts around its chunk size, paths longer than its staging
+    rows, and rows too long for it (hop_num > 65535 takes the lane-per-walker kernel)."""
+    g = rmat12
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    ctx.walk_records_build()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    for n in (1, 63, 64, 65, 511, 513):
+        starts = oracle.gen_starts(n, g.V, 100 + n)
+        paths, lens, _, edges = ctx.walk(starts, 40, app=APP_PPR, tp=0.02, seed=n, walker_base=7)   # long walks
+        opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 40, app=APP_PPR, tp=0.02, seed=n,
+                                    walker_base=7)
+        _cmp_walks(paths, lens, opaths, olens)
+        assert edges == int(olens.sum())
+    starts = oracle.gen_starts(48, g.V, 3)
+    paths, lens, _, _ = ctx.walk(starts, 70000, app=APP_PPR, tp=0.3, seed=2)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 70000, app=APP_PPR, tp=0.3, seed=2)
+    _cmp_walks(paths, lens, opaths, olens)
