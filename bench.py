@@ -202,15 +202,18 @@ def cpu_leg(ctx, wl, threads, want_seconds=12.0):
 
 def online_algorithmic_bytes(ctx, wl, result, lengths):
     """Algorithmic bytes of one online step from the realised frontier: 16 + 4*deg(v) per walk step,
-    8 + 4*deg(v) per frontier vertex plus 8 per sample for k-hop."""
+    8 + 4*deg(v) per DISTINCT frontier vertex of each hop (a vertex met several times in one hop is
+    built once) plus 8 per sample for k-hop."""
     xadj = ctx.download(weights=False)[0].astype(np.int64)
     deg = np.diff(xadj)
     if wl["kind"] == "khop":
         data, sl = result, lengths
         f1 = wl["fanout"][0]
-        parents = np.concatenate([data[:, 0], data[:, 1:1 + f1].reshape(-1)])
-        parents = parents[parents != 0xFFFFFFFF]
-        return float((8 + 4 * deg[parents]).sum() + 8 * int(sl.sum()))
+        total = 8.0 * int(sl.sum())
+        for parents in (data[:, 0], data[:, 1:1 + f1].reshape(-1)):
+            parents = np.unique(parents[parents != 0xFFFFFFFF])
+            total += float((8 + 4 * deg[parents]).sum())
+        return total
     paths, lens = result, lengths
     hop = paths.shape[1]
     live = np.arange(hop)[None, :] < lens[:, None]
@@ -529,7 +532,7 @@ def main():
         edges_per_step_rank = edges_all / args.steps / world
         if online:
             bytes_note = ("16 + 4*deg(v) bytes per walk step" if not khop else
-                          "8 + 4*deg(v) per frontier vertex + 8 per sample") + ", summed over the last step's frontier"
+                          "8 + 4*deg(v) per distinct frontier vertex of a hop + 8 per sample") + ", summed over the last step's frontier"
             achieved = online_bytes / (per_step_ms * 1e-3) / 1e9 * (edges_per_step_rank / max(last_edges, 1.0))
             direct = (not khop) and n_local * max_deg <= 8 * E   # the library's own rule (skw_walk_device)
             kernel_name = ("walk_online_direct_kernel" if direct else
