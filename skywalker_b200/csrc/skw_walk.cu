@@ -609,8 +609,9 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
 // against 1.17 ms for the lane-owns-a-stride kernel; 0.67 ms with the path stores left out, i.e.
 // the 8 M isolated row prefixes (one or two 32-byte sectors each, rows hop_num * 4 bytes apart)
 // cost DRAM about as much as the record reads, whether they are written step by step or together
-// at the end, with default or streaming stores.  Chunks of 64 walkers with 8 warps per CTA were
-// the best of {64, 128, 256} x {4, 8, 16}.
+// at the end, with default or streaming stores; padding the prefixes to whole 32-byte sectors
+// (so that no partly written sector leaves L2) made the launch 12 % slower.  Chunks of 64 walkers
+// with 8 warps per CTA were the best of {64, 128, 256} x {4, 8, 16}.
 constexpr u32 kChunk = 64, kStage = 8, kStagePitch = kStage + 1;
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) walk_records_ppr_kernel(const RecordWalkArgs a) {
