@@ -274,9 +274,15 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
   // sweep 1: masses up to p; per-lane sums of the deficits before p and of the excesses up to and
   // including p
   u64 carryQ = 0, accD = 0, accX = 0, Mp = 0;
+  u64 saveQ = 0, saveD = 0, saveX = 0;  // the same sums at the start of p's tile
   u64 m[kDirectEpt];
   for (u32 t = 0; t <= tp; ++t) {
     const u32 base = t * kDirectTile;
+    if (t == tp) {
+      saveQ = carryQ;
+      saveD = accD;
+      saveX = accX;
+    }
     tile_masses(w, n, base, lane, L, carryQ, m);
 #pragma unroll
     for (u32 k = 0; k < kDirectEpt; ++k) {
@@ -295,9 +301,16 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
     const u64 T = warp_sum_u64(accD);
     out.prob = mass_to_prob_fast(Mp, L.B);
     out.alias = p;
+    // if the larges before p do not reach T the donor lies after p: resume at p's tile
     u64 cq = 0, carryX = 0;
+    u32 start = 0;
+    if (warp_sum_u64(accX) < T) {
+      start = tp * kDirectTile;
+      cq = saveQ;
+      carryX = warp_sum_u64(saveX);
+    }
     bool found = false;
-    for (u32 base = 0; base < n && !found; base += kDirectTile) {
+    for (u32 base = start; base < n && !found; base += kDirectTile) {
       tile_masses(w, n, base, lane, L, cq, m);
       u64 xs = 0;
 #pragma unroll
@@ -352,8 +365,15 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
   out.prob = 1.0f;
   out.alias = p;
   if (next_large == kNoVertex) return out;  // the last large: no small can be left for it (D_total = X_total)
+  // if the smalls before p do not exceed T the crossing lies after p: resume at p's tile
   u64 cq = 0, carryD = 0;
-  for (u32 base = 0; base < n; base += kDirectTile) {
+  u32 start = 0;
+  if (warp_sum_u64(accD) <= T) {
+    start = tp * kDirectTile;
+    cq = saveQ;
+    carryD = warp_sum_u64(saveD);
+  }
+  for (u32 base = start; base < n; base += kDirectTile) {
     tile_masses(w, n, base, lane, L, cq, m);
     u64 ds = 0;
 #pragma unroll
@@ -387,7 +407,7 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
 
 // One warp per walker, all steps in one launch.  Same draws and rules as walk_step.
 template <int APP>
-__global__ void __launch_bounds__(256) walk_online_direct_kernel(const WalkArgs a, const float* __restrict__ wgt) {
+__global__ void __launch_bounds__(256, 4) walk_online_direct_kernel(const WalkArgs a, const float* __restrict__ wgt) {
   const u32 lane = threadIdx.x & 31;
   const u64 nwarps = ((u64)gridDim.x * blockDim.x) >> 5;
   u64 edges = 0;
