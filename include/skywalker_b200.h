@@ -255,10 +255,11 @@ int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts,
  * walks back to back in walker order, walk w holding lengths[w] + 1 vertices (its start first)
  * from cell sum_{u<w}(lengths[u] + 1) on -- the same values the row layout holds in
  * paths[w * hop_num + 0 .. lengths[w]].  *cells = cells the result needs (= sampled edges + n).
- * When capacity_cells is smaller (or h_packed is NULL) the call fills h_lengths and *cells, writes
- * nothing to h_packed and returns SKW_ERR_ARG; the same call with a buffer of *cells cells then
- * returns the same walks.  Rows are packed on the device and leave in one contiguous copy, so
- * only cells that hold a result cross the bus (fastest with pinned h_packed / h_lengths). */
+ * When capacity_cells is smaller (or h_packed is NULL) the call fills h_lengths and *cells, leaves
+ * h_packed unspecified (never written past capacity_cells) and returns SKW_ERR_ARG; the same call
+ * with a buffer of *cells cells then returns the same walks.  Rows are packed on the device and
+ * leave in contiguous copies, so only cells that hold a result cross the bus; large batches run as
+ * a pipeline of slices whose copies overlap the next slice's walk (fastest with pinned buffers). */
 int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
                     uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_lengths, uint64_t* cells,
                     float* ms, uint64_t* sampled_edges);

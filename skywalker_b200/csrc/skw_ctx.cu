@@ -219,9 +219,13 @@ int skw_ctx_create(int device, skw_ctx** out) {
   CK(cudaEventCreateWithFlags(&ctx->bfork, cudaEventDisableTiming));
   CK(cudaEventCreate(&ctx->ev0));
   CK(cudaEventCreate(&ctx->ev1));
-  CK(cudaMalloc(&ctx->d_err, 4 * sizeof(uint32_t)));
-  CK(cudaMemset(ctx->d_err, 0, 4 * sizeof(uint32_t)));
-  CK(cudaMallocHost(&ctx->h_err, 4 * sizeof(uint32_t)));
+  // two error records of four words: [0..4) reset and checked by every call, [4..8) owned by the
+  // packing pipeline of skw_walk_packed, which spans several such calls
+  CK(cudaMalloc(&ctx->d_err, 8 * sizeof(uint32_t)));
+  CK(cudaMemset(ctx->d_err, 0, 8 * sizeof(uint32_t)));
+  CK(cudaMallocHost(&ctx->h_err, 8 * sizeof(uint32_t)));
+  CK(cudaEventCreateWithFlags(&ctx->pk_ready, cudaEventDisableTiming));
+  for (int i = 0; i < 2; ++i) CK(cudaEventCreateWithFlags(&ctx->pk_done[i], cudaEventDisableTiming));
   CK(cudaMalloc(&ctx->d_sum, 2 * sizeof(uint64_t)));
   CK(cudaMemset(ctx->d_sum, 0, 2 * sizeof(uint64_t)));
   CK(cudaMallocHost(&ctx->h_sum, 2 * sizeof(uint64_t)));
@@ -256,6 +260,9 @@ void skw_ctx_destroy(skw_ctx* ctx) {
     if (ctx->bjoin[i]) cudaEventDestroy(ctx->bjoin[i]);
   }
   if (ctx->bfork) cudaEventDestroy(ctx->bfork);
+  if (ctx->pk_ready) cudaEventDestroy(ctx->pk_ready);
+  for (int i = 0; i < 2; ++i)
+    if (ctx->pk_done[i]) cudaEventDestroy(ctx->pk_done[i]);
   delete ctx;
 }
 

@@ -26,6 +26,7 @@ struct skw_ctx {
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   cudaStream_t side_stream = nullptr;  // result copies that overlap kernels of `stream`
+  cudaEvent_t pk_ready = nullptr, pk_done[2] = {nullptr, nullptr};  // skw_walk_packed: packed -> copied
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // the degree-class builders of one build run side by side: classes 257+ on streams of their own,
   // forked from and joined back into `stream` by events

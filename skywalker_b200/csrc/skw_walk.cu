@@ -1095,68 +1095,109 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
   if (!ctx || !prm) return SKW_ERR_ARG;
   if (!cells) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: cells must not be null");
   *cells = 0;
+  if (ms) *ms = 0;
+  if (sampled_edges) *sampled_edges = 0;
   if (n && (!h_starts || !h_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: null buffer");
   if (prm->hop_num < 1) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: hop_num must be >= 1");
+  if (!n) return SKW_OK;
   DeviceGuard g(ctx->device);
   int rc;
-  cudaStream_t st = ctx->stream;
-  const size_t nb = sizeof(uint32_t) * (size_t)n;
-  if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], nb)) != SKW_OK) return rc;
-  if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], nb * prm->hop_num)) != SKW_OK) return rc;
-  if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], nb)) != SKW_OK) return rc;
-  if (n) SKW_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0], h_starts, nb, cudaMemcpyHostToDevice, st));
-  float walk_ms = 0;
-  uint64_t edges = 0;
-  u32* d_rows = static_cast<u32*>(ctx->stage[1]);
-  u32* d_len = static_cast<u32*>(ctx->stage[2]);
-  rc = skw_walk_device(ctx, prm, static_cast<uint32_t*>(ctx->stage[0]), n, d_rows, d_len, &walk_ms, &edges);
-  if (rc != SKW_OK) return rc;
-  if (ms) *ms = walk_ms;
-  if (sampled_edges) *sampled_edges = edges;
-  *cells = edges + n;  // every walk holds its start plus one vertex per sampled edge
-  if (!n) return SKW_OK;
-  // row offsets: exclusive sum of (length + 1) in walker order
-  cub::TransformInputIterator<u64, CellsOfRow, const u32*> row_cells(d_len, CellsOfRow());
+  cudaStream_t st = ctx->stream, side = ctx->side_stream;
+  // Large batches run as a pipeline of up to four slices: while slice c walks on the context's
+  // stream, the packed result of slice c - 1 goes home on the side stream (and the start vertices of
+  // slice c come in: the bus carries both directions at once).  Walker ids, hence walks, do not
+  // depend on the slicing.
+  const uint64_t kSliceMin = 1u << 19;
+  const uint32_t slices = n >= 4 * kSliceMin ? 4 : (n >= 2 * kSliceMin ? 2 : 1);
+  const uint64_t per = (n + slices - 1) / slices;
+  const uint64_t stride = prm->walker_stride ? prm->walker_stride : 1;
+  const size_t offs_bytes = (sizeof(u64) * (size_t)per + 255) & ~(size_t)255;
   size_t tmp_bytes = 0;
-  SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, row_cells, (u64*)nullptr, (long long)n, st));
-  const size_t offs_bytes = (sizeof(u64) * (size_t)n + 255) & ~(size_t)255;
-  const bool fits = *cells <= capacity_cells && h_packed;
-  if (fits) {
-    if ((rc = ensure_bytes(ctx, &ctx->stage[3], &ctx->stage_bytes[3], offs_bytes + tmp_bytes)) != SKW_OK) return rc;
-    // The size of the result changes from call to call (another seed, other lengths).  When the
-    // buffer has to grow it grows by an eighth more than needed (capped by the row matrix), so that
-    // later calls do not reallocate: a free and an allocation between two calls cost milliseconds
-    // and at times far more.
-    const size_t need = sizeof(u32) * (size_t)*cells;
-    if (ctx->stage_bytes[4] < need || !ctx->stage[4]) {
-      const size_t roomy = std::min<size_t>(need + (need >> 3) + 4096, nb * prm->hop_num);
-      if ((rc = ensure_bytes(ctx, &ctx->stage[4], &ctx->stage_bytes[4], roomy)) != SKW_OK) return rc;
-    }
+  {
+    cub::TransformInputIterator<u64, CellsOfRow, const u32*> probe(static_cast<const u32*>(nullptr), CellsOfRow());
+    SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, probe, (u64*)nullptr, (long long)per, st));
   }
-  // the walk has completed (skw_walk_device waited for it): the lengths go home on the side stream
-  // while the rows are packed
-  SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths, d_len, nb, cudaMemcpyDeviceToHost, ctx->side_stream));
-  if (!fits) {
-    SKW_CUDA(ctx, cudaStreamSynchronize(ctx->side_stream));
-    return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: the result needs %llu cells, the buffer holds %llu",
-                (unsigned long long)*cells, (unsigned long long)capacity_cells);
-  }
+  if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], sizeof(u32) * (size_t)n)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], sizeof(u32) * (size_t)per * prm->hop_num)) != SKW_OK)
+    return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], sizeof(u32) * (size_t)n)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[3], &ctx->stage_bytes[3], offs_bytes + tmp_bytes)) != SKW_OK) return rc;
+  u32* d_starts = static_cast<u32*>(ctx->stage[0]);
+  u32* d_rows = static_cast<u32*>(ctx->stage[1]);  // one slice of rows at a time
+  u32* d_len = static_cast<u32*>(ctx->stage[2]);
   u64* d_offs = static_cast<u64*>(ctx->stage[3]);
-  u32* d_packed = static_cast<u32*>(ctx->stage[4]);
-  SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(static_cast<char*>(ctx->stage[3]) + offs_bytes, tmp_bytes, row_cells,
-                                              d_offs, (long long)n, st));
-  SKW_LAUNCHED(ctx);
-  if ((rc = err_reset(ctx)) != SKW_OK) return rc;
-  // Packed on the device, then one contiguous copy: measured on B200 with 8 M PPR walks, 4.9 ms per
-  // call against 9.9 ms when the pack kernel wrote the pinned host buffer itself (its 4-byte
-  // stores per row do not merge into full-size bus writes).
-  pack_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(d_rows, d_packed, d_len, d_offs, n, prm->hop_num, *cells,
-                                                      ctx->d_err);
-  SKW_LAUNCHED(ctx);
-  SKW_CUDA(ctx, cudaMemcpyAsync(h_packed, d_packed, sizeof(u32) * (size_t)*cells, cudaMemcpyDeviceToHost, st));
-  rc = err_check(ctx, "skw_walk_packed");
-  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->side_stream));
-  if (rc != SKW_OK) return rc;
+  u32* pack_err = ctx->d_err + 4;
+  SKW_CUDA(ctx, cudaMemsetAsync(pack_err, 0, 4 * sizeof(u32), st));
+  float total_ms = 0;
+  uint64_t total_edges = 0, total_cells = 0;
+  bool fits = h_packed != nullptr;
+  bool copied[2] = {false, false};  // a copy out of packing buffer b is or was in flight
+  for (uint32_t c = 0; c < slices; ++c) {
+    const uint64_t base = (uint64_t)c * per;
+    if (base >= n) break;
+    const uint64_t nc = std::min<uint64_t>(per, n - base);
+    SKW_CUDA(ctx, cudaMemcpyAsync(d_starts + base, h_starts + base, sizeof(u32) * (size_t)nc, cudaMemcpyHostToDevice, st));
+    skw_walk_params p = *prm;
+    p.walker_base = prm->walker_base + base * stride;
+    float slice_ms = 0;
+    uint64_t slice_edges = 0;
+    rc = skw_walk_device(ctx, &p, d_starts + base, nc, d_rows, d_len + base, &slice_ms, &slice_edges);  // waits for it
+    if (rc != SKW_OK) {
+      cudaStreamSynchronize(side);
+      return rc;
+    }
+    total_ms += slice_ms;
+    total_edges += slice_edges;
+    const uint64_t slice_cells = slice_edges + nc;  // every walk holds its start plus one vertex per sampled edge
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths + base, d_len + base, sizeof(u32) * (size_t)nc, cudaMemcpyDeviceToHost, side));
+    if (fits && total_cells + slice_cells > capacity_cells) fits = false;  // keep walking: the caller gets the size
+    if (fits) {
+      const int b = (int)(c & 1);
+      if (copied[b]) SKW_CUDA(ctx, cudaEventSynchronize(ctx->pk_done[b]));  // the buffer may be reallocated below
+      // The size of a result changes from call to call (another seed, other lengths).  When a buffer
+      // has to grow it grows by an eighth more than needed, so that later calls do not reallocate: a
+      // free and an allocation between two calls cost milliseconds and at times far more.
+      const size_t need = sizeof(u32) * (size_t)slice_cells;
+      if (ctx->stage_bytes[4 + b] < need || !ctx->stage[4 + b]) {
+        const size_t roomy = std::min<size_t>(need + (need >> 3) + 4096, sizeof(u32) * (size_t)nc * prm->hop_num);
+        if ((rc = ensure_bytes(ctx, &ctx->stage[4 + b], &ctx->stage_bytes[4 + b], roomy)) != SKW_OK) {
+          cudaStreamSynchronize(side);
+          return rc;
+        }
+      }
+      u32* d_packed = static_cast<u32*>(ctx->stage[4 + b]);
+      // row offsets: exclusive sum of (length + 1) in walker order
+      cub::TransformInputIterator<u64, CellsOfRow, const u32*> row_cells(d_len + base, CellsOfRow());
+      size_t tb = tmp_bytes;
+      SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(reinterpret_cast<char*>(d_offs) + offs_bytes, tb, row_cells, d_offs,
+                                                  (long long)nc, st));
+      SKW_LAUNCHED(ctx);
+      // Packed on the device, then one contiguous copy per slice: measured on B200 with 8 M PPR walks,
+      // half the time of a pack kernel that writes the pinned host buffer itself (its 4-byte stores
+      // per row do not merge into full-size bus writes).
+      pack_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(d_rows, d_packed, d_len + base, d_offs, nc, prm->hop_num,
+                                                          slice_cells, pack_err);
+      SKW_LAUNCHED(ctx);
+      SKW_CUDA(ctx, cudaEventRecord(ctx->pk_ready, st));
+      SKW_CUDA(ctx, cudaStreamWaitEvent(side, ctx->pk_ready, 0));
+      SKW_CUDA(ctx, cudaMemcpyAsync(h_packed + total_cells, d_packed, need, cudaMemcpyDeviceToHost, side));
+      SKW_CUDA(ctx, cudaEventRecord(ctx->pk_done[b], side));
+      copied[b] = true;
+    }
+    total_cells += slice_cells;
+  }
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_err + 4, pack_err, 4 * sizeof(u32), cudaMemcpyDeviceToHost, st));
+  SKW_CUDA(ctx, cudaStreamSynchronize(st));
+  SKW_CUDA(ctx, cudaStreamSynchronize(side));
+  *cells = total_cells;
+  if (ms) *ms = total_ms;
+  if (sampled_edges) *sampled_edges = total_edges;
+  if (ctx->h_err[4] != DEV_OK)
+    return fail(ctx, SKW_ERR_DEVICE, "skw_walk_packed: device error %u while packing, detail %u %u %u", ctx->h_err[4],
+                ctx->h_err[5], ctx->h_err[6], ctx->h_err[7]);
+  if (!fits)
+    return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: the result needs %llu cells, the buffer holds %llu",
+                (unsigned long long)total_cells, (unsigned long long)(h_packed ? capacity_cells : 0));
   return SKW_OK;
 }
 

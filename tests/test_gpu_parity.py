@@ -644,3 +644,29 @@ def test_ppr_records_chunk_edges_and_long_rows(ctx, oracle, rmat12):
     paths, lens, _, _ = ctx.walk(starts, 70000, app=APP_PPR, tp=0.3, seed=2)
     opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 70000, app=APP_PPR, tp=0.3, seed=2)
     _cmp_walks(paths, lens, opaths, olens)
+
+
+def test_packed_result_sliced_pipeline(ctx, oracle, rmat16):
+    """Batches of a million walkers and more leave the GPU slice by slice; the packed result and the
+    lengths are those of one big call, whatever the slicing."""
+    from skywalker_b200.api import SkwError
+    g = rmat16
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    for n in ((1 << 20) + 12345, (1 << 21) + 77):          # two slices, four slices
+        starts = oracle.gen_starts(n, g.V, 5)
+        opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 21, app=APP_PPR, tp=0.3, seed=8,
+                                    walker_base=11)
+        live = np.arange(21)[None, :] <= olens[:, None]
+        want = opaths[live]                                  # row-major: walks back to back
+        out, lens, cells, ms, edges = ctx.walk_packed(starts, 21, app=APP_PPR, tp=0.3, seed=8, walker_base=11)
+        assert cells == len(want) and edges == int(olens.sum()) and ms > 0
+        assert np.array_equal(lens, olens)
+        assert np.array_equal(out[:cells], want)
+        # too small by one cell: the overflow shows up in the last slice; lengths and size still come back
+        small = np.zeros(cells - 1, np.uint32)
+        lens2 = np.zeros(n, np.uint32)
+        with pytest.raises(SkwError) as e:
+            ctx.walk_packed(starts, 21, app=APP_PPR, tp=0.3, seed=8, walker_base=11, packed=small, lengths=lens2)
+        assert str(cells) in str(e.value) and np.array_equal(lens2, olens)
