@@ -507,16 +507,23 @@ def main():
                            "back to back into the pinned result buffer, lengths D2H",
                    "row_layout": rows}
 
-    # NCCL gather of the per-unit lengths to rank 0 (results gather; outside the timed region)
-    gather_ms = None
+    # NCCL gather of the results to rank 0 (outside the timed region): the per-unit lengths, and the
+    # result arrays themselves when the shards are equal and fit beside the graph on rank 0
+    gather_ms, gather_note = None, None
     if dist is not None:
         bufs = [torch.empty_like(lengths) for _ in range(world)] if rank == 0 else None
         dist.gather(lengths, bufs, dst=0)       # first collective sets NCCL up
         torch.cuda.synchronize()
+        whole = wl["units"] % world == 0 and result.numel() * 4 * world <= (16 << 30)
+        rbufs = [torch.empty_like(result) for _ in range(world)] if (rank == 0 and whole) else None
         t0 = time.perf_counter()
         dist.gather(lengths, bufs, dst=0)
+        if whole:
+            dist.gather(result, rbufs, dst=0)
         torch.cuda.synchronize()
         gather_ms = (time.perf_counter() - t0) * 1e3
+        gather_note = ("lengths and result arrays (%d MB per rank)" % (result.numel() * 4 >> 20)) if whole else "lengths"
+        del rbufs
 
     # the ceiling the step kernels run against: dependent random 32-byte accesses per second, probed
     # live on this GPU (footprint 16 GiB, far beyond L2)
@@ -581,7 +588,7 @@ def main():
                                  "probe access, not the byte fraction, says how close the step kernel is to the "
                                  "hardware"},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "result_gather_ms": gather_ms,
+            "result_gather_ms": gather_ms, "result_gather": gather_note,
         }
         print(json.dumps(out))
     if dist is not None:
