@@ -18,7 +18,7 @@ OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(PKG, "libskywalker_b200.so")
 CLI = os.path.join(PKG, "skywalker")
 
-CU_SOURCES = ["skw_ctx.cu", "skw_alias_build.cu", "skw_walk.cu", "skw_khop.cu", "skw_gen.cu"]
+CU_SOURCES = ["skw_ctx.cu", "skw_alias_build.cu", "skw_walk.cu", "skw_walk_direct.cu", "skw_khop.cu", "skw_gen.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
               "--expt-relaxed-constexpr"]
