@@ -45,6 +45,9 @@ def _newer(target, deps):
 
 def _headers():
     hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    cli = os.path.join(CSRC, "cli")
+    if os.path.isdir(cli):
+        hs += [os.path.join(cli, f) for f in os.listdir(cli) if f.endswith(".h")]
     hs.append(os.path.join(ROOT, "include", "skywalker_b200.h"))
     return hs
 

@@ -14,13 +14,11 @@
 // --d is honoured when given explicitly together with --deepwalk / --ppr / --node2vec (the
 // reference overrides it with 100).
 #include <algorithm>
-#include <condition_variable>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <map>
-#include <mutex>
 #include <string>
 #include <thread>
 #include <vector>
@@ -31,6 +29,7 @@
 #endif
 
 #include "skywalker_b200.h"
+#include "rendezvous.h"
 
 namespace {
 
@@ -179,40 +178,6 @@ struct DevResult {
   uint64_t sampled = 0;
   int rc = 0;
   std::string err;
-};
-
-// Host-side agreement of the device threads before a collective: a thread that failed earlier must
-// never leave its peers waiting inside an NCCL kernel, so each thread reports its status here and
-// enters the collective only when every thread is present and healthy.
-struct Rendezvous {
-  std::mutex m;
-  std::condition_variable cv;
-  int ndev = 1, arrived = 0, gone = 0;
-  uint64_t gen = 0;
-  bool ok = true, verdict = true;
-  void release() {  // caller holds m
-    verdict = ok && gone == 0;
-    arrived = 0;
-    ok = true;
-    ++gen;
-    cv.notify_all();
-  }
-  bool agree(bool mine) {
-    std::unique_lock<std::mutex> l(m);
-    ok = ok && mine;
-    const uint64_t g = gen;
-    if (++arrived + gone >= ndev) {
-      release();
-      return verdict;
-    }
-    cv.wait(l, [&] { return gen != g; });
-    return verdict;
-  }
-  void leave() {  // a thread that ends (for whatever reason) takes part in no later agreement
-    std::lock_guard<std::mutex> l(m);
-    ++gone;
-    if (arrived && arrived + gone >= ndev) release();
-  }
 };
 
 struct Shared {
