@@ -106,6 +106,10 @@ def test_alias_every_degree_class_and_edge_cases(ctx, oracle):
     lists.append(np.asarray([np.nan, -1, np.inf, 2, 3], np.float32))   # unusable entries
     lists.append((2.0 ** -np.arange(20)).astype(np.float32))           # wide range
     lists.append(rng.uniform(0, 1, 3000).astype(np.float32) ** 8)      # skewed, many tiny
+    lists.append(np.asarray([1e-40, 2e-40, 3e-41, 0, 1e-45], np.float32))           # denormals only
+    lists.append(np.full(300, 1e-45, np.float32))                                   # the smallest denormal, warp class
+    lists.append(np.asarray([1e-38, 1e-40, 1.0, 3e-39] * 20, np.float32))           # denormals beside normals
+    lists.append(np.asarray([3.0e38, 1.0, 2.9e38, 1e-30] * 10, np.float32))         # near the largest float
     xadj, adj, w = _star_graph(lists)
     ctx.upload(xadj, adj, w)
     ctx.alias_build_offline()
@@ -614,6 +618,9 @@ def test_online_direct_slots_every_degree_class(ctx, oracle):
     lists.append(np.asarray([0, 1, 2, 0, 5] * 40, np.float32))         # zeros inside
     lists.append(np.asarray([np.nan, -1, np.inf, 2, 3], np.float32))
     lists.append(rng.uniform(0, 1, 3000).astype(np.float32) ** 8)      # skewed, many tiny
+    lists.append(np.asarray([1e-40, 2e-40, 3e-41, 0, 1e-45], np.float32))           # denormals only
+    lists.append(np.asarray([1e-38, 1e-40, 1.0, 3e-39] * 20, np.float32))           # denormals beside normals
+    lists.append(np.asarray([3.0e38, 1.0, 2.9e38, 1e-30] * 10, np.float32))         # near the largest float
     xadj, adj, w = _star_graph(lists)
     ctx.upload(xadj, adj, w)
     starts = np.concatenate([np.full(min(4 * len(l), 6000), i, np.uint32) for i, l in enumerate(lists)])

@@ -202,3 +202,15 @@ def test_unbiased_walks_and_samples_ignore_weights(oracle, rmat12):
     for s in range(0, 256, 17):
         d = int(deg[seeds[s]])
         assert sl[s, 0] == (min(d, 6) if d else 0)
+
+
+def test_alias_denormal_and_huge_weights_reconstruct(oracle):
+    for w in ([1e-40, 2e-40, 3e-41, 0, 1e-45], [1e-38, 1e-40, 1.0, 3e-39] * 20, [3.0e38, 1.0, 2.9e38, 1e-30] * 10):
+        w = np.asarray(w, np.float32)
+        xadj = np.asarray([0, len(w)], np.uint32)
+        prob, alias, valid = oracle.alias_build(xadj, w)
+        assert valid[0] == 1
+        got = _encoded_probs(w, prob, alias)
+        want = w.astype(np.float64) / w.astype(np.float64).sum()
+        # quantisation keeps 2^-39 of the largest weight: weights far below that may round to zero mass
+        assert np.allclose(got, want, rtol=1e-6, atol=2.0 ** -38)
