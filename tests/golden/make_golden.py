@@ -6,7 +6,7 @@
 The reference ships no golden vectors for this path (its outputs are not reproducible), so the
 fixture pins the definitions of this build instead: a seeded R-MAT graph (scale 8, 16 edges per
 vertex, plus one hub and hand-made corner vertices), its alias table, and walks / k-hop trees for
-every application and mode.  Tests compare both the oracle (so that it cannot drift silently) and
+every application and mode, weighted and unbiased.  Tests compare both the oracle (so that it cannot drift silently) and
 the CUDA library against the stored arrays.
 """
 import os
@@ -47,9 +47,14 @@ def main():
         out["walk_%s_paths" % name], out["walk_%s_lengths" % name] = p, l
         p2, l2 = O.walk(xadj, adj, wgt, None, starts, 21, seed=42, walker_base=5, online=True, **kw)
         assert np.array_equal(p, p2) and np.array_equal(l, l2)
+        # unbiased (uniform neighbour choice, no table, no weights)
+        pu, lu = O.walk(xadj, adj, None, None, starts, 21, seed=42, walker_base=5, unbiased=True, **kw)
+        out["walk_unbiased_%s_paths" % name], out["walk_unbiased_%s_lengths" % name] = pu, lu
     for flags in (0, 1):
         d, s = O.khop(xadj, adj, wgt, table, starts, [5, 3], flags=flags, seed=42, instance_base=9)
         out["khop_flags%d_data" % flags], out["khop_flags%d_lengths" % flags] = d, s
+    d, s = O.khop(xadj, adj, None, None, starts, [5, 3], flags=2, seed=42, instance_base=9)
+    out["khop_unbiased_data"], out["khop_unbiased_lengths"] = d, s
     np.savez_compressed(os.path.join(HERE, "small_graph.npz"), **out)
     print("wrote small_graph.npz: V=%d E=%d" % (V, len(adj)))
 

@@ -29,6 +29,11 @@ def test_oracle_reproduces_golden(oracle, gold):
         p, l = oracle.walk(x, a, w, table, gold["starts"], 21, seed=42, walker_base=5, **kw)
         assert np.array_equal(l, gold["walk_%s_lengths" % name])
         assert np.array_equal(p, gold["walk_%s_paths" % name])
+        p, l = oracle.walk(x, a, None, None, gold["starts"], 21, seed=42, walker_base=5, unbiased=True, **kw)
+        assert np.array_equal(l, gold["walk_unbiased_%s_lengths" % name])
+        assert np.array_equal(p, gold["walk_unbiased_%s_paths" % name])
+    d, s = oracle.khop(x, a, None, None, gold["starts"], [5, 3], flags=2, seed=42, instance_base=9)
+    assert np.array_equal(d, gold["khop_unbiased_data"]) and np.array_equal(s, gold["khop_unbiased_lengths"])
     for flags in (0, 1):
         d, s = oracle.khop(x, a, w, table, gold["starts"], [5, 3], flags=flags, seed=42, instance_base=9)
         assert np.array_equal(d, gold["khop_flags%d_data" % flags])
@@ -67,7 +72,17 @@ def test_library_reproduces_golden(ctx, gold, mode):
             p, l, _, _ = ctx.walk(gold["starts"], 21, mode=m, seed=42, walker_base=5, **kw)
             assert np.array_equal(l, gl) and np.array_equal(p[_live(p, l)], gp[_live(gp, gl)])
             ctx.walk_records_free()
+        if mode == "online":    # both ways of obtaining the drawn slot: tables per step (4), direct (8)
+            for flags in (4, 8):
+                p, l, _, _ = ctx.walk(gold["starts"], 21, mode=m, seed=42, walker_base=5, flags=flags, **kw)
+                assert np.array_equal(l, gl) and np.array_equal(p[_live(p, l)], gp[_live(gp, gl)])
+        gp, gl = gold["walk_unbiased_%s_paths" % name], gold["walk_unbiased_%s_lengths" % name]
+        p, l, _, e = ctx.walk(gold["starts"], 21, mode=m, seed=42, walker_base=5, flags=2, **kw)   # WALK_UNBIASED
+        assert np.array_equal(l, gl) and e == int(gl.sum())
+        assert np.array_equal(p[_live(p, l)], gp[_live(gp, gl)])
     for flags in (0, 1):
         d, s, _, _ = ctx.sample_khop(gold["starts"], [5, 3], mode=m, flags=flags, seed=42, instance_base=9)
         assert np.array_equal(d, gold["khop_flags%d_data" % flags])
         assert np.array_equal(s, gold["khop_flags%d_lengths" % flags])
+    d, s, _, _ = ctx.sample_khop(gold["starts"], [5, 3], mode=m, flags=2, seed=42, instance_base=9)    # KHOP_UNBIASED
+    assert np.array_equal(d, gold["khop_unbiased_data"]) and np.array_equal(s, gold["khop_unbiased_lengths"])
