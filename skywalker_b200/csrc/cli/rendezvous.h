@@ -13,9 +13,9 @@ struct Rendezvous {
   std::condition_variable cv;
   int ndev = 1, arrived = 0, gone = 0;
   uint64_t gen = 0;
-  bool ok = true, verdict = true;
+  bool ok = true, outcome = true;
   void release() {  // caller holds m
-    verdict = ok && gone == 0;
+    outcome = ok && gone == 0;
     arrived = 0;
     ok = true;
     ++gen;
@@ -27,10 +27,10 @@ struct Rendezvous {
     const uint64_t g = gen;
     if (++arrived + gone >= ndev) {
       release();
-      return verdict;
+      return outcome;
     }
     cv.wait(l, [&] { return gen != g; });
-    return verdict;
+    return outcome;
   }
   void leave() {  // a thread that ends (for whatever reason) takes part in no later agreement
     std::lock_guard<std::mutex> l(m);

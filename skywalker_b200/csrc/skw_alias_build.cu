@@ -776,7 +776,7 @@ __global__ void __launch_bounds__(NT) build_cta_staged_kernel(const u32* __restr
     } else {
       for (u32 i = threadIdx.x; i < n; i += NT) sW[head + i] = __ldg(w + i);
     }
-    // the same verdict in every thread (and the barrier that publishes the plain stores)
+    // the same outcome in every thread (and the barrier that publishes the plain stores)
     if (!__syncthreads_and(mine_ok ? 1 : 0)) {
       // the copy did not report completion in time: record it, give it one more bounded chance to
       // land so that nothing still writes this CTA's shared memory when it leaves, and stop
@@ -1066,7 +1066,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
 // ------------------------------------------------------------------ online frontier --------
 // Collect the distinct vertices the live units stand on and bin them by degree class.  Unit u
 // reads verts[(u / width) * cells + offs + u % width]; alive (optional) holds kAliveMark for
-// units still running.  A vertex is claimed by the first unit that stamps it this round.
+// units still running.  A vertex is claimed by the first unit that stamps it in the current collection.
 constexpr u32 kAliveMark = 0xFFFFFFFFu;
 
 __global__ void frontier_reset_kernel(u32* __restrict__ cls, u32 cap) {
