@@ -95,6 +95,25 @@ def test_fullsize_ppr_statistics(ctx, oracle, big):
     assert (lens[~alive0] == 0).all()
 
 
+def test_fullsize_packed_result_equals_rows(ctx, oracle, big):
+    """4 M PPR walkers (four slices of the packed pipeline): the packed result holds exactly the live
+    cells of the row matrix, in walker order, with and without walk records."""
+    xadj, adjncy, w = big
+    V = len(xadj) - 1
+    n = 4 << 20
+    starts = oracle.gen_starts(n, V, 9)
+    paths, lens, _, edges = ctx.walk(starts, 41, app=APP_PPR, tp=0.15, seed=5, walker_base=3)
+    live = np.arange(41)[None, :] <= lens[:, None]
+    want = paths[live]
+    packed, plens, cells, _, pedges = ctx.walk_packed(starts, 41, app=APP_PPR, tp=0.15, seed=5, walker_base=3)
+    assert cells == len(want) == edges + n and pedges == edges
+    assert np.array_equal(plens, lens) and np.array_equal(packed[:cells], want)
+    ctx.walk_records_build()
+    packed2, plens2, cells2, _, _ = ctx.walk_packed(starts, 41, app=APP_PPR, tp=0.15, seed=5, walker_base=3)
+    ctx.walk_records_free()
+    assert cells2 == cells and np.array_equal(plens2, lens) and np.array_equal(packed2[:cells], want)
+
+
 def test_fullsize_khop(ctx, oracle, big):
     xadj, adjncy, w = big
     V = len(xadj) - 1
