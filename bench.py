@@ -55,9 +55,10 @@ GRAPH_SEED, WEIGHT_SEED, START_SEED, WALK_SEED = 1, 7, 42, 42
 ALG_BYTES_PER_EDGE = 24        # offline step: 8 offsets + 8 slot + 4 neighbour + 4 path store
 ALG_BYTES_PER_BUILD_EDGE = 12  # offline build: 4 weight + 8 slot
 # DRAM bytes per sampled edge, (dram__bytes_read.sum + dram__bytes_write.sum) / sampled edges of one
-# launch, from ncu captures of the reduced PPR workload "c5s" (same kernels, scale 22, 1 M walkers;
-# summary in profiles/walk_kernels_ppr_rmat22_1Mwalkers.md).  Traffic grows in proportion to walkers
-# and steps, so roofline.traffic = this figure x the sampled edges of a full launch.
+# launch, from an ncu capture of the reduced PPR workload "c5s" (same kernels, scale 22, 1 M walkers).
+# Traffic grows in proportion to walkers and steps, so roofline.traffic = this figure x the sampled
+# edges of a full launch.  The figures belong to the kernels as they were when captured: a change to a
+# step kernel needs a new capture.
 DRAM_BYTES_PER_SAMPLED_EDGE = {"walk_records_ppr_kernel": 101.5, "walk_records_walk_kernel": 105.2,
                                "walk_offline_kernel": 162.9}
 
@@ -152,26 +153,59 @@ def app_id(wl):
     return {"deepwalk": APP_DEEPWALK, "ppr": APP_PPR, "node2vec": APP_NODE2VEC}[wl.get("app", "deepwalk")]
 
 
-def cpu_leg(ctx, wl, threads, want_seconds=12.0, steps=1, warmup=0):
+def host_memory_available():
+    """Bytes this process may still allocate on the host: the smaller of MemAvailable and what the
+    cgroup limit leaves (a rank that outgrows it takes the whole box down)."""
+    avail = None
+    try:
+        for line in open("/proc/meminfo"):
+            if line.startswith("MemAvailable:"):
+                avail = int(line.split()[1]) * 1024
+    except Exception:
+        pass
+    try:
+        lim = open("/sys/fs/cgroup/memory.max").read().strip()
+        cur = int(open("/sys/fs/cgroup/memory.current").read().strip())
+        if lim != "max":
+            left = int(lim) - cur
+            avail = left if avail is None else min(avail, left)
+    except Exception:
+        pass
+    return avail
+
+
+def host_copy_bytes(V, E, online):
+    """Host bytes of the CPU checker's inputs: offsets, neighbours, and weights (online) or the
+    exported table (offline), plus staging."""
+    return 4 * (V + 1) + 4 * E + (4 * E if online else 8 * E + V) + (1 << 30)
+
+
+def host_copy(ctx, online, with_weights=False):
+    """The resident graph (and, for offline modes, the GPU-built table) copied to the host."""
+    xadj, adjncy, wgt = ctx.download(weights=online or with_weights)
+    table = None if online else ctx.alias_export()
+    return {"xadj": xadj, "adjncy": adjncy, "wgt": wgt if online else np.zeros(1, np.float32), "table": table,
+            "build_weights": wgt if (with_weights and not online) else None}
+
+
+def cpu_leg(host, wl, threads, want_seconds=12.0, steps=1, warmup=0, build_weights=None):
     """Time the CPU oracle on a bounded sample of the workload, same inputs (downloaded from the GPU)
     and same Philox streams: alias build over a vertex prefix, then the workload's own step."""
     from oracle import oracle as O
-    V, E, _ = ctx.graph_info()
-    xadj, adjncy, wgt = ctx.download()
+    xadj, adjncy, wgt, table = host["xadj"], host["adjncy"], host["wgt"], host["table"]
+    V, E = len(xadj) - 1, int(xadj[-1])
     # all host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which must not shrink the
     # CPU arm to one thread)
     threads = threads or len(os.sched_getaffinity(0)) or O.num_threads()
     online = wl["mode"] == "online"
     target = min(E, max(1 << 20, E // 16))
     v_end = max(1, min(V, int(np.searchsorted(xadj, target, side="left"))))
-    t0 = time.perf_counter()
-    O.alias_build(xadj, wgt, 0, v_end, threads)
-    build_eps = float(xadj[v_end]) / (time.perf_counter() - t0)
-    if online:
-        table = None
-    else:
-        wgt = np.zeros(1, np.float32)
-        table = ctx.alias_export()
+    bw = wgt if online else build_weights
+    build_eps = None
+    if bw is not None:
+        t0 = time.perf_counter()
+        O.alias_build(xadj, bw, 0, v_end, threads)
+        build_eps = float(xadj[v_end]) / (time.perf_counter() - t0)
     n_total = wl["units"]
     cap = min(n_total, 2000000)
     starts = O.gen_starts(cap, V, START_SEED)
@@ -199,11 +233,57 @@ def cpu_leg(ctx, wl, threads, want_seconds=12.0, steps=1, warmup=0):
         t_run += time.perf_counter() - t0
     edges //= max(1, steps)
     t_run /= max(1, steps)
-    return {"value": edges / t_run, "unit": "sampled edges/s", "cores": threads, "kind": "port",
-            "sample": "first %d of %d %s (%.2f s); alias build of the first %d vertices / %d edges: %.3g edges/s"
-                      % (n_s, n_total, "seeds" if wl["kind"] == "khop" else "walkers", t_run, v_end,
-                         int(xadj[v_end]), build_eps),
+    sample = "first %d of %d %s (%.2f s)" % (n_s, n_total, "seeds" if wl["kind"] == "khop" else "walkers", t_run)
+    if build_eps is not None:
+        sample += "; alias build of the first %d vertices / %d edges: %.3g edges/s" % (v_end, int(xadj[v_end]), build_eps)
+    return {"value": edges / t_run, "unit": "sampled edges/s", "cores": threads, "kind": "port", "sample": sample,
             "alias_build_edges_per_s": build_eps, "seconds": t_run, "edges": edges}
+
+
+PARITY_WALKERS, PARITY_SEEDS = 10000, 2048
+
+
+def parity_sample(ctx, wl, host, lo, n_local, d_starts, d_result, d_lengths, mode, hop, threads):
+    """Bit-compare the product path with the CPU oracle on the first K units of this rank's shard, at
+    the workload's own size: one extra untimed pass over the WHOLE shard through the same entry point
+    and path selection the timed steps use (seed WALK_SEED, start seed START_SEED), then the first K
+    result rows against oracle.walk / oracle.khop on the same global unit ids; walks also through the
+    packed host entry point.  Returns (units compared, equal)."""
+    import torch
+    from oracle import oracle as O
+    khop = wl["kind"] == "khop"
+    online = wl["mode"] == "online"
+    V = len(host["xadj"]) - 1
+    threads = threads or len(os.sched_getaffinity(0)) or O.num_threads()
+    K = min(n_local, PARITY_SEEDS if khop else PARITY_WALKERS)
+    if K == 0:
+        return 0, True
+    ctx.generate_starts(n_local, START_SEED, d_starts, id_base=lo)
+    h_starts = O.gen_starts(K, V, START_SEED, id_base=lo)
+    ok = bool(np.array_equal(d_starts[:K].cpu().numpy().view(np.uint32), h_starts))
+    if khop:
+        ctx.sample_khop(d_starts, wl["fanout"], mode=mode, seed=WALK_SEED, instance_base=lo, data=d_result,
+                        sample_lengths=d_lengths, n=n_local)
+        cells, lens_per = ctx.khop_layout(wl["fanout"])
+        got_d = d_result[:K * cells].cpu().numpy().view(np.uint32).reshape(K, cells)
+        got_l = d_lengths[:K * lens_per].cpu().numpy().view(np.uint32).reshape(K, lens_per)
+        want_d, want_l = O.khop(host["xadj"], host["adjncy"], host["wgt"], host["table"], h_starts, wl["fanout"],
+                                online=online, seed=WALK_SEED, instance_base=lo, threads=threads)
+        return K, ok and bool(np.array_equal(got_d, want_d)) and bool(np.array_equal(got_l, want_l))
+    kw = dict(app=app_id(wl), tp=wl.get("tp", 0.0), p=wl.get("p", 2.0), q=wl.get("q", 0.5), seed=WALK_SEED,
+              walker_base=lo)
+    ctx.walk(d_starts, hop, mode=mode, paths=d_result, lengths=d_lengths, n=n_local, **kw)
+    got_p = d_result[:K * hop].cpu().numpy().view(np.uint32).reshape(K, hop)
+    got_l = d_lengths[:K].cpu().numpy().view(np.uint32)
+    want_p, want_l = O.walk(host["xadj"], host["adjncy"], host["wgt"], host["table"], h_starts, hop, online=online,
+                            threads=threads, **kw)
+    live = np.arange(hop)[None, :] <= want_l[:, None]
+    ok = ok and bool(np.array_equal(got_l, want_l)) and bool(np.array_equal(got_p[live], want_p[live]))
+    # the packed host entry point on the same walkers
+    packed, pl, cells, _, _ = ctx.walk_packed(h_starts, hop, mode=mode, **kw)
+    ok = ok and bool(np.array_equal(pl, want_l)) and cells == int(want_l.sum()) + K
+    ok = ok and bool(np.array_equal(packed[:cells], want_p[live]))
+    return K, ok
 
 
 def online_algorithmic_bytes(ctx, wl, result, lengths):
@@ -235,6 +315,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the bit-comparison with the CPU oracle")
     ap.add_argument("--no-records", action="store_true", help="walk over the 8-byte slot table only")
     ap.add_argument("--cpu-threads", type=int, default=0)
     args = ap.parse_args()
@@ -270,17 +351,19 @@ def main():
         V, E, md = make_graph(ctx, wl)
         if not online:
             ctx.alias_build_offline()
+        host = host_copy(ctx, online, with_weights=True)
         # every step = one pass of the CPU path over the same bounded sample (at most ~10 s, and ~2 minutes
-        # for the K steps together); value = edges of the K steps / their time
-        ref_warm = min(args.warmup, 1)
-        best = cpu_leg(ctx, wl, args.cpu_threads, want_seconds=min(10.0, 120.0 / max(1, args.steps)),
-                       steps=args.steps, warmup=ref_warm)
+        # for the W + K passes together); value = edges of the K steps / their time
+        ref_warm = args.warmup
+        best = cpu_leg(host, wl, args.cpu_threads, want_seconds=min(10.0, 120.0 / max(1, args.steps + ref_warm)),
+                       steps=args.steps, warmup=ref_warm, build_weights=host["build_weights"])
         out = {"impl": "reference", "metric": "sampled edges/s", "value": best["value"], "unit": "sampled edges/s",
                "n_gpus": args.gpus, "steps": args.steps, "warmup": ref_warm, "ms_per_step": best["seconds"] * 1e3,
                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32 ids / f32 prob",
                "data": "synthetic",
-               "config": dict(config, V=V, E=E, inputs="generated on the GPU by the library's seeded generator, then "
-                              "copied to the host; only the CPU path is timed"),
+               "config": dict(config, V=V, E=E),
+               "inputs": "generated on the GPU by the library's seeded generator, then copied to the host; only the "
+                         "CPU path is timed",
                "cpu_baseline": {k: best[k] for k in ("value", "unit", "cores", "kind", "sample")},
                "e2e": {"value": best["value"], "unit": "sampled edges/s", "h2d_bytes_per_step": 0,
                        "d2h_bytes_per_step": 0}}
@@ -463,10 +546,11 @@ def main():
         np_s, np_r, np_l = (t.numpy().view(np.uint32) for t in (h_starts, h_res, h_len))
         if khop:
             np_r, np_l = np_r.reshape(nl, -1), np_l.reshape(nl, -1)
-        e_steps = max(1, min(args.steps, 5))
+        e_steps = max(1, min(args.steps, 20))
 
         def timed_host_calls(call):
-            call(0)
+            for i in range(3):      # warm calls: staging buffers reach their steady size
+                call(50 + i)
             barrier()
             t0 = time.perf_counter()
             edges, per_call = 0, []
@@ -480,7 +564,7 @@ def main():
             return m2[0], s2[1], per_call
 
         e_ms, e_edges, e_calls = timed_host_calls(lambda i: step(i, np_s, np_r, np_l)[3])
-        rows = {"ms_per_call_this_rank": e_calls, "value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+        rows = {"ms_per_call_this_rank": e_calls, "ms_per_call_median": float(np.median(e_calls)), "value": e_edges / (e_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
                 "ms_per_step": e_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
                 # walks into pinned memory transfer the written cells of each row (length + 1) and the lengths;
                 # k-hop trees are dense and are copied whole
@@ -499,7 +583,7 @@ def main():
                                        q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, packed=np_r,
                                        lengths=np_l, n=n_local)[4]
             p_ms, p_edges, p_calls = timed_host_calls(packed_call)
-            e2e = {"ms_per_call_this_rank": p_calls, "value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+            e2e = {"ms_per_call_this_rank": p_calls, "ms_per_call_median": float(np.median(p_calls)), "value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
                    "ms_per_step": p_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
                    "d2h_bytes_per_step": int(4 * (p_edges / e_steps / world + 2 * n_local)),
                    "note": "host-buffer entry point skw_walk_packed with pinned memory: start vertices H2D, walk "
@@ -534,14 +618,46 @@ def main():
         except Exception:
             probe_gacc = None
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        try:
-            cpu = cpu_leg(ctx, wl, args.cpu_threads)
-            cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample", "alias_build_edges_per_s")}
-        except MemoryError as e:   # the host copy of graph + table needs ~4 x E x 4 bytes
-            cpu = {"value": None, "unit": "sampled edges/s", "cores": 0, "kind": "port",
-                   "sample": "unavailable: host memory too small for the graph copy (%s)" % e}
+    # Parity at the workload's own size, on every rank: the first K units of the rank's shard against the
+    # CPU oracle (bit for bit), verdicts AND-reduced.  The oracle needs the graph (and table) on the host;
+    # ranks take turns in waves sized by the host memory that is free.
+    cpu, parity = None, None
+    need = host_copy_bytes(V, E, online) + (4 * E if world == 1 and not online else 0)
+    avail = host_memory_available()
+    at_once = world if avail is None else int(min(world, (0.6 * avail) // need))
+    if dist is not None:
+        t = torch.tensor([at_once], dtype=torch.int64, device=dev)
+        dist.broadcast(t, src=0)       # rank 0's reading decides for all (one host)
+        at_once = int(t.item())
+    if args.no_parity:
+        parity = {"units": 0, "equal": None, "ranks": world, "skipped": "--no-parity"}
+    elif at_once < 1:
+        parity = {"units": 0, "equal": None, "ranks": world,
+                  "skipped": "host memory: %.1f GB free, the checker's inputs need %.1f GB" % ((avail or 0) / 1e9, need / 1e9)}
+    else:
+        units, equal = 0, True
+        for wave in range(0, world, at_once):
+            if wave <= rank < wave + at_once:
+                host = host_copy(ctx, online, with_weights=(world == 1))
+                units, equal = parity_sample(ctx, wl, host, lo, n_local, starts, result, lengths, mode, hop,
+                                             args.cpu_threads)
+                if rank == 0 and world == 1 and not args.no_cpu_baseline:
+                    cpu = cpu_leg(host, wl, args.cpu_threads, build_weights=host["build_weights"])
+                    cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample", "alias_build_edges_per_s")}
+                del host
+            if dist is not None:
+                dist.barrier()
+        t = torch.tensor([1 if equal else 0, units], dtype=torch.int64, device=dev)
+        if dist is not None:
+            mn = t.clone()
+            dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+            t = mn
+        parity = {"units": int(t[1].item()), "equal": bool(t[0].item()), "ranks": world,
+                  "what": "first K %s of every rank's shard, row layout%s, against the CPU oracle bit for bit"
+                          % ("seeds" if khop else "walkers", "" if khop else " and packed layout")}
+    config["parity_sample"] = parity
+    if sliced is not None:
+        config["alias_build_sliced_equals_replicated"] = sliced["equals_replicated_build"]
 
     if rank == 0:
         per_step_ms = kernel_ms / args.steps
@@ -567,7 +683,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": span_ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u32 ids / f32 prob", "data": "synthetic",
-            "config": dict(config, V=V, E=E, max_degree=max_deg, units_per_gpu=n_local, graph_gen_s=t_gen),
+            "config": dict(config, V=V, E=E),
+            "max_degree": max_deg, "units_per_gpu": n_local, "graph_gen_s": t_gen,
             "kernel_ms_per_step": per_step_ms,
             "sampled_edges_per_step": edges_all / args.steps,
             "alias_build": {"value": E / (build_best * 1e-3), "unit": "edges/s", "ms": build_best,

@@ -173,8 +173,11 @@ int skw_alias_device_ptrs(const skw_ctx* ctx, const void** d_slots, const uint8_
  * image, present on every GPU that loads the library until the process exits; longer lists are
  * rejected with SKW_ERR_ARG.  The result is bit-identical to what skw_alias_build_offline writes
  * for a vertex with this weight list.
- * The first call on a device looks up the array's device address; make that first call outside
- * any stream capture.  Every call uses the same array, which keeps whatever the previous call
+ * The first call on a device looks up the array's device address (and, where the CUDA runtime
+ * loads modules lazily, is what places the array and the kernel on the GPU): make it at start-up,
+ * before the host's own pool reserves the remaining memory, and outside any stream capture.  The
+ * address is remembered per device for the life of the process and does not survive a
+ * cudaDeviceReset() by the host.  Every call uses the same array, which keeps whatever the previous call
  * left (the call clears the part that must start at zero): two calls whose kernels can overlap
  * on the GPU (different streams, different threads) race on it and must be serialised by the
  * caller.  The function calls no cudaMalloc / cudaFree and no allocating library routine. */

@@ -1278,12 +1278,18 @@ extern "C" int skw_alias_build_list_static(const float* d_weights, uint32_t n, v
     return static_fail(errbuf, errbuf_len, SKW_ERR_CUDA, "skw_alias_build_list_static: cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= 64)
     return static_fail(errbuf, errbuf_len, SKW_ERR_ARG, "skw_alias_build_list_static: device %d not supported", dev);
-  cudaPointerAttributes at;
-  e = cudaPointerGetAttributes(&at, d_weights);
-  if (e != cudaSuccess || at.type != cudaMemoryTypeDevice || at.device != dev) {
-    cudaGetLastError();
-    return static_fail(errbuf, errbuf_len, SKW_ERR_ARG,
-                       "skw_alias_build_list_static: d_weights is not device memory of the current device %d", dev);
+  // a host or peer pointer handed to the kernel would fault: all three buffers must be device memory
+  // of the current device
+  const void* bufs[3] = {d_weights, d_slots, d_valid};
+  const char* names[3] = {"d_weights", "d_slots", "d_valid"};
+  for (int i = 0; i < 3; ++i) {
+    cudaPointerAttributes at;
+    e = cudaPointerGetAttributes(&at, bufs[i]);
+    if (e != cudaSuccess || at.type != cudaMemoryTypeDevice || at.device != dev) {
+      cudaGetLastError();
+      return static_fail(errbuf, errbuf_len, SKW_ERR_ARG,
+                         "skw_alias_build_list_static: %s is not device memory of the current device %d", names[i], dev);
+    }
   }
   unsigned char* scratch = nullptr;
   {

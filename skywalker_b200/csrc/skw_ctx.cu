@@ -83,6 +83,7 @@ static void free_graph(skw_ctx* ctx) {
   ctx->records = nullptr;
   ctx->vinfo = nullptr;
   ctx->vbits = nullptr;
+  ctx->records_ready = false;
   ctx->stamp = nullptr;
   ctx->stamp_round = 0;
   ctx->slots = nullptr;
@@ -133,6 +134,110 @@ __global__ void fill_random_weights_kernel(float* __restrict__ w, size_t n, uint
   }
 }
 
+// Structural check of a CSR handed in by a caller: offsets non-decreasing and at most E, every
+// destination below V.  Every kernel of the library indexes with these values unchecked, so a bad
+// array is refused here (error word, no fault) instead of being walked.
+__global__ void __launch_bounds__(256) validate_csr_kernel(const uint32_t* __restrict__ xadj,
+                                                           const uint32_t* __restrict__ adjncy, uint32_t V,
+                                                           uint64_t E, uint32_t* __restrict__ err) {
+  const size_t T = (size_t)gridDim.x * blockDim.x, t0 = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  for (size_t v = t0; v < V; v += T) {
+    const uint32_t a = xadj[v], b = xadj[v + 1];
+    if (a > b || b > E) dev_fail(err, DEV_ERR_INDEX, (uint32_t)v, a, b);
+  }
+  if (t0 == 0 && (xadj[0] != 0 || xadj[V] != (uint32_t)E)) dev_fail(err, DEV_ERR_INDEX, V, xadj[0], xadj[V]);
+  for (size_t e = t0; e < E; e += T) {
+    const uint32_t d = adjncy[e];
+    if (d >= V) dev_fail(err, DEV_ERR_INDEX, d, (uint32_t)e, 21);
+  }
+}
+
+int validate_graph(skw_ctx* ctx, const char* who) {
+  int rc = err_reset(ctx);
+  if (rc != SKW_OK) return rc;
+  validate_csr_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(ctx->xadj, ctx->adjncy, ctx->V, ctx->E, ctx->d_err);
+  SKW_LAUNCHED(ctx);
+  rc = err_check(ctx, who);
+  if (rc == SKW_ERR_DEVICE) {
+    const std::string why = ctx->err;
+    free_graph(ctx);
+    return fail(ctx, SKW_ERR_ARG, "%s: the CSR is malformed (offsets must be non-decreasing from 0 to E, destinations below V) -- %s",
+                who, why.c_str());
+  }
+  return rc;
+}
+
+// Every slot starts as {prob = -1, alias = 0}: "no usable table here".  A walker or k-hop draw that
+// meets such a slot ends, so vertices outside the range a sliced build has covered so far (or whose
+// slice has not arrived yet) are dead ends rather than reads of uninitialised memory.
+__global__ void __launch_bounds__(256) fill_unbuilt_slots_kernel(Slot* __restrict__ slots, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    slots[i] = Slot{-1.0f, 0u};
+}
+
+// Check of a table that did not come from the builders (import, checkpoint): every alias must point
+// inside its vertex's list and every prob must be -1 (invalid vertex) or in [0, 1].
+__global__ void __launch_bounds__(256) validate_table_kernel(const uint32_t* __restrict__ xadj,
+                                                             const Slot* __restrict__ slots, uint32_t V,
+                                                             uint32_t* __restrict__ err) {
+  const uint32_t lane = threadIdx.x & 31;
+  const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t v = warp; v < V; v += nwarps) {
+    const uint32_t off = xadj[v], deg = xadj[v + 1] - off;
+    for (uint32_t i = lane; i < deg; i += 32) {
+      const Slot s = slots[(size_t)off + i];
+      const bool prob_ok = s.prob == -1.0f || (s.prob >= 0.0f && s.prob <= 1.0f);
+      if (s.alias >= deg || !prob_ok) dev_fail(err, DEV_ERR_INDEX, (uint32_t)v, i, s.alias);
+    }
+  }
+}
+
+int validate_table(skw_ctx* ctx, const char* who) {
+  int rc = err_reset(ctx);
+  if (rc != SKW_OK) return rc;
+  if (ctx->V) {
+    validate_table_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(ctx->xadj, ctx->slots, ctx->V, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  rc = err_check(ctx, who);
+  if (rc == SKW_ERR_DEVICE) {
+    const std::string why = ctx->err;
+    return fail(ctx, SKW_ERR_ARG, "%s: the table does not fit the resident graph (an alias outside its vertex's list or a prob "
+                "outside [0,1]) -- %s", who, why.c_str());
+  }
+  return rc;
+}
+
+// 64-bit fingerprint of the offset array: sum over v of mix(v, xadj[v]).  Stored in a table
+// checkpoint so that a table written for another graph with the same V and E is refused.
+__global__ void __launch_bounds__(256) xadj_fingerprint_kernel(const uint32_t* __restrict__ xadj, uint32_t V,
+                                                               unsigned long long* __restrict__ out) {
+  unsigned long long acc = 0;
+  for (size_t v = blockIdx.x * (size_t)blockDim.x + threadIdx.x; v <= V; v += (size_t)gridDim.x * blockDim.x) {
+    unsigned long long x = ((unsigned long long)v << 32) ^ xadj[v];
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdull;
+    x ^= x >> 33;
+    x *= 0xc4ceb9fe1a85ec53ull;
+    x ^= x >> 33;
+    acc += x;
+  }
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd(out, acc);
+}
+
+static int xadj_fingerprint(skw_ctx* ctx, uint64_t* out) {
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), ctx->stream));
+  xadj_fingerprint_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(ctx->xadj, ctx->V,
+                                                                      reinterpret_cast<unsigned long long*>(ctx->d_sum));
+  SKW_LAUNCHED(ctx);
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, ctx->stream));
+  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  *out = *ctx->h_sum;
+  return SKW_OK;
+}
+
 int finish_graph(skw_ctx* ctx) {
   SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), ctx->stream));
   if (ctx->V) {
@@ -148,6 +253,7 @@ int finish_graph(skw_ctx* ctx) {
 }
 
 void drop_records(skw_ctx* ctx) {
+  ctx->records_ready = false;
   if (ctx->records || ctx->vinfo) cudaStreamSynchronize(ctx->stream);
   cudaFree(ctx->records);
   cudaFree(ctx->vinfo);
@@ -159,7 +265,11 @@ void drop_records(skw_ctx* ctx) {
 
 int alloc_table(skw_ctx* ctx) {
   // kSlotSlack spare entries let a multi-GPU caller all-gather the table in equal chunks in place
-  if (!ctx->slots) SKW_CUDA(ctx, cudaMalloc(&ctx->slots, sizeof(Slot) * (ctx->E + kSlotSlack)));
+  if (!ctx->slots) {
+    SKW_CUDA(ctx, cudaMalloc(&ctx->slots, sizeof(Slot) * (ctx->E + kSlotSlack)));
+    fill_unbuilt_slots_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(ctx->slots, (size_t)ctx->E + kSlotSlack);
+    SKW_LAUNCHED(ctx);
+  }
   if (!ctx->valid) {
     SKW_CUDA(ctx, cudaMalloc(&ctx->valid, ctx->V ? ctx->V : 1));
     SKW_CUDA(ctx, cudaMemsetAsync(ctx->valid, 0, ctx->V ? ctx->V : 1, ctx->stream));
@@ -310,6 +420,8 @@ int skw_graph_upload(skw_ctx* ctx, uint32_t V, uint64_t E, const uint32_t* h_xad
       SKW_LAUNCHED(ctx);
     }
   }
+  int rc = validate_graph(ctx, "skw_graph_upload");
+  if (rc != SKW_OK) return rc;
   return finish_graph(ctx);
 }
 
@@ -332,6 +444,8 @@ int skw_graph_adopt_device(skw_ctx* ctx, uint32_t V, uint64_t E, const uint32_t*
     fill_ones_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(ctx->adjwgt, E);
     SKW_LAUNCHED(ctx);
   }
+  int rc = validate_graph(ctx, "skw_graph_adopt_device");
+  if (rc != SKW_OK) return rc;
   return finish_graph(ctx);
 }
 
@@ -511,12 +625,15 @@ int skw_alias_import(skw_ctx* ctx, const float* h_prob, const uint32_t* h_alias,
   if (ctx->V)
     SKW_CUDA(ctx, cudaMemcpyAsync(ctx->valid, h_valid, ctx->V, cudaMemcpyHostToDevice, ctx->stream));
   SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->table_ready = false;
+  if ((rc = validate_table(ctx, "skw_alias_import")) != SKW_OK) return rc;
   ctx->table_ready = true;
   return SKW_OK;
 }
 
-// Table checkpoint: 32-byte header {magic "SKWTABLE", V, E, slot bytes} + E packed slots + V valid
-// bytes.  A built table is a pure function of the graph, so a checkpoint saves only the build time.
+// Table checkpoint: 48-byte header {magic "SKWTABLE", V, E, slot bytes, fingerprint of the offset
+// array, 0} + E packed slots + V valid bytes.  A built table is a pure function of the graph, so a
+// checkpoint saves only the build time.
 static const char kTableMagic[8] = {'S', 'K', 'W', 'T', 'A', 'B', 'L', 'E'};
 
 int skw_alias_save(skw_ctx* ctx, const char* path) {
@@ -525,12 +642,17 @@ int skw_alias_save(skw_ctx* ctx, const char* path) {
   DeviceGuard g(ctx->device);
   FILE* f = fopen(path, "wb");
   if (!f) return fail(ctx, SKW_ERR_IO, "skw_alias_save: cannot create %s", path);
-  uint64_t hdr[4];
+  uint64_t hdr[6];
   memcpy(&hdr[0], kTableMagic, 8);
   hdr[1] = ctx->V;
   hdr[2] = ctx->E;
   hdr[3] = sizeof(Slot);
-  bool ok = fwrite(hdr, 8, 4, f) == 4;
+  hdr[5] = 0;
+  if (xadj_fingerprint(ctx, &hdr[4]) != SKW_OK) {
+    fclose(f);
+    return SKW_ERR_CUDA;
+  }
+  bool ok = fwrite(hdr, 8, 6, f) == 6;
   const size_t chunk = 64u << 20;  // staged through a bounded host buffer
   std::vector<unsigned char> buf(chunk);
   auto dump = [&](const void* dptr, size_t bytes) {
@@ -561,14 +683,19 @@ int skw_alias_load(skw_ctx* ctx, const char* path) {
     FILE* f;
     ~Closer() { fclose(f); }
   } closer{f};
-  uint64_t hdr[4];
-  if (fread(hdr, 8, 4, f) != 4 || memcmp(&hdr[0], kTableMagic, 8) != 0)
+  uint64_t hdr[6];
+  if (fread(hdr, 8, 6, f) != 6 || memcmp(&hdr[0], kTableMagic, 8) != 0)
     return fail(ctx, SKW_ERR_IO, "skw_alias_load: %s is not a table checkpoint", path);
   if (hdr[1] != ctx->V || hdr[2] != ctx->E || hdr[3] != sizeof(Slot))
     return fail(ctx, SKW_ERR_IO, "skw_alias_load: %s holds a table for V=%llu E=%llu, the resident graph has V=%u E=%llu",
                 path, (unsigned long long)hdr[1], (unsigned long long)hdr[2], ctx->V, (unsigned long long)ctx->E);
+  uint64_t fp = 0;
+  int rc = xadj_fingerprint(ctx, &fp);
+  if (rc != SKW_OK) return rc;
+  if (hdr[4] != fp)
+    return fail(ctx, SKW_ERR_IO, "skw_alias_load: %s was written for another graph (same V and E, different offsets)", path);
   drop_records(ctx);
-  int rc = alloc_table(ctx);
+  rc = alloc_table(ctx);
   if (rc != SKW_OK) return rc;
   ctx->table_ready = false;
   const size_t chunk = 64u << 20;
@@ -585,6 +712,7 @@ int skw_alias_load(skw_ctx* ctx, const char* path) {
   };
   if ((rc = fill(ctx->slots, sizeof(Slot) * ctx->E)) != SKW_OK) return rc;
   if ((rc = fill(ctx->valid, ctx->V)) != SKW_OK) return rc;
+  if ((rc = validate_table(ctx, "skw_alias_load")) != SKW_OK) return rc;
   ctx->table_ready = true;
   return SKW_OK;
 }

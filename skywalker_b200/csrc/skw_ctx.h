@@ -54,6 +54,7 @@ struct skw_ctx {
   void* records = nullptr;
   void* vinfo = nullptr;
   void* vbits = nullptr;  // one bit per vertex: usable degree != 0
+  bool records_ready = false;  // set once records, vinfo and vbits were all written
 
   // device error word (4 x u32) and its pinned host mirror
   uint32_t* d_err = nullptr;

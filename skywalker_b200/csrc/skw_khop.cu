@@ -71,8 +71,12 @@ __global__ void __launch_bounds__(256) khop_hop_kernel(const KhopArgs a) {
             const Slot sl = load_slot(a.slots + (u64)off + col);
             if (!(sl.prob < 0.0f)) {
               const u32 cand = u01(r.y) < sl.prob ? col : sl.alias;
-              out = ldg_once(a.adjncy + (u64)off + cand);
-              got = a.fanout;
+              if (cand >= deg) {  // a table that does not belong to this graph
+                dev_fail(a.err, DEV_ERR_INDEX, v, cand, 23);
+              } else {
+                out = ldg_once(a.adjncy + (u64)off + cand);
+                got = a.fanout;
+              }
             }
           }
         }

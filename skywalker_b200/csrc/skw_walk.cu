@@ -14,6 +14,7 @@
 // word x -> column (multiply-high by the degree), y -> acceptance uniform, z -> PPR stop test,
 // w -> node2vec rejection uniform.
 #include <algorithm>
+#include <string>
 
 #include <cub/device/device_scan.cuh>
 #include <cub/iterator/transform_input_iterator.cuh>
@@ -47,6 +48,10 @@ __device__ __forceinline__ bool walk_step(const WalkArgs& a, u64 gw, u32 step, u
         const Slot s = load_slot(a.slots + (u64)off + col);
         if (s.prob < 0.0f) return false;  // vertex without usable weight
         cand = u01(r.y) < s.prob ? col : s.alias;
+        if (cand >= deg) {  // a table that does not belong to this graph
+          dev_fail(a.err, DEV_ERR_INDEX, cur, cand, 20);
+          return false;
+        }
       }
       next = ldg_once(a.adjncy + (u64)off + cand);
       const float f = next == prev ? a.inv_p : (connected(a.xadj, a.adjncy, prev, next) ? 1.0f : a.inv_q);
@@ -62,6 +67,10 @@ __device__ __forceinline__ bool walk_step(const WalkArgs& a, u64 gw, u32 step, u
     const Slot s = load_slot(a.slots + (u64)off + col);
     if (s.prob < 0.0f) return false;
     cand = u01(r.y) < s.prob ? col : s.alias;
+    if (cand >= deg) {
+      dev_fail(a.err, DEV_ERR_INDEX, cur, cand, 20);
+      return false;
+    }
   }
   next = ldg_once(a.adjncy + (u64)off + cand);
   return true;
@@ -203,38 +212,85 @@ __global__ void __launch_bounds__(256) vertex_info_kernel(const u32* __restrict_
   }
 }
 
-// One thread per edge slot e: find the first-edge offset of its source vertex by binary search
-// in xadj, then gather both outcomes.
+// One thread per edge slot, a CTA per tile of kRecTile consecutive slots.  The source vertex of a
+// slot is found in two levels: two threads bisect the whole offset array for the tile's first and
+// last slot, the offsets of the vertices in between are copied to shared memory (a tile of 2048
+// slots spans 75 vertices on average on the R-MAT graphs, empty ones included), and every thread
+// bisects that copy.  A tile that spans more vertices than the copy holds (long runs of empty
+// vertices) bisects the global array inside the tile's vertex range instead.
+constexpr u32 kRecTile = 2048, kRecSpan = 4096;
+__device__ __forceinline__ u32 last_vertex_at_or_before(const u32* __restrict__ xadj, u32 lo, u32 hi, u32 e) {
+  while (lo < hi) {  // last v in [lo, hi] with xadj[v] <= e
+    const u32 mid = lo + ((hi - lo + 1) >> 1);
+    if (__ldg(xadj + mid) <= e) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
 __global__ void __launch_bounds__(256) walk_records_kernel(const u32* __restrict__ xadj,
                                                            const u32* __restrict__ adjncy,
                                                            const Slot* __restrict__ slots,
                                                            const uint2* __restrict__ vinfo, u32 V,
-                                                           u64 E, WalkRecord* __restrict__ rec) {
-  for (u64 e = (u64)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (u64)gridDim.x * blockDim.x) {
-    u32 lo = 0, hi = V;  // last v with xadj[v] <= e
-    while (lo < hi) {
-      const u32 mid = lo + ((hi - lo + 1) >> 1);
-      if (__ldg(xadj + mid) <= (u32)e) lo = mid;
-      else hi = mid - 1;
+                                                           u64 E, WalkRecord* __restrict__ rec,
+                                                           u32* __restrict__ err) {
+  __shared__ u32 s_x[kRecSpan + 1];
+  __shared__ u32 s_v[2];
+  const u64 tiles = (E + kRecTile - 1) / kRecTile;
+  for (u64 tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const u64 e0 = tile * kRecTile;
+    const u64 e1 = e0 + kRecTile < E ? e0 + kRecTile : E;
+    if (threadIdx.x < 2)
+      s_v[threadIdx.x] = last_vertex_at_or_before(xadj, 0, V - 1, threadIdx.x ? (u32)(e1 - 1) : (u32)e0);
+    __syncthreads();
+    const u32 v0 = s_v[0], v1 = s_v[1];
+    const bool staged = v1 - v0 < kRecSpan;
+    if (staged)
+      for (u32 i = threadIdx.x; i <= v1 - v0 + 1; i += blockDim.x) s_x[i] = __ldg(xadj + v0 + i);
+    __syncthreads();
+    for (u64 e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+      u32 off, deg;
+      if (staged) {
+        u32 lo = 0, hi = v1 - v0;
+        while (lo < hi) {
+          const u32 mid = lo + ((hi - lo + 1) >> 1);
+          if (s_x[mid] <= (u32)e) lo = mid;
+          else hi = mid - 1;
+        }
+        off = s_x[lo];
+        deg = s_x[lo + 1] - off;
+      } else {
+        const u32 v = last_vertex_at_or_before(xadj, v0, v1, (u32)e);
+        off = __ldg(xadj + v);
+        deg = __ldg(xadj + v + 1) - off;
+      }
+      Slot s = load_slot(slots + e);
+      if (s.alias >= deg) {  // a table that does not belong to this graph: keep the read inside the list
+        dev_fail(err, DEV_ERR_INDEX, (u32)e, s.alias, 22);
+        s.alias = 0;
+      }
+      const u32 n_self = __ldg(adjncy + e);
+      const u32 n_alias = __ldg(adjncy + (u64)off + s.alias);
+      uint2 i_self = make_uint2(0u, 0u), i_alias = make_uint2(0u, 0u);
+      if (n_self < V && n_alias < V) {
+        i_self = __ldg(vinfo + n_self);
+        i_alias = __ldg(vinfo + n_alias);
+      } else {
+        dev_fail(err, DEV_ERR_INDEX, (u32)e, n_self, n_alias);
+      }
+      uint4 a, b;
+      a.x = __float_as_uint(s.prob);
+      a.y = n_self;
+      a.z = i_self.x;
+      a.w = i_self.y;
+      b.x = n_alias;
+      b.y = i_alias.x;
+      b.z = i_alias.y;
+      b.w = s.alias;
+      uint4* out = reinterpret_cast<uint4*>(rec + e);
+      out[0] = a;
+      out[1] = b;
     }
-    const u32 off = __ldg(xadj + lo);
-    const Slot s = load_slot(slots + e);
-    const u32 n_self = __ldg(adjncy + e);
-    const u32 n_alias = __ldg(adjncy + (u64)off + s.alias);
-    const uint2 i_self = __ldg(vinfo + n_self);
-    const uint2 i_alias = __ldg(vinfo + n_alias);
-    uint4 a, b;
-    a.x = __float_as_uint(s.prob);
-    a.y = n_self;
-    a.z = i_self.x;
-    a.w = i_self.y;
-    b.x = n_alias;
-    b.y = i_alias.x;
-    b.z = i_alias.y;
-    b.w = s.alias;
-    uint4* out = reinterpret_cast<uint4*>(rec + e);
-    out[0] = a;
-    out[1] = b;
+    __syncthreads();
   }
 }
 
@@ -537,25 +593,43 @@ int skw_walk_records_build(skw_ctx* ctx, float* ms) {
   if (!ctx) return SKW_ERR_ARG;
   if (!ctx->table_ready) return fail(ctx, SKW_ERR_STATE, "skw_walk_records_build: build or import the alias table first");
   DeviceGuard g(ctx->device);
-  if (!ctx->records) SKW_CUDA(ctx, cudaMalloc(&ctx->records, sizeof(WalkRecord) * (ctx->E ? ctx->E : 1)));
-  if (!ctx->vinfo) SKW_CUDA(ctx, cudaMalloc(&ctx->vinfo, sizeof(uint2) * ((size_t)ctx->V + 1)));
-  if (!ctx->vbits) SKW_CUDA(ctx, cudaMalloc(&ctx->vbits, sizeof(u32) * ((size_t)ctx->V / 32 + 1)));
-  cudaStream_t st = ctx->stream;
-  SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
-  const int grid = ctx->sm_count * 16;
-  if (ctx->V) {
-    vertex_info_kernel<<<grid, 256, 0, st>>>(ctx->xadj, ctx->slots, ctx->V, static_cast<uint2*>(ctx->vinfo),
-                                              static_cast<u32*>(ctx->vbits));
-    SKW_LAUNCHED(ctx);
+  ctx->records_ready = false;
+  // any failure below leaves no half-built records behind
+  auto body = [&]() -> int {
+    if (!ctx->records) SKW_CUDA(ctx, cudaMalloc(&ctx->records, sizeof(WalkRecord) * (ctx->E ? ctx->E : 1)));
+    if (!ctx->vinfo) SKW_CUDA(ctx, cudaMalloc(&ctx->vinfo, sizeof(uint2) * ((size_t)ctx->V + 1)));
+    if (!ctx->vbits) SKW_CUDA(ctx, cudaMalloc(&ctx->vbits, sizeof(u32) * ((size_t)ctx->V / 32 + 1)));
+    int rc = err_reset(ctx);
+    if (rc != SKW_OK) return rc;
+    cudaStream_t st = ctx->stream;
+    SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+    if (ctx->V) {
+      vertex_info_kernel<<<ctx->sm_count * 16, 256, 0, st>>>(ctx->xadj, ctx->slots, ctx->V,
+                                                              static_cast<uint2*>(ctx->vinfo), static_cast<u32*>(ctx->vbits));
+      SKW_LAUNCHED(ctx);
+    }
+    if (ctx->E && ctx->V) {
+      const u64 tiles = (ctx->E + kRecTile - 1) / kRecTile;
+      const u64 cap = (u64)ctx->sm_count * 32;
+      walk_records_kernel<<<(unsigned)(tiles < cap ? tiles : cap), 256, 0, st>>>(
+          ctx->xadj, ctx->adjncy, ctx->slots, static_cast<const uint2*>(ctx->vinfo), ctx->V, ctx->E,
+          static_cast<WalkRecord*>(ctx->records), ctx->d_err);
+      SKW_LAUNCHED(ctx);
+    }
+    SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+    if ((rc = err_check(ctx, "skw_walk_records_build")) != SKW_OK) return rc;  // synchronises the stream
+    if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+    return SKW_OK;
+  };
+  const int rc = body();
+  if (rc != SKW_OK) {
+    const std::string why = ctx->err;
+    cudaGetLastError();
+    drop_records(ctx);
+    ctx->err = why;
+    return rc;
   }
-  if (ctx->E) {
-    walk_records_kernel<<<grid, 256, 0, st>>>(ctx->xadj, ctx->adjncy, ctx->slots, static_cast<const uint2*>(ctx->vinfo),
-                                              ctx->V, ctx->E, static_cast<WalkRecord*>(ctx->records));
-    SKW_LAUNCHED(ctx);
-  }
-  SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
-  SKW_CUDA(ctx, cudaStreamSynchronize(st));
-  if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+  ctx->records_ready = true;
   return SKW_OK;
 }
 
@@ -612,6 +686,7 @@ int skw_walk_records_free(skw_ctx* ctx) {
   ctx->records = nullptr;
   ctx->vinfo = nullptr;
   ctx->vbits = nullptr;
+  ctx->records_ready = false;
   return SKW_OK;
 }
 
@@ -683,7 +758,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
     SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
   }
   if (n) {
-    if (!online && !unbiased && ctx->records && prm->app != SKW_APP_NODE2VEC) {
+    if (!online && !unbiased && ctx->records_ready && prm->app != SKW_APP_NODE2VEC) {
       RecordWalkArgs ra;
       ra.rec = static_cast<const WalkRecord*>(ctx->records);
       ra.vinfo = static_cast<const uint2*>(ctx->vinfo);

@@ -677,3 +677,88 @@ def test_packed_result_sliced_pipeline(ctx, oracle, rmat16):
         with pytest.raises(SkwError) as e:
             ctx.walk_packed(starts, 21, app=APP_PPR, tp=0.3, seed=8, walker_base=11, packed=small, lengths=lens2)
         assert str(cells) in str(e.value) and np.array_equal(lens2, olens)
+
+
+def test_malformed_csr_is_refused(ctx, rmat12):
+    """A CSR with decreasing offsets or a destination >= V is refused at upload / adopt with an error
+    code (no kernel ever indexes with it), and the context stays usable."""
+    import torch
+    from skywalker_b200.api import SkwError
+    g = rmat12
+    bad_x = g.xadj.copy()
+    bad_x[5], bad_x[6] = bad_x[6] + 3, bad_x[5]            # offsets go down
+    with pytest.raises(SkwError) as e:
+        ctx.upload(bad_x, g.adjncy, g.adjwgt)
+    assert e.value.code == -1
+    bad_a = g.adjncy.copy()
+    bad_a[len(bad_a) // 2] = g.V + 7                       # destination out of range
+    with pytest.raises(SkwError) as e:
+        ctx.upload(g.xadj, bad_a, g.adjwgt)
+    assert e.value.code == -1
+    d_x = torch.from_numpy(g.xadj.astype(np.int32)).cuda()
+    d_a = torch.from_numpy(bad_a.astype(np.int64).astype(np.int32)).cuda()
+    with pytest.raises(SkwError) as e:
+        ctx.adopt_device(g.V, g.E, d_x, d_a)
+    assert e.value.code == -1
+    with pytest.raises(SkwError):                          # nothing resident after a refusal
+        ctx.alias_build_offline()
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    paths, lens, _, _ = ctx.walk(np.asarray([1], np.uint32), 5)
+    assert paths[0, 0] == 1
+
+
+def test_foreign_or_corrupt_table_is_refused(ctx, oracle, rmat12, tmp_path):
+    """Tables that do not fit the resident graph: an imported alias outside its list, a checkpoint of
+    another graph with the same V and E, a checkpoint with a corrupted slot."""
+    from skywalker_b200.api import SkwError
+    g = rmat12
+    _upload(ctx, g)
+    prob, alias, valid = oracle.alias_build(g.xadj, g.adjwgt)
+    bad = alias.copy()
+    v = int(np.argmax(np.diff(g.xadj.astype(np.int64)) > 3))
+    bad[g.xadj[v]] = 1 << 20
+    with pytest.raises(SkwError) as e:
+        ctx.alias_import(prob, bad, valid)
+    assert e.value.code == -1
+    with pytest.raises(SkwError):                          # the refused table is not usable
+        ctx.walk(np.zeros(2, np.uint32), 3)
+    ctx.alias_import(prob, alias, valid)
+    path = str(tmp_path / "t.skw")
+    ctx.alias_save(path)
+    # same V and E, other offsets: move one edge from vertex a to vertex b
+    deg = np.diff(g.xadj.astype(np.int64))
+    a = int(np.argmax(deg > 2))
+    x2 = g.xadj.astype(np.int64).copy()
+    if a + 1 < g.V:
+        x2[a + 1] -= 1                                      # vertex a loses its last edge to a + 1
+    ctx.upload(x2.astype(np.uint32), g.adjncy, g.adjwgt)
+    with pytest.raises(SkwError) as e:
+        ctx.alias_load(path)
+    assert "another graph" in str(e.value)
+    # right graph, one slot of the file overwritten with an alias far outside its list
+    _upload(ctx, g)
+    raw = bytearray(open(path, "rb").read())
+    slot0 = 48 + 8 * int(g.xadj[v])
+    raw[slot0 + 4:slot0 + 8] = (0x7FFFFFF0).to_bytes(4, "little")
+    open(path, "wb").write(bytes(raw))
+    with pytest.raises(SkwError) as e:
+        ctx.alias_load(path)
+    assert e.value.code == -1
+
+
+def test_walk_over_a_partly_built_table_ends_at_unbuilt_vertices(ctx, oracle, rmat12):
+    """After a build of a vertex slice only, walkers that reach a vertex outside the slice stop
+    there (its slots still say "no table"), they do not read garbage."""
+    g = rmat12
+    _upload(ctx, g)
+    half = g.V // 2
+    ctx.alias_build_offline(0, half)
+    starts = oracle.gen_starts(2000, g.V, 8)
+    paths, lens, _, _ = ctx.walk(starts, 21, seed=3)
+    prob, alias, valid = oracle.alias_build(g.xadj, g.adjwgt)
+    valid2 = valid.copy()
+    valid2[half:] = 0
+    op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, (prob, alias, valid2), starts, 21, seed=3)
+    _cmp_walks(paths, lens, op, ol)
+    assert (ol < 20).any() and (ol == 20).any()

@@ -55,6 +55,29 @@ def test_static_scratch_builder_matches_regular_builder(ctx):
         assert valid == rvalid == 1
         assert np.array_equal(alias, ralias)
         assert np.array_equal(prob.view(np.uint32), rprob.view(np.uint32))
+    # short lists around every internal boundary (warp, tile of 1024 threads), with zeros, denormals
+    # and one dominant weight mixed in
+    for n in (1, 2, 4, 31, 33, 256, 257, 1024, 1025, 4096, 4097, 16385):
+        w = rng.uniform(1, 10, n).astype(np.float32)
+        if n >= 4:
+            w[rng.integers(0, n, n // 4)] = 0.0
+            w[rng.integers(0, n)] = 1e-42               # denormal
+            w[rng.integers(0, n)] = 3.0e7               # dominates the list
+        w[0] = max(w[0], 1.0)
+        rc, msg, prob, alias, valid = _static(lib, w)
+        assert rc == 0, msg
+        rprob, ralias, rvalid = _regular(ctx, w)
+        assert valid == rvalid == 1, n
+        assert np.array_equal(alias, ralias), n
+        assert np.array_equal(prob.view(np.uint32), rprob.view(np.uint32)), n
+    # output buffers that are not device memory are refused before anything is launched
+    host_slots = np.zeros((8, 2), np.int32)
+    d_w = torch.ones(8, device="cuda")
+    d_valid = torch.zeros(1, dtype=torch.uint8, device="cuda")
+    err = C.create_string_buffer(256)
+    rc = lib.skw_alias_build_list_static(C.c_void_p(d_w.data_ptr()), 8, C.c_void_p(host_slots.ctypes.data),
+                                         C.c_void_p(d_valid.data_ptr()), C.c_void_p(0), err, 256)
+    assert rc == -1 and b"d_slots" in err.value
     # a list without usable weight: flagged, every slot marked
     rc, msg, prob, alias, valid = _static(lib, np.zeros(40, np.float32))
     assert rc == 0 and valid == 0 and (prob == -1.0).all()
