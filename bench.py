@@ -48,6 +48,10 @@ WORKLOADS = {
     "dw26": dict(graph="rmat", scale=26, edge_factor=28, kind="walk", mode="offline", units=8000000, length=80,
                  app="deepwalk", tp=0.0,
                  desc="biased offline DeepWalk, R-MAT scale 26 (~1.8G directed edges), 8M walkers x 80"),
+    "dw22": dict(graph="rmat", scale=22, edge_factor=16, kind="walk", mode="offline", units=1000000, length=80,
+                 app="deepwalk", tp=0.0,
+                 desc="biased offline DeepWalk on the graph of configuration 2 (R-MAT scale 22), 1M walkers x 80: the "
+                      "reduced DeepWalk case for profiling and for the reference's own kernel"),
     "c5s": dict(graph="rmat", scale=22, edge_factor=28, kind="walk", mode="offline", units=1000000, length=100,
                 app="ppr", tp=0.15, desc="reduced config 5 for profiling: PPR on R-MAT scale 22, 1M walkers"),
 }
@@ -240,6 +244,29 @@ def cpu_leg(host, wl, threads, want_seconds=12.0, steps=1, warmup=0, build_weigh
             "alias_build_edges_per_s": build_eps, "seconds": t_run, "edges": edges}
 
 
+def reference_cuda_leg(host, wl, hop, device):
+    """The reference's OWN offline walk kernel (sample_kernel_static through OfflineWalk) on this
+    workload's graph, start vertices and GPU-built table: throughput by the reference's own timer.  Only
+    for offline DeepWalk on graphs small enough to hand over through host arrays; its walks come from
+    another random stream, so only the rate is comparable."""
+    from oracle import oracle as O
+    from oracle import reference_kernel as R
+    if not R.available():
+        return {"unavailable": "oracle/_ref/libskw_ref.so was not built (no reference tree on the build machine)"}
+    V, E = len(host["xadj"]) - 1, int(host["xadj"][-1])
+    if wl["kind"] != "walk" or wl["mode"] != "offline" or wl.get("app") != "deepwalk" or E > (1 << 28):
+        return {"unavailable": "the reference's static offline kernel covers offline DeepWalk only (no stop rule, no "
+                               "node2vec); run --workload c1, c2 or dw22"}
+    n = wl["units"]
+    starts = O.gen_starts(n, V, START_SEED)
+    paths, lens, sec = R.offline_walk(host["xadj"], host["adjncy"], host["table"], starts, hop, device=device, repeats=3)
+    edges = int(lens.sum())
+    return {"kernel": "sample_kernel_static via OfflineWalk (src/offline_walk.cu:75-124, 181-230)", "value": edges / sec,
+            "unit": "sampled edges/s", "seconds": sec, "sampled_edges": edges, "walkers": n,
+            "note": "best of 3 runs, the reference's own wall-clock timer around its launch (cuRAND XORWOW set-up "
+                    "per thread included, as in the reference); table built by this library"}
+
+
 PARITY_WALKERS, PARITY_SEEDS = 10000, 2048
 
 
@@ -316,6 +343,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the bit-comparison with the CPU oracle")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip the reference's own CUDA walk kernel")
     ap.add_argument("--no-records", action="store_true", help="walk over the 8-byte slot table only")
     ap.add_argument("--cpu-threads", type=int, default=0)
     args = ap.parse_args()
@@ -621,7 +649,7 @@ def main():
     # Parity at the workload's own size, on every rank: the first K units of the rank's shard against the
     # CPU oracle (bit for bit), verdicts AND-reduced.  The oracle needs the graph (and table) on the host;
     # ranks take turns in waves sized by the host memory that is free.
-    cpu, parity = None, None
+    cpu, parity, ref_cuda = None, None, None
     need = host_copy_bytes(V, E, online) + (4 * E if world == 1 and not online else 0)
     avail = host_memory_available()
     at_once = world if avail is None else int(min(world, (0.6 * avail) // need))
@@ -644,6 +672,11 @@ def main():
                 if rank == 0 and world == 1 and not args.no_cpu_baseline:
                     cpu = cpu_leg(host, wl, args.cpu_threads, build_weights=host["build_weights"])
                     cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample", "alias_build_edges_per_s")}
+                if rank == 0 and world == 1 and not args.no_reference_cuda:
+                    try:
+                        ref_cuda = reference_cuda_leg(host, wl, hop, local_rank)
+                    except Exception as e:      # never lose the bench line to the comparison arm
+                        ref_cuda = {"unavailable": "failed: %s" % e}
                 del host
             if dist is not None:
                 dist.barrier()
@@ -704,7 +737,7 @@ def main():
                                  "accesses this GPU sustains whatever their size (8-128 B), so sampled edges per "
                                  "probe access, not the byte fraction, says how close the step kernel is to the "
                                  "hardware"},
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "cpu_baseline": cpu, "reference_cuda": ref_cuda, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "result_gather_ms": gather_ms, "result_gather": gather_note,
         }
         print(json.dumps(out))

@@ -68,6 +68,14 @@ typedef enum skw_mode {
 #define SKW_KHOP_UNBIASED 2u /* uniform draws with replacement, no table (--bias=0,            *
                               * src/unbiased_sample.cu:28-36); `mode` is ignored               */
 
+#define SKW_KHOP_DISTINCT 4u /* the rule of the reference's ONLINE sampler (roll_atomic / roll_once,   *
+                             * src/online_sample_new.cu:73-111, 3-37): a vertex whose degree is <=   *
+                             * the fan-out hands over every neighbour once; otherwise a draw counts  *
+                             * only if its column was not drawn before, for at most 352 numbered     *
+                             * trials (32 lanes x 11 rounds there); sample_lengths holds how many    *
+                             * distinct neighbours were found.  Fan-outs up to 256.  Ignored with    *
+                             * SKW_KHOP_UNBIASED.                                                    */
+
 #define SKW_INVALID_VERTEX 0xFFFFFFFFu /* written into k-hop cells that hold no sample */
 
 /* ---------------------------------------------------------------- context ---------------- */
@@ -289,7 +297,8 @@ int skw_khop_layout(const skw_khop_params* prm, uint32_t* cells_per_seed,
  * data[s * cells + offset(h) + idx]: the child number j of the vertex at (hop h, idx) is at
  * (hop h+1, idx * fanout[h+1] + j) (include/sampler_result.cuh:334-352, 421-426);
  * sample_lengths[s * lens + offset(h) + idx] = children actually sampled from that vertex.
- * Draws are with replacement.  Cells without a sample hold SKW_INVALID_VERTEX. */
+ * Draws are with replacement unless SKW_KHOP_DISTINCT is set.  Cells without a sample hold
+ * SKW_INVALID_VERTEX. */
 int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds,
                            uint64_t n, uint32_t* d_data, uint32_t* d_sample_lengths, float* ms,
                            uint64_t* sampled_edges);

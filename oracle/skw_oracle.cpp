@@ -354,6 +354,17 @@ void orc_walk(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
 // fanout[h+1] neighbours with replacement from its table; with take_all, a vertex whose degree
 // is <= the fan-out contributes each neighbour once instead (120-128).  Cells without a sample
 // hold 0xFFFFFFFF.  fanout[0..nhops-1] are the reference's hops[1..].
+//
+// flags & 4 (distinct): the rule of the reference's ONLINE sampler, roll_atomic / roll_once
+// (src/online_sample_new.cu:73-111, 3-37): a vertex whose degree is <= the fan-out contributes every
+// neighbour once; otherwise columns are drawn from the table and a draw counts only if its column was
+// not drawn before, until fan-out distinct columns are found or the trials run out.  The reference
+// lets the 32 lanes of a warp draw at once for at most 11 rounds, in whatever order the atomics land;
+// here the 352 trials are numbered (trial t = lane + 32 * round) and taken in that order, each with
+// its own Philox words keyed by (seed id, parent index, trial, hop), so the result is reproducible.
+// The sample length is the number of distinct columns found.
+enum { KHOP_DISTINCT_TRIALS = 352 };  // 32 lanes x 11 rounds (src/online_sample_new.cu:86-96)
+
 void orc_khop(const u32* xadj, const u32* adjncy, const float* adjwgt, const float* prob,
               const u32* alias, const uint8_t* valid, int online, u32 nhops, const u32* fanout,
               u32 flags, u64 seed, u64 instance_base, u64 instance_stride, const u32* seeds, u64 n,
@@ -393,7 +404,9 @@ void orc_khop(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
             ok = deg > 0;
           }
           if (ok) {
-            if ((flags & 1u) && f >= deg) {
+            // distinct draws are a rule of the biased sampler; with the unbiased flag it is ignored
+            const bool distinct = (flags & 4u) && !(flags & 2u);
+            if (((flags & 1u) || distinct) && f >= deg) {
               for (u32 j = 0; j < deg; ++j) child[j] = adjncy[off + j];
               got = deg;
             } else if (flags & 2u) {  // unbiased: uniform column, no table (src/unbiased_sample.cu:28-36)
@@ -415,7 +428,17 @@ void orc_khop(const u32* xadj, const u32* adjncy, const float* adjwgt, const flo
                 vp = prob + off;
                 va = alias + off;
               }
-              if (ok) {
+              if (ok && distinct) {
+                std::vector<u32> seen;
+                for (u32 t = 0; t < KHOP_DISTINCT_TRIALS && got < f; ++t) {
+                  u32 r[4];
+                  philox_tagged(seed, TAG_KHOP, gi, idx, (t << 8) | 0x80u | (h + 1), r);
+                  const u32 c = alias_draw(vp, va, deg, r[0], r[1]);
+                  if (std::find(seen.begin(), seen.end(), c) != seen.end()) continue;
+                  seen.push_back(c);
+                  child[got++] = adjncy[off + c];
+                }
+              } else if (ok) {
                 for (u32 j = 0; j < f; ++j) {
                   u32 r[4];
                   philox_tagged(seed, TAG_KHOP, gi, idx * f + j, h + 1, r);

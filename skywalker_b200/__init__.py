@@ -6,7 +6,7 @@ path: importing `skywalker_b200.api` without the built library raises ImportErro
 """
 from ._capi import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, INVALID_VERTEX, KHOP_TAKE_ALL, MODE_OFFLINE,
                     MODE_ONLINE, WALK_CACHE_TABLES, WALK_UNBIASED, WALK_BUILD_TABLES, WALK_DIRECT_SLOTS,
-                    KHOP_UNBIASED)
+                    KHOP_UNBIASED, KHOP_DISTINCT)
 
 __all__ = ["APP_DEEPWALK", "APP_NODE2VEC", "APP_PPR", "INVALID_VERTEX", "KHOP_TAKE_ALL", "MODE_OFFLINE",
-           "MODE_ONLINE", "WALK_CACHE_TABLES", "WALK_UNBIASED", "WALK_BUILD_TABLES", "WALK_DIRECT_SLOTS", "KHOP_UNBIASED"]
+           "MODE_ONLINE", "WALK_CACHE_TABLES", "WALK_UNBIASED", "WALK_BUILD_TABLES", "WALK_DIRECT_SLOTS", "KHOP_UNBIASED", "KHOP_DISTINCT"]

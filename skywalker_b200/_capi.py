@@ -18,6 +18,7 @@ WALK_UNBIASED = 2
 WALK_BUILD_TABLES = 4
 WALK_DIRECT_SLOTS = 8
 KHOP_UNBIASED = 2
+KHOP_DISTINCT = 4
 INVALID_VERTEX = 0xFFFFFFFF
 
 

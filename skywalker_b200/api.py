@@ -20,7 +20,7 @@ import numpy as np
 
 from . import _capi
 from ._capi import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, INVALID_VERTEX, KHOP_TAKE_ALL,
-                    MODE_OFFLINE, MODE_ONLINE, WALK_CACHE_TABLES, WALK_UNBIASED, KHOP_UNBIASED, KhopParams,
+                    MODE_OFFLINE, MODE_ONLINE, WALK_CACHE_TABLES, WALK_UNBIASED, KHOP_UNBIASED, KHOP_DISTINCT, KhopParams,
                     WalkParams)
 
 
@@ -451,9 +451,11 @@ def OfflineSample(sampler):
     return _sample(sampler, MODE_OFFLINE)
 
 
-def OnlineGBSampleNew(sampler):
-    """src/online_sample_new.cu:459-547."""
-    return _sample(sampler, MODE_ONLINE)
+def OnlineGBSampleNew(sampler, with_replacement=False):
+    """src/online_sample_new.cu:459-547.  The reference's online sampler keeps only draws of columns it
+    has not drawn before (roll_atomic, src/online_sample_new.cu:73-111): KHOP_DISTINCT.
+    with_replacement=True gives independent draws instead (sampler.flags then apply as they are)."""
+    return _sample(sampler, MODE_ONLINE, 0 if with_replacement else KHOP_DISTINCT)
 
 
 def UnbiasedSample(sampler):

@@ -163,6 +163,7 @@ void define_flags() {
   def("records", Flag::BOOL, "false");
   def("batches", Flag::INT, "1");
   def("gather", Flag::BOOL, "true");
+  def("replacement", Flag::BOOL, "false");
 }
 
 #define LOGV(...)                      \
@@ -192,6 +193,8 @@ struct Shared {
   std::vector<ncclComm_t> comms;
 #endif
   std::vector<uint32_t> gathered_lengths;  // rank 0 fills it when --gather
+  std::vector<uint32_t> gathered_paths;    // and the path rows, device by device
+  int gather_rows = 0;                     // GPU 0's decision whether the rows fit beside its own data
 };
 
 int fail_dev(DevResult& r, skw_ctx* ctx, int rc, const char* what) {
@@ -382,8 +385,11 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     p.nhops = (uint32_t)sh.depth;
     if (p.nhops > 4) return fail_dev(out, nullptr, SKW_ERR_ARG, "k-hop sampling supports --d up to 4");
     for (uint32_t h = 0; h < p.nhops; ++h) p.fanout[h] = sh.hops[h + 1];
-    // the reference copies all neighbours when fan-out >= degree; --bias=0 draws uniformly
+    // the reference copies all neighbours when fan-out >= degree; its online sampler also keeps only
+    // draws of columns not drawn before (src/online_sample_new.cu:73-111) unless --replacement asks for
+    // independent draws; --bias=0 draws uniformly
     p.flags = SKW_KHOP_TAKE_ALL | (bias ? 0 : SKW_KHOP_UNBIASED);
+    if (online && bias && !fb("replacement")) p.flags |= SKW_KHOP_DISTINCT;
     p.seed = (uint64_t)fi("seed");
     uint32_t cells, lens;
     if (skw_khop_layout(&p, &cells, &lens)) return fail_dev(out, nullptr, SKW_ERR_ARG, "bad --k/--d for k-hop sampling");
@@ -427,16 +433,38 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     if (dev == 0) cudaMalloc(&d_all, sizeof(uint32_t) * cnt * sh.ndev);
     cudaStream_t st;
     cudaStreamCreate(&st);
+    // the path rows too (n_local x hop_num per device), when they fit beside GPU 0's own data
+    const size_t row_cnt = cnt * (size_t)(fi("d") + 1);
+    size_t free_b = 0, total_b = 0;
+    if (dev == 0) cudaMemGetInfo(&free_b, &total_b);
+    uint32_t* d_rows_all = nullptr;
+    int rows_too = dev == 0 && free_b > sizeof(uint32_t) * row_cnt * sh.ndev + (1ull << 30) ? 1 : 0;
+    if (dev == 0) sh.gather_rows = rows_too;
+    sh.rv.agree(true);  // every device thread sees GPU 0's decision after this point
+    rows_too = sh.gather_rows;
+    if (rows_too && dev == 0 && cudaMalloc(&d_rows_all, sizeof(uint32_t) * row_cnt * sh.ndev) != cudaSuccess) d_rows_all = nullptr;
     ncclGroupStart();
     ncclSend(d_len, cnt, ncclUint32, 0, sh.comms[dev], st);
     if (dev == 0)
       for (int r = 0; r < sh.ndev; ++r) ncclRecv(d_all + (size_t)r * cnt, cnt, ncclUint32, r, sh.comms[dev], st);
     ncclGroupEnd();
+    if (rows_too) {
+      ncclGroupStart();
+      ncclSend(d_data, row_cnt, ncclUint32, 0, sh.comms[dev], st);
+      if (dev == 0 && d_rows_all)
+        for (int r = 0; r < sh.ndev; ++r) ncclRecv(d_rows_all + (size_t)r * row_cnt, row_cnt, ncclUint32, r, sh.comms[dev], st);
+      ncclGroupEnd();
+    }
     cudaStreamSynchronize(st);
     if (dev == 0) {
       sh.gathered_lengths.resize(cnt * sh.ndev);
       cudaMemcpy(sh.gathered_lengths.data(), d_all, sizeof(uint32_t) * cnt * sh.ndev, cudaMemcpyDeviceToHost);
       cudaFree(d_all);
+      if (d_rows_all) {
+        sh.gathered_paths.resize(row_cnt * sh.ndev);
+        cudaMemcpy(sh.gathered_paths.data(), d_rows_all, sizeof(uint32_t) * row_cnt * sh.ndev, cudaMemcpyDeviceToHost);
+        cudaFree(d_rows_all);
+      }
     }
     cudaStreamDestroy(st);
   }
@@ -533,6 +561,14 @@ int main(int argc, char** argv) {
     for (uint32_t l : sh.gathered_lengths) total += l;
     LOGV("gathered %zu walk lengths on GPU 0 over NCCL, sum %llu\n", sh.gathered_lengths.size(),
          (unsigned long long)total);
+    if (!sh.gathered_paths.empty()) {
+      // every gathered row starts with a vertex and holds length + 1 cells: count them as a check
+      const size_t hop = (size_t)fi("d") + 1;
+      uint64_t cells = 0;
+      for (size_t w = 0; w < sh.gathered_lengths.size(); ++w) cells += std::min<size_t>(sh.gathered_lengths[w] + 1, hop);
+      LOGV("gathered %zu path rows x %zu cells on GPU 0 over NCCL, %llu cells hold a vertex\n",
+           sh.gathered_paths.size() / hop, hop, (unsigned long long)cells);
+    }
   }
   const bool offline_biased = !fb("ol") && fb("bias");
   if (fb("csv")) {

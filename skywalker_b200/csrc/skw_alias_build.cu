@@ -43,18 +43,18 @@ namespace skw {
 // degree classes: groups of 4/8/16/32 lanes; one warp per vertex (two capacities); one CTA of
 // 256 threads with its lists in shared memory; one CTA of 1024 threads with its lists in a
 // global scratch slab, merged through shared-memory windows
-enum { K_G4 = 0, K_G8, K_G16, K_G32, K_W256, K_W1K, K_C, K_C2, K_H, K_CLASSES };
-constexpr u32 kWarpSmallMax = 256;
+enum { K_G1 = 0, K_G2, K_G4, K_G8, K_G16, K_G32, K_W1K, K_C, K_C2, K_H, K_CLASSES };
+constexpr u32 kGroupEpt = 8;          // list elements a lane of a sub-warp group keeps in registers
+constexpr u32 kWarpSmallMax = 32 * kGroupEpt;  // 256: the largest list a whole warp holds in registers
 constexpr u32 kWarpMax = 1024;
 constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 4096: 12 bytes of list state per edge, 4 CTAs per SM
 constexpr u32 kHugeSmemMax = 16384;           // one 1024-thread CTA per SM with 192 KB of lists
 
 __device__ __forceinline__ int degree_class(u32 deg) {
-  if (deg <= 4) return K_G4;
-  if (deg <= 8) return K_G8;
-  if (deg <= 16) return K_G16;
-  if (deg <= 32) return K_G32;
-  if (deg <= kWarpSmallMax) return K_W256;
+  if (deg <= kWarpSmallMax) {  // groups of 1, 2, 4 ... 32 lanes, kGroupEpt elements per lane
+    if (deg <= kGroupEpt) return K_G1;
+    return K_G1 + (32 - __clz((int)((deg - 1) / kGroupEpt)));
+  }
   if (deg <= kWarpMax) return K_W1K;
   if (deg <= kLargeMax) return K_C;
   if (deg <= kHugeSmemMax) return K_C2;
@@ -137,122 +137,6 @@ __global__ void __launch_bounds__(256) classify_fill_kernel(const u32* __restric
     __syncthreads();
     if (c >= 0) worklist[s_base[c] + s_warp[c][warp] + my_rank] = (u32)v;
     __syncthreads();
-  }
-}
-
-// ------------------------------------------------------------------ sub-warp groups --------
-template <int G>
-__device__ __forceinline__ u64 group_sum(u64 x) {
-#pragma unroll
-  for (int o = G / 2; o; o >>= 1) x += __shfl_xor_sync(0xFFFFFFFFu, x, o, G);
-  return x;
-}
-template <int G>
-__device__ __forceinline__ u64 group_scan(u64 x, u32 lane) {
-#pragma unroll
-  for (int o = 1; o < G; o <<= 1) {
-    const u64 t = __shfl_up_sync(0xFFFFFFFFu, x, o, G);
-    if (lane >= (u32)o) x += t;
-  }
-  return x;
-}
-
-// One group of G lanes per vertex of degree <= G; lane i owns edge i.
-template <int G>
-__global__ void __launch_bounds__(256) build_group_kernel(const u32* __restrict__ worklist,
-                                                          const u32* __restrict__ cls, int k,
-                                                          const u32* __restrict__ xadj,
-                                                          const float* __restrict__ wgt,
-                                                          Slot* __restrict__ slots,
-                                                          uint8_t* __restrict__ valid,
-                                                          u32* __restrict__ err) {
-  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
-  const u32 wlane = threadIdx.x & 31;
-  const u32 lane = wlane & (G - 1);
-  const u32 gshift = wlane & ~(u32)(G - 1);
-  const u32 gmask_all = G == 32 ? 0xFFFFFFFFu : ((1u << G) - 1u);
-  const u32 groups_per_warp = 32 / G;
-  const u32 warp_id = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const u32 nwarps = (gridDim.x * blockDim.x) >> 5;
-  constexpr int B = 40;  // degree <= 32 always gives 40 bucket bits
-  const u64 C = (u64)1 << B;
-  for (u64 it0 = (u64)warp_id * groups_per_warp; it0 < count; it0 += (u64)nwarps * groups_per_warp) {
-    const u64 it = it0 + wlane / G;
-    const bool active = it < count;
-    u32 v = 0, off = 0, n = 0;
-    if (active) {
-      v = worklist[base + it];
-      off = xadj[v];
-      n = xadj[v + 1] - off;
-      if (n > G) {  // classification and kernel disagree: record and skip
-        dev_fail(err, DEV_ERR_INTERNAL, v, n, G);
-        n = 0;
-      }
-    }
-    const bool mine = lane < n;
-    const float w = mine ? sane_weight(__ldg(wgt + off + lane)) : 0.0f;
-    float wmax = w;
-#pragma unroll
-    for (int o = G / 2; o; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xFFFFFFFFu, wmax, o, G));
-    const bool usable = wmax > 0.0f;
-    const double scale = weight_scale(usable ? wmax : 1.0f, B);
-    const u64 q = quantise(w, scale);
-    const u64 Qi = group_scan<G>(q, lane);                         // inclusive
-    const u64 W = __shfl_sync(0xFFFFFFFFu, Qi, G - 1, G);
-    const u64 nC = (u64)n << B;
-    const double K = mass_factor(n ? n : 1, B, W ? W : 1);
-    const u64 m = mine ? cum_mass(Qi, W, nC, K) - cum_mass(Qi - q, W, nC, K) : 0;
-    const bool is_small = mine && m < C;
-    const bool is_large = mine && m >= C;
-    const u32 large_mask = (__ballot_sync(0xFFFFFFFFu, is_large) >> gshift) & gmask_all;
-    const u64 d = is_small ? C - m : 0;
-    const u64 x = is_large ? m - C : 0;
-    const u64 Di = group_scan<G>(d, lane);
-    const u64 Xi = group_scan<G>(x, lane);
-    // first lane whose prefix reaches the target: smalls look in X, larges look in D
-    const u64 target = is_small ? Di - d : Xi + 1;
-    u32 pos = 0;
-#pragma unroll
-    for (int s = G / 2; s; s >>= 1) {
-      const u64 ax = __shfl_sync(0xFFFFFFFFu, Xi, pos + s - 1, G);
-      const u64 ad = __shfl_sync(0xFFFFFFFFu, Di, pos + s - 1, G);
-      if ((is_small ? ax : ad) < target) pos += s;
-    }
-    const u64 ax = __shfl_sync(0xFFFFFFFFu, Xi, pos, G);
-    const u64 ad = __shfl_sync(0xFFFFFFFFu, Di, pos, G);
-    const bool found = (is_small ? ax : ad) >= target;
-    if (mine) {
-      Slot out;
-      if (!usable) {
-        out.prob = -1.0f;  // marks a vertex without usable weight for the draw kernels
-        out.alias = lane;
-      } else if (is_small) {
-        // found is guaranteed by mass conservation; the donor is the first large at or after pos
-        const u32 rest = found ? (large_mask >> pos) : 0u;
-        if (!rest) {
-          dev_fail(err, DEV_ERR_INTERNAL, v, lane, 1);
-          out.alias = lane;
-        } else {
-          out.alias = pos + __ffs(rest) - 1;
-        }
-        out.prob = mass_to_prob(m, B);
-      } else if (!found) {
-        out.prob = 1.0f;
-        out.alias = lane;
-      } else {
-        const u32 rest = lane == 31 ? 0u : (large_mask >> (lane + 1));
-        if (!rest) {
-          dev_fail(err, DEV_ERR_INTERNAL, v, lane, 2);
-          out.alias = lane;
-          out.prob = 1.0f;
-        } else {
-          out.alias = lane + __ffs(rest);
-          out.prob = mass_to_prob(Xi + C - ad, B);
-        }
-      }
-      slots[(u64)off + lane] = out;
-      if (lane == 0) valid[v] = usable ? 1 : 0;
-    }
   }
 }
 
@@ -651,24 +535,302 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
   if (t == 0) valid[v] = 1;
 }
 
-// One warp per vertex of degree <= CAP; WPB warps per CTA; lists in dynamic shared memory
-// (12 bytes per edge per warp).
+// ------------------------------------------------------------------ packed lists (n <= 4096) --
+// Lists of at most 4096 elements get a leaner form of the same construction.
+//   * One list entry is one 64-bit word: (prefix key << 12) | position.  With n <= 4096 the bucket
+//     has 40 bits, every prefix stays below 2^52 and a position needs 12 bits, so the merge reads
+//     and compares single words (8 instead of 12 bytes of shared memory per edge).
+//   * Only the deficit prefix D is scanned, with the number of smalls riding in bits 52..63 of the
+//     same word (there is always at least one large, so the count is at most 4095).  The excess prefix
+//     follows from the cumulative mass: sum over k <= p of (M_k - C) = X(p) - D(p), hence
+//     X(p) = D(p) + g(Q_(p+1)) - (p + 1) * C, with g(Q_(p+1)) already at hand.
+//   * Each thread owns EPT consecutive elements of a tile, so the prefix sums are short serial
+//     loops plus one cross-thread scan per tile; when the whole list fits one tile (SINGLE) the
+//     weights are loaded and quantised once and stay in registers, and the scan of the quantised
+//     weights yields their total as well.
+//   * The merge keeps the heads of both lists in registers: one shared-memory load per output.
+constexpr int kPosBits = 12;
+constexpr u64 kPosMask = (1ull << kPosBits) - 1;
+constexpr int kCntShift = 52;
+constexpr u64 kKeyMask = (1ull << kCntShift) - 1;
+constexpr u64 kListEnd = ~0ull;  // stands for "no entry left": its key exceeds every real key
+constexpr u32 kPackedMax = 1u << kPosBits;
+
+// Cooperation inside a group of G lanes of one warp (G = 1, 2, 4 ... 32).  Groups of a warp work on
+// different vertices and may diverge, so every shuffle names only the lanes of its own group.
+template <int G>
+struct GroupCoop {
+  static constexpr int NT = G;
+  u32 mask, t;
+  __device__ __forceinline__ GroupCoop() {
+    const u32 lane = threadIdx.x & 31;
+    t = lane & (G - 1);
+    mask = G == 32 ? 0xFFFFFFFFu : (((1u << G) - 1u) << (lane & ~(u32)(G - 1)));
+  }
+  __device__ __forceinline__ void sync() const { __syncwarp(mask); }
+  __device__ __forceinline__ float max(float v) const {
+#pragma unroll
+    for (int o = G / 2; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(mask, v, o, G));
+    return v;
+  }
+  __device__ __forceinline__ u64 sum(u64 x) const {
+#pragma unroll
+    for (int o = G / 2; o; o >>= 1) x += __shfl_xor_sync(mask, x, o, G);
+    return x;
+  }
+  // v becomes the exclusive prefix over the group, total the group's sum
+  __device__ __forceinline__ void scan(u64& v, u64& total) const {
+    u64 inc = v;
+#pragma unroll
+    for (int o = 1; o < G; o <<= 1) {
+      const u64 x = __shfl_up_sync(mask, inc, o, G);
+      if (t >= (u32)o) inc += x;
+    }
+    total = __shfl_sync(mask, inc, G - 1, G);
+    v = inc - v;
+  }
+};
+
+// Cooperation inside a CTA of NTHREADS threads (s_tmp: NTHREADS / 32 + 1 words of shared memory).
+template <int NTHREADS>
+struct CtaCoop {
+  static constexpr int NT = NTHREADS;
+  u32 t;
+  u64* s_tmp;
+  __device__ __forceinline__ explicit CtaCoop(u64* tmp) : t(threadIdx.x), s_tmp(tmp) {}
+  __device__ __forceinline__ void sync() const { __syncthreads(); }
+  __device__ __forceinline__ float max(float v) const { return coop_max<NTHREADS>(v, reinterpret_cast<float*>(s_tmp)); }
+  __device__ __forceinline__ u64 sum(u64 x) const {
+    u64 total;
+    coop_scan_u64<NTHREADS>(x, total, s_tmp);
+    return total;
+  }
+  __device__ __forceinline__ void scan(u64& v, u64& total) const { coop_scan_u64<NTHREADS>(v, total, s_tmp); }
+};
+
+// Merge of the packed lists: S smalls at A[0 .. S) with key = inclusive deficit prefix, L = n - S
+// larges from the back (large j at A[n - 1 - j]) with key = inclusive excess prefix.  Thread t emits
+// an equal share of the merged order.
+template <int NT>
+__device__ __forceinline__ void merge_packed(u32 t, u32 n, u32 S, const u64* A, u64 C, int B, u32 off,
+                                             Slot* __restrict__ slots, u32 v, u32* err) {
+  const u32 L = n - S;
+  const u32 VT = (n + NT - 1) / NT;
+  const u32 k0 = min(t * VT, n), k1 = min(k0 + VT, n);
+  if (k0 >= k1) return;
+  u32 i;
+  {
+    u32 lo = k0 > L ? k0 - L : 0, hi = min(k0, S);
+    while (lo < hi) {  // small mid precedes large k0-1-mid iff its key (deficit before it) <= that large's key
+      const u32 mid = (lo + hi) >> 1;
+      const u64 a = mid ? (A[mid - 1] >> kPosBits) : 0;
+      const u64 b = A[n - 1 - (k0 - 1 - mid)] >> kPosBits;
+      if (a <= b) lo = mid + 1;
+      else hi = mid;
+    }
+    i = lo;
+  }
+  u32 j = k0 - i;
+  u64 dsx = i ? (A[i - 1] >> kPosBits) : 0;  // deficit of the smalls before small i
+  u64 hs = i < S ? A[i] : kListEnd;          // heads of the two lists
+  u64 hl = j < L ? A[n - 1 - j] : kListEnd;
+  for (u32 k = k0; k < k1; ++k) {
+    Slot out;
+    u32 p;
+    if (i < S && dsx <= (hl >> kPosBits)) {
+      p = (u32)(hs & kPosMask);
+      const u64 dincl = hs >> kPosBits;
+      if (j >= L) {  // mass conservation: the last large is emitted after every small
+        dev_fail(err, DEV_ERR_INTERNAL, v, p, 10);
+        out.alias = p;
+      } else {
+        out.alias = (u32)(hl & kPosMask);
+      }
+      out.prob = mass_to_prob_fast(C - (dincl - dsx), B);
+      dsx = dincl;
+      ++i;
+      hs = i < S ? A[i] : kListEnd;
+    } else {
+      if (j >= L) {  // cannot happen: k < n outputs remain, so one of the lists has an entry
+        dev_fail(err, DEV_ERR_INTERNAL, v, k, 9);
+        break;
+      }
+      p = (u32)(hl & kPosMask);
+      const u64 xl = hl >> kPosBits;
+      const u64 nx = j + 1 < L ? A[n - 2 - j] : kListEnd;
+      if (dsx <= xl) {  // only once every small is placed: the large owns one full bucket
+        out.alias = p;
+        out.prob = 1.0f;
+      } else if (nx == kListEnd) {
+        dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
+        out.alias = p;
+        out.prob = 1.0f;
+      } else {
+        out.alias = (u32)(nx & kPosMask);
+        out.prob = mass_to_prob_fast(xl + C - dsx, B);
+      }
+      ++j;
+      hl = nx;
+    }
+    slots[(u64)off + p] = out;
+  }
+}
+
+// Table of one vertex (degree n <= 4096) by the threads of `co`; A holds n packed list entries.
+// SINGLE: n <= NT * EPT.  STAGED: w points at a copy of the weights in shared memory.
+template <class Coop, int EPT, bool SINGLE, bool STAGED>
+__device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 off, u32 n, const float* w,
+                                                    Slot* __restrict__ slots, uint8_t* __restrict__ valid,
+                                                    u64* A, u32* err) {
+  constexpr int NT = Coop::NT;
+  const u32 t = co.t;
+  auto weight = [&](u32 p) { return sane_weight(STAGED ? w[p] : __ldg(w + p)); };
+  float wr[EPT];
+  float wmax = 0.0f;
+  if constexpr (SINGLE) {
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      const u32 p = t * EPT + k;
+      wr[k] = p < n ? weight(p) : 0.0f;
+      wmax = fmaxf(wmax, wr[k]);
+    }
+  } else {
+    for (u32 p = t; p < n; p += NT) wmax = fmaxf(wmax, weight(p));
+  }
+  wmax = co.max(wmax);
+  if (!(wmax > 0.0f)) {
+    for (u32 p = t; p < n; p += NT) slots[(u64)off + p] = Slot{-1.0f, p};
+    if (t == 0) valid[v] = 0;
+    return;
+  }
+  const int B = bucket_bits(n);
+  const u64 C = (u64)1 << B;
+  const int sh = weight_shift(wmax, B);
+  u64 m[EPT];
+  u64 W = 0, Qex = 0;
+  if constexpr (SINGLE) {
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      m[k] = quantise_bits(wr[k], sh);
+      Qex += m[k];
+    }
+    co.scan(Qex, W);  // one scan gives the prefix of this thread and the total
+  } else {
+    u64 acc = 0;
+    for (u32 p = t; p < n; p += NT) acc += quantise_bits(weight(p), sh);
+    W = co.sum(acc);
+  }
+  const u64 nC = (u64)n << B;
+  const double K = mass_factor(n, B, W);
+  u64 cQ = 0, cPK = 0;  // carries between tiles (the same value in every thread)
+  for (u32 base = 0; base < (SINGLE ? 1u : n); base += NT * EPT) {
+    const u32 p0 = base + t * EPT;
+    if constexpr (!SINGLE) {
+      Qex = 0;
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) {
+        m[k] = p0 + k < n ? quantise_bits(weight(p0 + k), sh) : 0;
+        Qex += m[k];
+      }
+      u64 tq;
+      co.scan(Qex, tq);
+      Qex += cQ;
+      cQ += tq;
+    }
+    const u64 gex = cum_mass(Qex, W, nC, K);  // cumulative mass before this thread's elements
+    u64 g_prev = gex, Q = Qex, pk = 0;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      if (p0 + k < n) {
+        Q += m[k];
+        const u64 g = cum_mass(Q, W, nC, K);
+        m[k] = g - g_prev;
+        g_prev = g;
+        if (m[k] < C) pk += (C - m[k]) + (1ull << kCntShift);
+      }
+    }
+    u64 tpk;
+    co.scan(pk, tpk);
+    pk += cPK;
+    cPK += tpk;
+    u64 Dr = pk & kKeyMask, gc = gex;
+    u32 Sr = (u32)(pk >> kCntShift);  // smalls before this thread's elements
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      const u32 p = p0 + k;
+      if (p < n) {
+        gc += m[k];
+        if (m[k] < C) {
+          Dr += C - m[k];
+          A[Sr++] = (Dr << kPosBits) | p;
+        } else {
+          const u64 X = Dr + gc - ((u64)(p + 1) << B);  // inclusive excess prefix
+          A[n - 1 - (p - Sr)] = (X << kPosBits) | p;
+        }
+      }
+    }
+  }
+  co.sync();
+  const u32 S = (u32)(cPK >> kCntShift);
+  if (S >= n) {  // mass conservation guarantees a large
+    if (t == 0) dev_fail(err, DEV_ERR_INTERNAL, v, S, 7);
+    for (u32 p = t; p < n; p += NT) slots[(u64)off + p] = Slot{1.0f, p};
+    if (t == 0) valid[v] = 1;
+    return;
+  }
+  merge_packed<NT>(t, n, S, A, C, B, off, slots, v, err);
+  if (t == 0) valid[v] = 1;
+}
+
+// Degrees up to 8 * G: one group of G lanes per vertex, 32 / G vertices per warp side by side, the
+// whole list in registers.  Every warp owns 256 list words of shared memory, 8 * G per group.
+template <int G>
+__global__ void __launch_bounds__(256) build_small_kernel(const u32* __restrict__ worklist,
+                                                          const u32* __restrict__ cls, int k,
+                                                          const u32* __restrict__ xadj,
+                                                          const float* __restrict__ wgt,
+                                                          Slot* __restrict__ slots,
+                                                          uint8_t* __restrict__ valid,
+                                                          u32* __restrict__ err) {
+  __shared__ u64 s_lists[8][32 * kGroupEpt];
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  const u32 lane = threadIdx.x & 31;
+  constexpr u32 GPW = 32 / G;  // groups per warp
+  const u32 warp_id = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const u32 nwarps = (gridDim.x * blockDim.x) >> 5;
+  u64* A = s_lists[threadIdx.x >> 5] + (lane / G) * (G * kGroupEpt);
+  const GroupCoop<G> co;
+  for (u64 it0 = (u64)warp_id * GPW; it0 < count; it0 += (u64)nwarps * GPW) {
+    const u64 it = it0 + lane / G;
+    if (it < count) {
+      const u32 v = worklist[base + it];
+      const u32 off = xadj[v], n = xadj[v + 1] - off;
+      if (n > G * kGroupEpt || n == 0) {  // classification and kernel disagree: record and skip
+        if (co.t == 0) dev_fail(err, DEV_ERR_INTERNAL, v, n, G);
+      } else {
+        build_vertex_packed<GroupCoop<G>, (int)kGroupEpt, true, false>(co, v, off, n, wgt + off, slots, valid, A, err);
+      }
+      co.sync();  // the group's list words are reused by its next vertex
+    }
+  }
+}
+
+// Degrees 257 .. 1024: one warp per vertex (tiles of 256 elements), WPB warps per CTA, vertices
+// handed out by an atomic cursor because their cost varies with the degree.
 template <int CAP, int WPB>
-__global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* __restrict__ worklist,
-                                                                    u32* __restrict__ cls, int k,
-                                                                    const u32* __restrict__ xadj,
-                                                                    const float* __restrict__ wgt,
-                                                                    Slot* __restrict__ slots,
-                                                                    uint8_t* __restrict__ valid,
-                                                                    u32* __restrict__ err) {
+__global__ void __launch_bounds__(WPB * 32) build_warp_packed_kernel(const u32* __restrict__ worklist,
+                                                                     u32* __restrict__ cls, int k,
+                                                                     const u32* __restrict__ xadj,
+                                                                     const float* __restrict__ wgt,
+                                                                     Slot* __restrict__ slots,
+                                                                     uint8_t* __restrict__ valid,
+                                                                     u32* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem[];
   const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
   const u32 lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   u64* A = reinterpret_cast<u64*>(smem) + (size_t)wib * CAP;
-  u32* P = reinterpret_cast<u32*>(reinterpret_cast<u64*>(smem) + (size_t)WPB * CAP) + (size_t)wib * CAP;
   u32* cursor = cls + 3 * K_CLASSES + k;
-  // vertices are handed out by an atomic cursor: their cost varies with the degree, so a fixed
-  // stride would leave the slowest warp running alone at the end
+  const GroupCoop<32> co;
   for (;;) {
     u32 it = 0;
     if (lane == 0) it = atomicAdd(cursor, 1u);
@@ -676,12 +838,45 @@ __global__ void __launch_bounds__(WPB * 32) build_warp_merge_kernel(const u32* _
     if (it >= count) break;
     const u32 v = worklist[base + it];
     const u32 off = xadj[v], n = xadj[v + 1] - off;
-    if (n > CAP) {
+    if (n > CAP || n == 0) {
       if (lane == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
       continue;
     }
-    build_vertex_merge<32, 4, 0, false>(lane, v, off, n, wgt + off, slots, valid, A, P, nullptr, nullptr, err);
+    build_vertex_packed<GroupCoop<32>, 8, false, false>(co, v, off, n, wgt + off, slots, valid, A, err);
     __syncwarp();
+  }
+}
+
+// Degrees 1025 .. 4096 when the weight array cannot be bulk-copied (not 16-byte aligned): one CTA
+// of NT threads per vertex, weights read from global memory.
+template <int NT>
+__global__ void __launch_bounds__(NT) build_cta_packed_kernel(const u32* __restrict__ worklist,
+                                                              u32* __restrict__ cls, int k,
+                                                              const u32* __restrict__ xadj,
+                                                              const float* __restrict__ wgt,
+                                                              Slot* __restrict__ slots,
+                                                              uint8_t* __restrict__ valid,
+                                                              u32* __restrict__ err) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ u64 s_tmp[NT / 32 + 1];
+  __shared__ u32 s_it;
+  u64* A = reinterpret_cast<u64*>(smem);
+  const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
+  const CtaCoop<NT> co(s_tmp);
+  for (;;) {
+    if (threadIdx.x == 0) s_it = atomicAdd(cls + 3 * K_CLASSES + k, 1u);
+    __syncthreads();
+    const u32 it = s_it;
+    __syncthreads();
+    if (it >= count) break;
+    const u32 v = worklist[base + it];
+    const u32 off = xadj[v], n = xadj[v + 1] - off;
+    if (n > kPackedMax || n == 0) {
+      if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, kPackedMax);
+      continue;
+    }
+    build_vertex_packed<CtaCoop<NT>, 8, false, false>(co, v, off, n, wgt + off, slots, valid, A, err);
+    __syncthreads();
   }
 }
 
@@ -724,7 +919,8 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
 // The 1025..CAP class with the weight list staged in shared memory by the bulk-copy engine: one
 // cp.async.bulk per vertex brings the 16-byte-aligned middle of the list (the up to 3 floats
 // before the first and after the last boundary come with plain loads), the three passes over the
-// weights then read shared memory.  Lists (12 B/edge) follow the weights in dynamic shared memory.
+// weights then read shared memory.  The packed lists (8 B/edge) precede the weights in dynamic
+// shared memory.
 template <int NT, int CAP>
 __global__ void __launch_bounds__(NT) build_cta_staged_kernel(const u32* __restrict__ worklist,
                                                               u32* __restrict__ cls, int k,
@@ -734,12 +930,12 @@ __global__ void __launch_bounds__(NT) build_cta_staged_kernel(const u32* __restr
                                                               uint8_t* __restrict__ valid,
                                                               u32* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ u64 s_tmp[3 * (NT / 32 + 1)];
+  __shared__ u64 s_tmp[NT / 32 + 1];
   __shared__ __align__(8) u64 s_bar;
   __shared__ u32 s_it;
   u64* A = reinterpret_cast<u64*>(smem);
-  u32* P = reinterpret_cast<u32*>(A + CAP);
-  float* sW = reinterpret_cast<float*>(P + CAP);  // CAP + 8 floats, 16-byte aligned
+  float* sW = reinterpret_cast<float*>(A + CAP);  // CAP + 8 floats, 16-byte aligned
+  const CtaCoop<NT> co(s_tmp);
   const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
   if (threadIdx.x == 0) mbar_init(&s_bar, 1);
   __syncthreads();
@@ -752,7 +948,7 @@ __global__ void __launch_bounds__(NT) build_cta_staged_kernel(const u32* __restr
     if (it >= count) break;
     const u32 v = worklist[base + it];
     const u32 off = xadj[v], n = xadj[v + 1] - off;
-    if (n > (u32)CAP) {
+    if (n > (u32)CAP || n == 0) {
       if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, CAP);
       continue;
     }
@@ -785,7 +981,7 @@ __global__ void __launch_bounds__(NT) build_cta_staged_kernel(const u32* __restr
       break;
     }
     if (bulk) parity ^= 1u;
-    build_vertex_merge<NT, 8, 0, true>(threadIdx.x, v, off, n, sW + head, slots, valid, A, P, s_tmp, nullptr, err);
+    build_vertex_packed<CtaCoop<NT>, 8, false, true>(co, v, off, n, sW + head, slots, valid, A, err);
     __syncthreads();
   }
 }
@@ -968,25 +1164,23 @@ __device__ void build_vertex_cta(u32 v, u32 off, u32 n, const float* __restrict_
 // bases at [2K + k]).
 static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   cudaStream_t st = ctx->stream;
-  constexpr int kCtaSmem = kLargeMax * 12;
+  static_assert(kLargeMax <= kPackedMax, "the 1025+ CTA class uses packed list entries");
+  constexpr int kCtaSmem = kLargeMax * 8;
   constexpr int kCta2Smem = kHugeSmemMax * 12;
-  constexpr int kCtaStagedSmem = kLargeMax * 12 + (kLargeMax + 8) * 4;
-  constexpr int kW256Smem = 8 * kWarpSmallMax * 12;
-  constexpr int kW1KSmem = 8 * kWarpMax * 12;
+  constexpr int kCtaStagedSmem = kLargeMax * 8 + (kLargeMax + 8) * 4;
+  constexpr int kW1KSmem = 8 * kWarpMax * 8;
   constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
   constexpr int kWinSmem = kWin * 12 + (1024 + 1) * 4;
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
-    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCta2Smem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_staged_kernel<256, kLargeMax>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaStagedSmem));
-    SKW_CUDA(ctx, cudaFuncSetAttribute(build_warp_merge_kernel<kWarpMax, 8>,
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_warp_packed_kernel<kWarpMax, 8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kW1KSmem));
     attr_set[ctx->device & 63] = true;
   }
-  // slabs of the global-scratch builder: one per CTA, sized by the largest degree
   // one slab per CTA of the scratch class, sized by the largest degree; fewer CTAs when a giant
   // hub would make the slabs exceed 4 GB in total
   const uint64_t slab_elems = ctx->max_degree > kHugeSmemMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
@@ -1026,33 +1220,32 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   }
   if (ctx->max_degree > kWarpMax) {
     if ((reinterpret_cast<uintptr_t>(ctx->adjwgt) & 15u) == 0) {
-      build_cta_staged_kernel<256, kLargeMax><<<ctx->sm_count * 3, 256, kCtaStagedSmem, s_c>>>(
+      build_cta_staged_kernel<256, kLargeMax><<<ctx->sm_count * 4, 256, kCtaStagedSmem, s_c>>>(
           worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
     } else {  // a borrowed weight array that is not 16-byte aligned cannot be bulk-copied
-      build_cta_merge_kernel<256, 0><<<ctx->sm_count * 4, 256, kCtaSmem, s_c>>>(
-          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kLargeMax, ctx->d_err);
+      build_cta_packed_kernel<256><<<ctx->sm_count * 6, 256, kCtaSmem, s_c>>>(
+          worklist, cls, K_C, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
     }
     SKW_LAUNCHED(ctx);
   }
   if (ctx->max_degree > kWarpSmallMax) {
-    build_warp_merge_kernel<kWarpMax, 8><<<ctx->sm_count * 2, 256, kW1KSmem, s_w1k>>>(
+    build_warp_packed_kernel<kWarpMax, 8><<<ctx->sm_count * 3, 256, kW1KSmem, s_w1k>>>(
         worklist, cls, K_W1K, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
-    SKW_LAUNCHED(ctx);
-  }
-  if (ctx->max_degree > 32) {
-    build_warp_merge_kernel<kWarpSmallMax, 8><<<ctx->sm_count * 8, 256, kW256Smem, st>>>(
-        worklist, cls, K_W256, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
     SKW_LAUNCHED(ctx);
   }
   const int ggrid = ctx->sm_count * 8;
 #define GROUP(GSZ, KCLS)                                                                          \
-  build_group_kernel<GSZ><<<ggrid, 256, 0, st>>>(worklist, cls, KCLS, ctx->xadj, ctx->adjwgt,     \
-                                                 ctx->slots, ctx->valid, ctx->d_err);             \
-  SKW_LAUNCHED(ctx)
-  GROUP(32, K_G32);
-  GROUP(16, K_G16);
-  GROUP(8, K_G8);
-  GROUP(4, K_G4);
+  if (ctx->max_degree > (GSZ) * kGroupEpt / 2 || (GSZ) == 1) {                                    \
+    build_small_kernel<GSZ><<<ggrid, 256, 0, st>>>(worklist, cls, KCLS, ctx->xadj, ctx->adjwgt,   \
+                                                   ctx->slots, ctx->valid, ctx->d_err);           \
+    SKW_LAUNCHED(ctx);                                                                            \
+  }
+  GROUP(32, K_G32)
+  GROUP(16, K_G16)
+  GROUP(8, K_G8)
+  GROUP(4, K_G4)
+  GROUP(2, K_G2)
+  GROUP(1, K_G1)
 #undef GROUP
   if (fork) {
     for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) {

@@ -321,6 +321,7 @@ int skw_ctx_create(int device, skw_ctx** out) {
   ctx->sm_count = prop.multiProcessorCount;
   CK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
   CK(cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+  CK(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
   ctx->stream = ctx->own_stream;
   for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) {
     CK(cudaStreamCreateWithFlags(&ctx->bstream[i], cudaStreamNonBlocking));
@@ -334,11 +335,19 @@ int skw_ctx_create(int device, skw_ctx** out) {
   CK(cudaMalloc(&ctx->d_err, 8 * sizeof(uint32_t)));
   CK(cudaMemset(ctx->d_err, 0, 8 * sizeof(uint32_t)));
   CK(cudaMallocHost(&ctx->h_err, 8 * sizeof(uint32_t)));
-  CK(cudaEventCreateWithFlags(&ctx->pk_ready, cudaEventDisableTiming));
-  for (int i = 0; i < 2; ++i) CK(cudaEventCreateWithFlags(&ctx->pk_done[i], cudaEventDisableTiming));
-  CK(cudaMalloc(&ctx->d_sum, 2 * sizeof(uint64_t)));
-  CK(cudaMemset(ctx->d_sum, 0, 2 * sizeof(uint64_t)));
-  CK(cudaMallocHost(&ctx->h_sum, 2 * sizeof(uint64_t)));
+  for (int i = 0; i < skw_ctx::kPackSlices; ++i) {
+    CK(cudaEventCreateWithFlags(&ctx->pk_ready[i], cudaEventDisableTiming));
+    CK(cudaEventCreateWithFlags(&ctx->pk_tot[i], cudaEventDisableTiming));
+    CK(cudaEventCreate(&ctx->pk_t0[i]));
+    CK(cudaEventCreate(&ctx->pk_t1[i]));
+  }
+  CK(cudaMalloc(&ctx->d_tot, skw_ctx::kPackSlices * sizeof(uint64_t)));
+  CK(cudaMallocHost(&ctx->h_tot, skw_ctx::kPackSlices * sizeof(uint64_t)));
+  CK(cudaMalloc(&ctx->d_sum, 4 * sizeof(uint64_t)));
+  CK(cudaMemset(ctx->d_sum, 0, 4 * sizeof(uint64_t)));
+  CK(cudaMallocHost(&ctx->h_sum, 4 * sizeof(uint64_t)));
+  CK(cudaMalloc(&ctx->d_cursor, 4 * sizeof(uint32_t)));
+  CK(cudaMemset(ctx->d_cursor, 0, 4 * sizeof(uint32_t)));
   CK(cudaMalloc(&ctx->cls_counts, 64 * sizeof(uint32_t)));
   CK(cudaMalloc(&ctx->frontier_cls, 64 * sizeof(uint32_t)));
 #undef CK
@@ -355,24 +364,31 @@ void skw_ctx_destroy(skw_ctx* ctx) {
   cudaFreeHost(ctx->h_err);
   cudaFree(ctx->d_sum);
   cudaFreeHost(ctx->h_sum);
+  cudaFree(ctx->d_cursor);
   cudaFree(ctx->worklist);
   cudaFree(ctx->cls_counts);
   cudaFree(ctx->cta_scratch);
   cudaFree(ctx->frontier_lists);
   cudaFree(ctx->frontier_cls);
-  for (int i = 0; i < 6; ++i) cudaFree(ctx->stage[i]);
+  for (int i = 0; i < skw_ctx::kStages; ++i) cudaFree(ctx->stage[i]);
+  cudaFree(ctx->d_tot);
+  cudaFreeHost(ctx->h_tot);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
+  if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
   for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) {
     if (ctx->bstream[i]) cudaStreamDestroy(ctx->bstream[i]);
     if (ctx->bjoin[i]) cudaEventDestroy(ctx->bjoin[i]);
   }
   if (ctx->bfork) cudaEventDestroy(ctx->bfork);
-  if (ctx->pk_ready) cudaEventDestroy(ctx->pk_ready);
-  for (int i = 0; i < 2; ++i)
-    if (ctx->pk_done[i]) cudaEventDestroy(ctx->pk_done[i]);
+  for (int i = 0; i < skw_ctx::kPackSlices; ++i) {
+    if (ctx->pk_ready[i]) cudaEventDestroy(ctx->pk_ready[i]);
+    if (ctx->pk_tot[i]) cudaEventDestroy(ctx->pk_tot[i]);
+    if (ctx->pk_t0[i]) cudaEventDestroy(ctx->pk_t0[i]);
+    if (ctx->pk_t1[i]) cudaEventDestroy(ctx->pk_t1[i]);
+  }
   delete ctx;
 }
 

@@ -26,7 +26,12 @@ struct skw_ctx {
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   cudaStream_t side_stream = nullptr;  // result copies that overlap kernels of `stream`
-  cudaEvent_t pk_ready = nullptr, pk_done[2] = {nullptr, nullptr};  // skw_walk_packed: packed -> copied
+  cudaStream_t copy_stream = nullptr;  // skw_walk_packed: the packed rows of each slice
+  // skw_walk_packed, per slice: rows packed; cell count on the host; start and end of the walk
+  static constexpr int kPackSlices = 4;
+  cudaEvent_t pk_ready[kPackSlices] = {}, pk_tot[kPackSlices] = {}, pk_t0[kPackSlices] = {}, pk_t1[kPackSlices] = {};
+  uint64_t* d_tot = nullptr;  // cells each slice's packed result needs
+  uint64_t* h_tot = nullptr;  // pinned mirror
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // the degree-class builders of one build run side by side: classes 257+ on streams of their own,
   // forked from and joined back into `stream` by events
@@ -62,6 +67,8 @@ struct skw_ctx {
   // pinned scalar for 64-bit reductions read back after a launch
   uint64_t* d_sum = nullptr;
   uint64_t* h_sum = nullptr;
+  // work cursor of the persistent walk kernels: {next chunk, finished warps}, zero between launches
+  uint32_t* d_cursor = nullptr;
 
   // builder scratch, grown on demand
   uint32_t* worklist = nullptr;      // V entries, vertices grouped by degree class
@@ -79,8 +86,9 @@ struct skw_ctx {
   uint32_t stamp_round = 0;
 
   // staging buffers of the host-pointer entry points, grown on demand
-  void* stage[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-  size_t stage_bytes[6] = {0, 0, 0, 0, 0, 0};
+  static constexpr int kStages = 8;
+  void* stage[kStages] = {};
+  size_t stage_bytes[kStages] = {};
 };
 
 namespace skw {

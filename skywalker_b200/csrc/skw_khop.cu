@@ -94,12 +94,88 @@ __global__ void __launch_bounds__(256) khop_hop_kernel(const KhopArgs a) {
   if ((threadIdx.x & 31) == 0 && got_sum) atomicAdd(a.sum, (unsigned long long)got_sum);
 }
 
+// SKW_KHOP_DISTINCT: one warp per parent vertex.  A parent whose degree is <= the fan-out hands over
+// every neighbour once.  Otherwise trial t (t = lane + 32 * round, 11 rounds at most, as the reference's
+// roll_atomic, src/online_sample_new.cu:73-111) draws a column with its own Philox words, keyed by
+// (seed id, parent index, trial, hop); a draw counts when its column was not drawn by an earlier trial.
+// "Earlier" is decided without atomics: columns accepted in earlier rounds sit in a per-warp list in
+// shared memory, and inside a round the lowest lane holding a column wins (match_any), so the result
+// is the one a sequential pass over the trials gives.
+constexpr u32 kDistinctMaxFanout = 256, kDistinctRounds = 11;
+__global__ void __launch_bounds__(256) khop_distinct_kernel(const KhopArgs a) {
+  __shared__ u32 s_seen[8][kDistinctMaxFanout];
+  const u32 lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const u64 warp = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const u64 nwarps = ((u64)gridDim.x * blockDim.x) >> 5;
+  const u64 parents = a.n * a.width_parent;
+  const u32 f = a.fanout;
+  u32* seen = s_seen[wib];
+  u64 got_sum = 0;
+  for (u64 u = warp; u < parents; u += nwarps) {
+    const u64 s = u / a.width_parent;
+    const u32 idx = (u32)(u - s * a.width_parent);
+    u32* row = a.data + s * a.cells;
+    u32* child = row + a.offs_child + (u64)idx * f;
+    const u32 v = row[a.offs_parent + idx];
+    u32 got = 0;
+    u32 off = 0, deg = 0;
+    if (v != SKW_INVALID_VERTEX) {
+      if (v >= a.V) {
+        if (lane == 0) dev_fail(a.err, DEV_ERR_INDEX, v, idx, a.hop);
+      } else {
+        off = __ldg(a.xadj + v);
+        deg = __ldg(a.xadj + v + 1) - off;
+      }
+    }
+    if (deg && f >= deg) {
+      for (u32 j = lane; j < deg; j += 32) child[j] = __ldg(a.adjncy + (u64)off + j);
+      got = deg;
+    } else if (deg) {
+      const u64 gi = a.instance_base + s * a.instance_stride;
+      for (u32 round = 0; round < kDistinctRounds && got < f; ++round) {
+        const u32 t = round * 32 + lane;
+        const Rand4 r = philox_tagged(a.seed, TAG_KHOP, gi, idx, (t << 8) | 0x80u | a.hop);
+        const u32 col = __umulhi(r.x, deg);
+        const Slot sl = load_slot(a.slots + (u64)off + col);
+        if (sl.prob < 0.0f) break;  // vertex without usable weight: the same in every lane
+        u32 cand = u01(r.y) < sl.prob ? col : sl.alias;
+        if (cand >= deg) {  // a table that does not belong to this graph
+          dev_fail(a.err, DEV_ERR_INDEX, v, cand, 24);
+          cand = 0;
+        }
+        bool fresh = true;
+        for (u32 i = 0; i < got; ++i) fresh = fresh && seen[i] != cand;
+        const u32 same = __match_any_sync(0xFFFFFFFFu, cand);
+        fresh = fresh && lane == (u32)(__ffs(same) - 1);
+        const u32 acc = __ballot_sync(0xFFFFFFFFu, fresh);
+        const u32 at = got + __popc(acc & ((1u << lane) - 1u));
+        if (fresh && at < f) {
+          seen[at] = cand;
+          child[at] = ldg_once(a.adjncy + (u64)off + cand);
+        }
+        got = min(f, got + (u32)__popc(acc));
+        __syncwarp();
+      }
+    }
+    for (u32 j = got + lane; j < f; j += 32) child[j] = SKW_INVALID_VERTEX;
+    if (lane == 0) {
+      a.lens[s * a.lens_per + a.offs_parent + idx] = got;
+      got_sum += got;
+    }
+    __syncwarp();  // the list is reused by the next parent
+  }
+  if (lane == 0 && got_sum) atomicAdd(a.sum, (unsigned long long)got_sum);
+}
+
 static int khop_check(skw_ctx* ctx, const skw_khop_params* prm) {
   if (prm->nhops < 1 || prm->nhops > 4) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: nhops must be 1..4");
   if (prm->mode > SKW_MODE_ONLINE) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: unknown mode %u", prm->mode);
   u64 w = 1, cells = 1;
   for (u32 h = 0; h < prm->nhops; ++h) {
     if (prm->fanout[h] == 0) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: fan-out of hop %u is 0", h + 1);
+    if ((prm->flags & SKW_KHOP_DISTINCT) && !(prm->flags & SKW_KHOP_UNBIASED) && prm->fanout[h] > kDistinctMaxFanout)
+      return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: SKW_KHOP_DISTINCT takes fan-outs up to %u, hop %u asks for %u",
+                  kDistinctMaxFanout, h + 1, prm->fanout[h]);
     w *= prm->fanout[h];
     cells += w;
     if (cells > 0x7FFFFFFFull) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: tree of %llu cells per seed is too large",
@@ -187,8 +263,13 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
       a.width_parent = width[h];
       a.fanout = prm->fanout[h];
       a.hop = h + 1;
-      want = (n * width[h + 1] + 255) / 256;
-      khop_hop_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
+      if ((prm->flags & SKW_KHOP_DISTINCT) && !unbiased) {
+        want = (n * width[h] + 7) / 8;  // one warp per parent vertex
+        khop_distinct_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
+      } else {
+        want = (n * width[h + 1] + 255) / 256;
+        khop_hop_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
+      }
       SKW_LAUNCHED(ctx);
     }
   }

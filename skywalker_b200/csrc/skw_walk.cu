@@ -310,6 +310,7 @@ struct RecordWalkArgs {
   u32 V;
   u32 hop_num;
   float tp;
+  u32* cursor;  // chunked PPR kernel: {next chunk, warps that have finished}; both zero between launches
 };
 
 // Same lane-owns-a-stride loop as walk_offline_kernel; a step is one record load.
@@ -388,98 +389,120 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
 // (so that no partly written sector leaves L2) made the launch 12 % slower.  Chunks of 64 walkers
 // with 8 warps per CTA were the best of {64, 128, 256} x {4, 8, 16}.
 constexpr u32 kChunk = 64, kStage = 8, kStagePitch = kStage + 1;
+// The grid is persistent: warps take chunks from a global cursor until none is left, so the launch has
+// no waves (1 M walkers are 1,954 CTAs' worth of chunks, 1.65 waves of the 1,184 resident CTAs) and
+// every SM runs out of work at about the same time.  A warp asks for its next chunk before it starts
+// on the current one, which hides the atomic's latency.  The last warp to finish puts the cursor back
+// to zero for the next launch (launches of one context are ordered on its stream).
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) walk_records_ppr_kernel(const RecordWalkArgs a) {
   __shared__ u32 s_buf[WARPS][kChunk * kStagePitch];
   __shared__ uint16_t s_len[WARPS][kChunk];
   const u32 lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const u64 w_begin = ((u64)blockIdx.x * WARPS + wib) * kChunk;
-  if (w_begin >= a.n) return;  // the whole warp leaves; nothing below synchronises the CTA
-  const u32 cnt = (u32)min((u64)kChunk, a.n - w_begin);
+  const u64 nchunks = (a.n + kChunk - 1) / kChunk;
   u32* buf = s_buf[wib];
   uint16_t* len = s_len[wib];
-  {
-    u32 st[kChunk / 32];
-    bool live[kChunk / 32];
-#pragma unroll
-    for (int k = 0; k < (int)(kChunk / 32); ++k) {
-      const u32 i = k * 32 + lane;
-      st[k] = i < cnt ? __ldg(a.starts + w_begin + i) : 0u;
-    }
-#pragma unroll
-    for (int k = 0; k < (int)(kChunk / 32); ++k) {
-      const u32 i = k * 32 + lane;
-      live[k] = false;
-      if (i < cnt) {
-        if (st[k] >= a.V) dev_fail(a.err, DEV_ERR_INDEX, st[k], 0, (u32)(w_begin + i));
-        else live[k] = (__ldg(a.vbits + (st[k] >> 5)) >> (st[k] & 31)) & 1u;
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < (int)(kChunk / 32); ++k) {
-      const u32 i = k * 32 + lane;
-      uint2 vi = make_uint2(0u, 0u);
-      if (live[k]) vi = ldg_once(a.vinfo + st[k]);
-      if (i < cnt) {
-        buf[i * kStagePitch] = st[k];
-        buf[i * kStagePitch + 1] = vi.x;
-        buf[i * kStagePitch + 2] = vi.y;
-      }
-    }
-  }
-  __syncwarp();
   const u32 lt = (1u << lane) - 1u;
-  u32 next = 0;  // walkers of the chunk handed out so far (the same in every lane)
-  bool active = false;
-  u32 local = 0, off = 0, deg = 0, step = 0;
   u64 edges = 0;
-  for (;;) {
-    const u32 need = __ballot_sync(0xFFFFFFFFu, !active);
-    if (need && next < cnt) {
-      const u32 mine = next + __popc(need & lt);
-      if (!active && mine < cnt) {
-        local = mine;
-        off = buf[local * kStagePitch + 1];
-        deg = buf[local * kStagePitch + 2];
-        step = 0;
-        active = true;
+  u32 chunk = 0;
+  if (lane == 0) chunk = atomicAdd(a.cursor, 1u);
+  chunk = __shfl_sync(0xFFFFFFFFu, chunk, 0);
+  while (chunk < nchunks) {
+    u32 chunk_next = 0;
+    if (lane == 0) chunk_next = atomicAdd(a.cursor, 1u);  // used only after this chunk is done
+    const u64 w_begin = (u64)chunk * kChunk;
+    const u32 cnt = (u32)min((u64)kChunk, a.n - w_begin);
+    {
+      u32 st[kChunk / 32];
+      bool live[kChunk / 32];
+#pragma unroll
+      for (int k = 0; k < (int)(kChunk / 32); ++k) {
+        const u32 i = k * 32 + lane;
+        st[k] = i < cnt ? __ldg(a.starts + w_begin + i) : 0u;
       }
-      next = min(cnt, next + (u32)__popc(need));
+#pragma unroll
+      for (int k = 0; k < (int)(kChunk / 32); ++k) {
+        const u32 i = k * 32 + lane;
+        live[k] = false;
+        if (i < cnt) {
+          if (st[k] >= a.V) dev_fail(a.err, DEV_ERR_INDEX, st[k], 0, (u32)(w_begin + i));
+          else live[k] = (__ldg(a.vbits + (st[k] >> 5)) >> (st[k] & 31)) & 1u;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < (int)(kChunk / 32); ++k) {
+        const u32 i = k * 32 + lane;
+        uint2 vi = make_uint2(0u, 0u);
+        if (live[k]) vi = ldg_once(a.vinfo + st[k]);
+        if (i < cnt) {
+          buf[i * kStagePitch] = st[k];
+          buf[i * kStagePitch + 1] = vi.x;
+          buf[i * kStagePitch + 2] = vi.y;
+        }
+      }
     }
-    if (!__any_sync(0xFFFFFFFFu, active)) break;
-    if (active) {
-      bool go = step + 1 < a.hop_num && deg != 0;
-      Rand4 r{0, 0, 0, 0};
-      if (go) {
-        r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, step, 0);
-        if (u01(r.z) < a.tp) go = false;
+    __syncwarp();
+    u32 next = 0;  // walkers of the chunk handed out so far (the same in every lane)
+    bool active = false;
+    u32 local = 0, off = 0, deg = 0, step = 0;
+    for (;;) {
+      const u32 need = __ballot_sync(0xFFFFFFFFu, !active);
+      if (need && next < cnt) {
+        const u32 mine = next + __popc(need & lt);
+        if (!active && mine < cnt) {
+          local = mine;
+          off = buf[local * kStagePitch + 1];
+          deg = buf[local * kStagePitch + 2];
+          step = 0;
+          active = true;
+        }
+        next = min(cnt, next + (u32)__popc(need));
       }
-      if (go) {
-        u32 rw[8];
-        load_record(a.rec + (u64)off + __umulhi(r.x, deg), rw);
-        const bool keep = u01(r.y) < __uint_as_float(rw[0]);
-        ++step;
-        const u32 nv = keep ? rw[1] : rw[4];
-        if (step < kStage) buf[local * kStagePitch + step] = nv;
-        else a.paths[(w_begin + local) * a.hop_num + step] = nv;
-        off = keep ? rw[2] : rw[5];
-        deg = keep ? rw[3] : rw[6];
-      } else {
-        len[local] = (uint16_t)step;
-        edges += step;
-        active = false;
+      if (!__any_sync(0xFFFFFFFFu, active)) break;
+      if (active) {
+        bool go = step + 1 < a.hop_num && deg != 0;
+        Rand4 r{0, 0, 0, 0};
+        if (go) {
+          r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, step, 0);
+          if (u01(r.z) < a.tp) go = false;
+        }
+        if (go) {
+          u32 rw[8];
+          load_record(a.rec + (u64)off + __umulhi(r.x, deg), rw);
+          const bool keep = u01(r.y) < __uint_as_float(rw[0]);
+          ++step;
+          const u32 nv = keep ? rw[1] : rw[4];
+          if (step < kStage) buf[local * kStagePitch + step] = nv;
+          else a.paths[(w_begin + local) * a.hop_num + step] = nv;
+          off = keep ? rw[2] : rw[5];
+          deg = keep ? rw[3] : rw[6];
+        } else {
+          len[local] = (uint16_t)step;
+          edges += step;
+          active = false;
+        }
       }
     }
+    __syncwarp();
+    // write-out: 8 lanes per row, four neighbouring rows per pass; then the lengths, coalesced
+    for (u32 r = lane >> 3; r < cnt; r += 4) {
+      const u32 c = lane & 7;
+      const u32 cells = min((u32)len[r] + 1u, kStage);
+      if (c < cells) a.paths[(w_begin + r) * a.hop_num + c] = buf[r * kStagePitch + c];
+    }
+    for (u32 i = lane; i < cnt; i += 32) a.lengths[w_begin + i] = len[i];
+    __syncwarp();  // the staging rows are reused by the next chunk
+    chunk = __shfl_sync(0xFFFFFFFFu, chunk_next, 0);
   }
-  __syncwarp();
-  // write-out: 8 lanes per row, four neighbouring rows per pass; then the lengths, coalesced
-  for (u32 r = lane >> 3; r < cnt; r += 4) {
-    const u32 c = lane & 7;
-    const u32 cells = min((u32)len[r] + 1u, kStage);
-    if (c < cells) a.paths[(w_begin + r) * a.hop_num + c] = buf[r * kStagePitch + c];
-  }
-  for (u32 i = lane; i < cnt; i += 32) a.lengths[w_begin + i] = len[i];
   add_edges(a.sum, edges);
+  if (lane == 0) {
+    const u32 total = gridDim.x * WARPS;
+    if (atomicAdd(a.cursor + 1, 1u) + 1u == total) {  // every warp has stopped asking: rewind
+      a.cursor[0] = 0;
+      a.cursor[1] = 0;
+      __threadfence();
+    }
+  }
 }
 
 // Copy the written part of every path row (cells 0..length) from the device matrix into a host
@@ -508,16 +531,16 @@ struct CellsOfRow {
 __global__ void __launch_bounds__(256) pack_rows_kernel(const u32* __restrict__ src, u32* __restrict__ packed,
                                                         const u32* __restrict__ lengths,
                                                         const u64* __restrict__ offs, u64 n, u32 hop_num,
-                                                        u64 capacity, u32* err) {
+                                                        u64 capacity, u64* __restrict__ total) {
   const u32 sub = threadIdx.x & 7;
   const u64 rows_per_pass = ((u64)gridDim.x * blockDim.x) >> 3;
   for (u64 w = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 3; w < n; w += rows_per_pass) {
     const u32 cells = min(__ldg(lengths + w) + 1u, hop_num);
     const u64 o = __ldg(offs + w);
-    if (o + cells > capacity) {  // cannot happen when the host sized the buffer from the edge count
-      if (sub == 0) dev_fail(err, DEV_ERR_CAPACITY, (u32)w, cells, (u32)(o >> 32));
-      continue;
-    }
+    if (w == n - 1 && sub == 0) *total = o + cells;  // cells the whole batch needs
+    // rows that do not fit are left out: the host compares *total with the capacity and packs again
+    // into a larger buffer
+    if (o + cells > capacity) continue;
     const u32* s = src + w * hop_num;
     for (u32 c = sub; c < cells; c += 8) packed[o + c] = ldg_once(s + c);
   }
@@ -690,11 +713,8 @@ int skw_walk_records_free(skw_ctx* ctx) {
   return SKW_OK;
 }
 
-int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_starts, uint64_t n,
-                    uint32_t* d_paths, uint32_t* d_lengths, float* ms, uint64_t* sampled_edges) {
-  if (!ctx || !prm) return SKW_ERR_ARG;
-  if (n && (!d_starts || !d_paths || !d_lengths))
-    return fail(ctx, SKW_ERR_ARG, "skw_walk: null buffer");
+// Argument and state checks shared by the walk entry points.
+static int walk_check(skw_ctx* ctx, const skw_walk_params* prm) {
   if (prm->hop_num < 1) return fail(ctx, SKW_ERR_ARG, "skw_walk: hop_num must be >= 1");
   if (prm->app > SKW_APP_NODE2VEC) return fail(ctx, SKW_ERR_ARG, "skw_walk: unknown app %u", prm->app);
   if (prm->mode > SKW_MODE_ONLINE) return fail(ctx, SKW_ERR_ARG, "skw_walk: unknown mode %u", prm->mode);
@@ -708,7 +728,15 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   if (!online && !unbiased && !ctx->table_ready)
     return fail(ctx, SKW_ERR_STATE, "skw_walk: offline mode needs skw_alias_build_offline or skw_alias_import first");
   if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_walk: online mode needs the edge weights");
-  DeviceGuard g(ctx->device);
+  return SKW_OK;
+}
+
+// Queue the kernels of one batch of walkers on the context's stream; sampled edges are added to *sum.
+// No reset, no readback, no synchronisation (the online table path allocates on first use).
+static int walk_launch(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_starts, uint64_t n,
+                       uint32_t* d_paths, uint32_t* d_lengths, unsigned long long* sum) {
+  const bool unbiased = (prm->flags & SKW_WALK_UNBIASED) != 0;
+  const bool online = prm->mode == SKW_MODE_ONLINE && !unbiased;
   int rc;
   // online walks evaluate the slot they draw straight from the weights; on request they build the
   // tables of the frontier at every step instead (same walks)
@@ -725,6 +753,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
     drop_records(ctx);  // online builds overwrite table slots
     if ((rc = alloc_table(ctx)) != SKW_OK) return rc;
   }
+  if (!n) return SKW_OK;
   WalkArgs a;
   a.xadj = ctx->xadj;
   a.adjncy = ctx->adjncy;
@@ -732,7 +761,7 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   a.starts = d_starts;
   a.paths = d_paths;
   a.lengths = d_lengths;
-  a.sum = reinterpret_cast<unsigned long long*>(ctx->d_sum);
+  a.sum = sum;
   a.err = ctx->d_err;
   a.n = n;
   a.seed = prm->seed;
@@ -746,69 +775,81 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   a.inv_q = prm->app == SKW_APP_NODE2VEC ? 1.0f / prm->q : 1.0f;
   a.fmax = fmaxf(1.0f, fmaxf(a.inv_p, a.inv_q));
   cudaStream_t st = ctx->stream;
+  if (!online && !unbiased && ctx->records_ready && prm->app != SKW_APP_NODE2VEC) {
+    RecordWalkArgs ra;
+    ra.rec = static_cast<const WalkRecord*>(ctx->records);
+    ra.vinfo = static_cast<const uint2*>(ctx->vinfo);
+    ra.vbits = static_cast<const u32*>(ctx->vbits);
+    ra.starts = d_starts;
+    ra.paths = d_paths;
+    ra.lengths = d_lengths;
+    ra.sum = a.sum;
+    ra.err = a.err;
+    ra.n = n;
+    ra.seed = a.seed;
+    ra.walker_base = a.walker_base;
+    ra.walker_stride = a.walker_stride;
+    ra.V = a.V;
+    ra.hop_num = a.hop_num;
+    ra.tp = a.tp;
+    ra.cursor = ctx->d_cursor;
+    const int grid = walk_grid(prm->app, n);
+    const u64 ctas = (n + 8 * kChunk - 1) / (8 * kChunk);
+    const u64 resident = (u64)ctx->sm_count * 8;
+    // (the chunked kernel stages lengths as 16-bit values and counts chunks in 32 bits)
+    if (prm->app == SKW_APP_PPR && prm->hop_num <= 65535 && (n + kChunk - 1) / kChunk < 0x7FFFFFFFull - 8 * resident) {
+      walk_records_ppr_kernel<8><<<(unsigned)(ctas < resident ? ctas : resident), 256, 0, st>>>(ra);
+    } else if (prm->app == SKW_APP_PPR) walk_records_walk_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(ra);
+    else walk_records_walk_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(ra);
+    SKW_LAUNCHED(ctx);
+  } else if (!online) {
+    const int grid = walk_grid(prm->app, n);
+    switch (prm->app) {
+      case SKW_APP_DEEPWALK: walk_offline_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a); break;
+      case SKW_APP_PPR: walk_offline_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a); break;
+      default: walk_offline_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a); break;
+    }
+    SKW_LAUNCHED(ctx);
+  } else if (!build_tables) {
+    if ((rc = launch_walk_online_direct(ctx, a, prm->app)) != SKW_OK) return rc;
+  } else {
+    const int grid = grid_for(ctx, n, 8);
+    walk_online_init_kernel<<<grid, 256, 0, st>>>(a);
+    SKW_LAUNCHED(ctx);
+    for (uint32_t step = 0; step + 1 < prm->hop_num; ++step) {
+      if ((rc = frontier_collect(ctx, d_paths, n, 1, prm->hop_num, step, d_lengths,
+                                 step == 0 || !(prm->flags & SKW_WALK_CACHE_TABLES))) != SKW_OK) return rc;
+      switch (prm->app) {
+        case SKW_APP_DEEPWALK: walk_online_step_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, step); break;
+        case SKW_APP_PPR: walk_online_step_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, step); break;
+        default: walk_online_step_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a, step); break;
+      }
+      SKW_LAUNCHED(ctx);
+    }
+  }
+  return SKW_OK;
+}
+
+int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_starts, uint64_t n,
+                    uint32_t* d_paths, uint32_t* d_lengths, float* ms, uint64_t* sampled_edges) {
+  if (!ctx || !prm) return SKW_ERR_ARG;
+  if (n && (!d_starts || !d_paths || !d_lengths))
+    return fail(ctx, SKW_ERR_ARG, "skw_walk: null buffer");
+  int rc = walk_check(ctx, prm);
+  if (rc != SKW_OK) return rc;
+  DeviceGuard g(ctx->device);
+  cudaStream_t st = ctx->stream;
   // With both result pointers null the call only enqueues work: no reset, no readback, no
   // synchronisation.  Sampled edges then add up in a second counter and a device error stays
   // recorded until skw_ctx_take_sampled_edges() (or a later synchronous call) looks at it.
   const bool enqueue_only = !ms && !sampled_edges;
-  if (enqueue_only) {
-    a.sum = reinterpret_cast<unsigned long long*>(ctx->d_sum) + 1;
-  } else {
+  unsigned long long* sum = reinterpret_cast<unsigned long long*>(ctx->d_sum) + (enqueue_only ? 1 : 0);
+  if (!enqueue_only) {
     if ((rc = err_reset(ctx)) != SKW_OK) return rc;
     SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
     SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
   }
-  if (n) {
-    if (!online && !unbiased && ctx->records_ready && prm->app != SKW_APP_NODE2VEC) {
-      RecordWalkArgs ra;
-      ra.rec = static_cast<const WalkRecord*>(ctx->records);
-      ra.vinfo = static_cast<const uint2*>(ctx->vinfo);
-      ra.vbits = static_cast<const u32*>(ctx->vbits);
-      ra.starts = d_starts;
-      ra.paths = d_paths;
-      ra.lengths = d_lengths;
-      ra.sum = a.sum;
-      ra.err = a.err;
-      ra.n = n;
-      ra.seed = a.seed;
-      ra.walker_base = a.walker_base;
-      ra.walker_stride = a.walker_stride;
-      ra.V = a.V;
-      ra.hop_num = a.hop_num;
-      ra.tp = a.tp;
-      const int grid = walk_grid(prm->app, n);
-      const u64 ctas = (n + 8 * kChunk - 1) / (8 * kChunk);
-      // (the chunked kernel stages lengths as 16-bit values and has no grid-stride loop)
-      if (prm->app == SKW_APP_PPR && prm->hop_num <= 65535 && ctas <= 0x7FFFFFFFull) {
-        walk_records_ppr_kernel<8><<<(unsigned)ctas, 256, 0, st>>>(ra);
-      } else if (prm->app == SKW_APP_PPR) walk_records_walk_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(ra);
-      else walk_records_walk_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(ra);
-      SKW_LAUNCHED(ctx);
-    } else if (!online) {
-      const int grid = walk_grid(prm->app, n);
-      switch (prm->app) {
-        case SKW_APP_DEEPWALK: walk_offline_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a); break;
-        case SKW_APP_PPR: walk_offline_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a); break;
-        default: walk_offline_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a); break;
-      }
-      SKW_LAUNCHED(ctx);
-    } else if (!build_tables) {
-      if ((rc = launch_walk_online_direct(ctx, a, prm->app)) != SKW_OK) return rc;
-    } else {
-      const int grid = grid_for(ctx, n, 8);
-      walk_online_init_kernel<<<grid, 256, 0, st>>>(a);
-      SKW_LAUNCHED(ctx);
-      for (uint32_t step = 0; step + 1 < prm->hop_num; ++step) {
-        if ((rc = frontier_collect(ctx, d_paths, n, 1, prm->hop_num, step, d_lengths,
-                                   step == 0 || !(prm->flags & SKW_WALK_CACHE_TABLES))) != SKW_OK) return rc;
-        switch (prm->app) {
-          case SKW_APP_DEEPWALK: walk_online_step_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, step); break;
-          case SKW_APP_PPR: walk_online_step_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, step); break;
-          default: walk_online_step_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a, step); break;
-        }
-        SKW_LAUNCHED(ctx);
-      }
-    }
-  }
+  if ((rc = walk_launch(ctx, prm, d_starts, n, d_paths, d_lengths, sum)) != SKW_OK) return rc;
   if (enqueue_only) return SKW_OK;
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
   SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
@@ -865,15 +906,16 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
   if (ms) *ms = 0;
   if (sampled_edges) *sampled_edges = 0;
   if (n && (!h_starts || !h_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: null buffer");
-  if (prm->hop_num < 1) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: hop_num must be >= 1");
+  int rc = walk_check(ctx, prm);
+  if (rc != SKW_OK) return rc;
   if (!n) return SKW_OK;
   DeviceGuard g(ctx->device);
-  int rc;
   cudaStream_t st = ctx->stream, side = ctx->side_stream;
-  // Large batches run as a pipeline of up to four slices: while slice c walks on the context's
-  // stream, the packed result of slice c - 1 goes home on the side stream (and the start vertices of
-  // slice c come in: the bus carries both directions at once).  Walker ids, hence walks, do not
-  // depend on the slicing.
+  // Large batches run as up to four slices.  Everything a slice needs on the device (walk, prefix sum
+  // of its row sizes, packing) is queued for ALL slices before the host waits for anything; the side
+  // stream brings each slice's cell count, lengths and packed rows home as soon as they exist, while
+  // the context's stream is already walking the next slice (the bus carries both directions at once).
+  // Walker ids, hence walks, do not depend on the slicing.
   const uint64_t kSliceMin = 1u << 19;
   const uint32_t slices = n >= 4 * kSliceMin ? 4 : (n >= 2 * kSliceMin ? 2 : 1);
   const uint64_t per = (n + slices - 1) / slices;
@@ -885,87 +927,119 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
     SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, probe, (u64*)nullptr, (long long)per, st));
   }
   if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], sizeof(u32) * (size_t)n)) != SKW_OK) return rc;
-  if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], sizeof(u32) * (size_t)per * prm->hop_num)) != SKW_OK)
+  if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], sizeof(u32) * (size_t)n * prm->hop_num)) != SKW_OK)
     return rc;
   if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], sizeof(u32) * (size_t)n)) != SKW_OK) return rc;
   if ((rc = ensure_bytes(ctx, &ctx->stage[3], &ctx->stage_bytes[3], offs_bytes + tmp_bytes)) != SKW_OK) return rc;
   u32* d_starts = static_cast<u32*>(ctx->stage[0]);
-  u32* d_rows = static_cast<u32*>(ctx->stage[1]);  // one slice of rows at a time
+  u32* d_rows = static_cast<u32*>(ctx->stage[1]);
   u32* d_len = static_cast<u32*>(ctx->stage[2]);
   u64* d_offs = static_cast<u64*>(ctx->stage[3]);
-  u32* pack_err = ctx->d_err + 4;
-  SKW_CUDA(ctx, cudaMemsetAsync(pack_err, 0, 4 * sizeof(u32), st));
-  float total_ms = 0;
-  uint64_t total_edges = 0, total_cells = 0;
-  bool fits = h_packed != nullptr;
-  bool copied[2] = {false, false};  // a copy out of packing buffer b is or was in flight
+  // Packing buffers, one per slice.  The size of a result changes from call to call (another seed,
+  // other lengths), so a buffer that exists is kept as it is and only a result that outgrows it makes
+  // it grow (by an eighth more than needed): steady-state calls do not allocate.  First guess: every
+  // walk at full length, or the expected PPR length with room to spare.
+  uint64_t cap[4] = {0, 0, 0, 0}, nc_of[4] = {0, 0, 0, 0};
   for (uint32_t c = 0; c < slices; ++c) {
     const uint64_t base = (uint64_t)c * per;
     if (base >= n) break;
     const uint64_t nc = std::min<uint64_t>(per, n - base);
-    SKW_CUDA(ctx, cudaMemcpyAsync(d_starts + base, h_starts + base, sizeof(u32) * (size_t)nc, cudaMemcpyHostToDevice, st));
-    skw_walk_params p = *prm;
-    p.walker_base = prm->walker_base + base * stride;
-    float slice_ms = 0;
-    uint64_t slice_edges = 0;
-    rc = skw_walk_device(ctx, &p, d_starts + base, nc, d_rows, d_len + base, &slice_ms, &slice_edges);  // waits for it
-    if (rc != SKW_OK) {
-      cudaStreamSynchronize(side);
-      return rc;
-    }
-    total_ms += slice_ms;
-    total_edges += slice_edges;
-    const uint64_t slice_cells = slice_edges + nc;  // every walk holds its start plus one vertex per sampled edge
-    SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths + base, d_len + base, sizeof(u32) * (size_t)nc, cudaMemcpyDeviceToHost, side));
-    if (fits && total_cells + slice_cells > capacity_cells) fits = false;  // keep walking: the caller gets the size
-    if (fits) {
-      const int b = (int)(c & 1);
-      if (copied[b]) SKW_CUDA(ctx, cudaEventSynchronize(ctx->pk_done[b]));  // the buffer may be reallocated below
-      // The size of a result changes from call to call (another seed, other lengths).  When a buffer
-      // has to grow it grows by an eighth more than needed, so that later calls do not reallocate: a
-      // free and an allocation between two calls cost milliseconds and at times far more.
-      const size_t need = sizeof(u32) * (size_t)slice_cells;
-      if (ctx->stage_bytes[4 + b] < need || !ctx->stage[4 + b]) {
-        const size_t roomy = std::min<size_t>(need + (need >> 3) + 4096, sizeof(u32) * (size_t)nc * prm->hop_num);
-        if ((rc = ensure_bytes(ctx, &ctx->stage[4 + b], &ctx->stage_bytes[4 + b], roomy)) != SKW_OK) {
-          cudaStreamSynchronize(side);
-          return rc;
-        }
-      }
-      u32* d_packed = static_cast<u32*>(ctx->stage[4 + b]);
-      // row offsets: exclusive sum of (length + 1) in walker order
-      cub::TransformInputIterator<u64, CellsOfRow, const u32*> row_cells(d_len + base, CellsOfRow());
-      size_t tb = tmp_bytes;
-      SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(reinterpret_cast<char*>(d_offs) + offs_bytes, tb, row_cells, d_offs,
-                                                  (long long)nc, st));
-      SKW_LAUNCHED(ctx);
-      // Packed on the device, then one contiguous copy per slice: measured on B200 with 8 M PPR walks,
-      // half the time of a pack kernel that writes the pinned host buffer itself (its 4-byte stores
-      // per row do not merge into full-size bus writes).
-      pack_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(d_rows, d_packed, d_len + base, d_offs, nc, prm->hop_num,
-                                                          slice_cells, pack_err);
-      SKW_LAUNCHED(ctx);
-      SKW_CUDA(ctx, cudaEventRecord(ctx->pk_ready, st));
-      SKW_CUDA(ctx, cudaStreamWaitEvent(side, ctx->pk_ready, 0));
-      SKW_CUDA(ctx, cudaMemcpyAsync(h_packed + total_cells, d_packed, need, cudaMemcpyDeviceToHost, side));
-      SKW_CUDA(ctx, cudaEventRecord(ctx->pk_done[b], side));
-      copied[b] = true;
-    }
-    total_cells += slice_cells;
+    nc_of[c] = nc;
+    const uint64_t full = nc * prm->hop_num;
+    uint64_t guess = full;
+    if (prm->app == SKW_APP_PPR && prm->tp > 0.0f)
+      guess = std::min<uint64_t>(full, (uint64_t)((double)nc * (1.0 / prm->tp + 2.0)) + 4096);
+    if (ctx->stage[4 + c] && ctx->stage_bytes[4 + c] >= sizeof(u32) * 1024) guess = ctx->stage_bytes[4 + c] / sizeof(u32);
+    if ((rc = ensure_bytes(ctx, &ctx->stage[4 + c], &ctx->stage_bytes[4 + c], sizeof(u32) * (size_t)guess)) != SKW_OK) return rc;
+    cap[c] = std::min<uint64_t>(ctx->stage_bytes[4 + c] / sizeof(u32), full);
   }
-  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_err + 4, pack_err, 4 * sizeof(u32), cudaMemcpyDeviceToHost, st));
-  SKW_CUDA(ctx, cudaStreamSynchronize(st));
-  SKW_CUDA(ctx, cudaStreamSynchronize(side));
-  *cells = total_cells;
-  if (ms) *ms = total_ms;
-  if (sampled_edges) *sampled_edges = total_edges;
-  if (ctx->h_err[4] != DEV_OK)
-    return fail(ctx, SKW_ERR_DEVICE, "skw_walk_packed: device error %u while packing, detail %u %u %u", ctx->h_err[4],
-                ctx->h_err[5], ctx->h_err[6], ctx->h_err[7]);
-  if (!fits)
-    return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: the result needs %llu cells, the buffer holds %llu",
-                (unsigned long long)total_cells, (unsigned long long)(h_packed ? capacity_cells : 0));
-  return SKW_OK;
+  if ((rc = err_reset(ctx)) != SKW_OK) return rc;
+  unsigned long long* scratch_sum = reinterpret_cast<unsigned long long*>(ctx->d_sum) + 2;
+  auto scan_and_pack = [&](uint32_t c) -> int {
+    const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+    cub::TransformInputIterator<u64, CellsOfRow, const u32*> row_cells(d_len + base, CellsOfRow());
+    size_t tb = tmp_bytes;
+    SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(reinterpret_cast<char*>(d_offs) + offs_bytes, tb, row_cells, d_offs,
+                                                (long long)nc, st));
+    SKW_LAUNCHED(ctx);
+    // Packed on the device, then one contiguous copy per slice: measured on B200 with 8 M PPR walks,
+    // half the time of a pack kernel that writes the pinned host buffer itself (its 4-byte stores
+    // per row do not merge into full-size bus writes).
+    pack_rows_kernel<<<grid_for(ctx, nc * 8, 8), 256, 0, st>>>(d_rows + base * prm->hop_num,
+                                                              static_cast<u32*>(ctx->stage[4 + c]), d_len + base, d_offs, nc,
+                                                              prm->hop_num, cap[c], ctx->d_tot + c);
+    SKW_LAUNCHED(ctx);
+    SKW_CUDA(ctx, cudaEventRecord(ctx->pk_ready[c], st));
+    SKW_CUDA(ctx, cudaStreamWaitEvent(side, ctx->pk_ready[c], 0));
+    SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_tot + c, ctx->d_tot + c, sizeof(u64), cudaMemcpyDeviceToHost, side));
+    SKW_CUDA(ctx, cudaEventRecord(ctx->pk_tot[c], side));
+    return SKW_OK;
+  };
+  auto body = [&]() -> int {
+    SKW_CUDA(ctx, cudaMemcpyAsync(d_starts, h_starts, sizeof(u32) * (size_t)n, cudaMemcpyHostToDevice, st));
+    for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
+      const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+      skw_walk_params p = *prm;
+      p.walker_base = prm->walker_base + base * stride;
+      SKW_CUDA(ctx, cudaEventRecord(ctx->pk_t0[c], st));
+      int r = walk_launch(ctx, &p, d_starts + base, nc, d_rows + base * prm->hop_num, d_len + base, scratch_sum);
+      if (r != SKW_OK) return r;
+      SKW_CUDA(ctx, cudaEventRecord(ctx->pk_t1[c], st));
+      if ((r = scan_and_pack(c)) != SKW_OK) return r;
+      SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths + base, d_len + base, sizeof(u32) * (size_t)nc, cudaMemcpyDeviceToHost, side));
+    }
+    // the host follows the device slice by slice: learn the size, start the copy
+    uint64_t total_cells = 0;
+    bool fits = h_packed != nullptr;
+    float total_ms = 0;
+    for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
+      SKW_CUDA(ctx, cudaEventSynchronize(ctx->pk_tot[c]));
+      uint64_t slice_cells = ctx->h_tot[c];
+      if (fits && total_cells + slice_cells > capacity_cells) fits = false;  // keep going: the caller gets the size
+      if (fits && slice_cells > cap[c]) {
+        // this slice outgrew its packing buffer: grow it and pack once more (its rows and lengths are
+        // still on the device).  Growing frees the old buffer, which waits for the device.
+        const uint64_t roomy = std::min<uint64_t>(slice_cells + (slice_cells >> 3) + 4096, nc_of[c] * prm->hop_num);
+        int r = ensure_bytes(ctx, &ctx->stage[4 + c], &ctx->stage_bytes[4 + c], sizeof(u32) * (size_t)roomy);
+        if (r != SKW_OK) return r;
+        cap[c] = roomy;
+        if ((r = scan_and_pack(c)) != SKW_OK) return r;
+        SKW_CUDA(ctx, cudaEventSynchronize(ctx->pk_tot[c]));
+        slice_cells = ctx->h_tot[c];
+      }
+      if (fits) {
+        // on a stream of its own: the side stream already holds the (still waiting) count and length
+        // copies of the later slices, and this copy must not queue up behind them
+        SKW_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->pk_ready[c], 0));
+        SKW_CUDA(ctx, cudaMemcpyAsync(h_packed + total_cells, ctx->stage[4 + c], sizeof(u32) * (size_t)slice_cells,
+                                      cudaMemcpyDeviceToHost, ctx->copy_stream));
+      }
+      total_cells += slice_cells;
+      float t = 0;
+      SKW_CUDA(ctx, cudaEventElapsedTime(&t, ctx->pk_t0[c], ctx->pk_t1[c]));  // the walk is long over
+      total_ms += t;
+    }
+    SKW_CUDA(ctx, cudaStreamSynchronize(side));
+    SKW_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+    int r = err_check(ctx, "skw_walk_packed");  // synchronises the context's stream
+    if (r != SKW_OK) return r;
+    *cells = total_cells;
+    if (ms) *ms = total_ms;
+    if (sampled_edges) *sampled_edges = total_cells - n;  // every walk holds its start plus one vertex per sampled edge
+    if (!fits)
+      return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: the result needs %llu cells, the buffer holds %llu",
+                  (unsigned long long)total_cells, (unsigned long long)(h_packed ? capacity_cells : 0));
+    return SKW_OK;
+  };
+  rc = body();
+  if (rc != SKW_OK && rc != SKW_ERR_ARG) {  // leave nothing in flight that still writes the caller's buffers
+    const std::string why = ctx->err;
+    cudaStreamSynchronize(side);
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamSynchronize(st);
+    ctx->err = why;
+  }
+  return rc;
 }
 
 }  // extern "C"

@@ -120,6 +120,35 @@ def test_alias_every_degree_class_and_edge_cases(ctx, oracle):
     assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
 
 
+def test_alias_packed_builders_boundaries(ctx, oracle):
+    """Lists on both sides of every boundary of the register-resident and packed-list builders
+    (8 elements per lane; groups of 1..32 lanes; tiles of 256 and 2048; 4096), as skewed lists with
+    zeros, uniform lists (no small at all), lists with one dominant weight and lists of all-equal
+    pairs (ties between deficit and excess prefixes)."""
+    rng = np.random.default_rng(2)
+    lists = []
+    for n in (1, 2, 7, 8, 9, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 128, 129, 250, 255, 256, 257, 600, 1024, 1025,
+              2047, 2048, 2049, 4095, 4096, 4097):
+        w = (rng.uniform(0, 1, n) ** 8).astype(np.float32)
+        if n > 3:
+            w[rng.integers(0, n, n // 5)] = 0.0
+        w[rng.integers(0, n)] = 0.7
+        lists.append(w)
+        lists.append(np.full(n, 2.5, np.float32))
+        d = rng.uniform(1, 2, n).astype(np.float32)
+        d[rng.integers(0, n)] = 1.0e6
+        lists.append(d)
+        lists.append(np.tile(np.asarray([1.0, 3.0], np.float32), n // 2 + 1)[:n])
+    xadj, adj, w = _star_graph(lists)
+    ctx.upload(xadj, adj, w)
+    ctx.alias_build_offline()
+    prob, alias, valid = ctx.alias_export()
+    oprob, oalias, ovalid = oracle.alias_build(xadj, w)
+    assert np.array_equal(valid, ovalid)
+    assert np.array_equal(alias, oalias)
+    assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
+
+
 def test_alias_build_partial_range(ctx, oracle, rmat12):
     g = rmat12
     _upload(ctx, g)
@@ -761,4 +790,4 @@ def test_walk_over_a_partly_built_table_ends_at_unbuilt_vertices(ctx, oracle, rm
     valid2[half:] = 0
     op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, (prob, alias, valid2), starts, 21, seed=3)
     _cmp_walks(paths, lens, op, ol)
-    assert (ol < 20).any() and (ol == 20).any()
+    assert (ol == 0).any() and (ol > 0).any()

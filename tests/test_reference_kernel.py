@@ -1,0 +1,103 @@
+"""The reference's own offline walk kernel (sample_kernel_static, src/offline_walk.cu:75-124 of
+wpybtw/Skywalker, driven through its OfflineWalk entry function) beside this library.
+
+The reference has no golden vectors and its random stream (XORWOW seeded by thread id) cannot be
+reproduced, so the comparison is statistical: fed with the alias table THIS library builds (exported
+as the reference's prob / alias / valid arrays), the reference kernel's transitions must follow the
+edge weights (chi-square, p > 0.01), and its walks must have the same length statistics and visit
+distribution as this library's walks over the same table.  The harness is built from the reference
+tree by oracle/ref_cuda/Makefile; on a machine that has neither the tree nor the built library the
+tests are skipped.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ref():
+    from oracle import reference_kernel as R
+    if not R.available():
+        pytest.skip("oracle/_ref/libskw_ref.so was not built (no reference tree on the build machine)")
+    return R
+
+
+def _two_way_star(w):
+    """Vertex 0 points at leaves 1..n with weights w; every leaf points back at vertex 0."""
+    n = len(w)
+    xadj = np.concatenate([[0, n], n + 1 + np.arange(n)]).astype(np.uint32)
+    adj = np.concatenate([np.arange(1, n + 1), np.zeros(n)]).astype(np.uint32)
+    wgt = np.concatenate([w, np.ones(n)]).astype(np.float32)
+    return xadj, adj, wgt
+
+
+def test_reference_kernel_follows_the_weights_of_our_table(ctx, ref):
+    """Chi-square of the reference kernel's transitions out of the hub of a two-way star against the
+    edge weights, with the table this library built.  Every walker returns to the hub after each leaf
+    (a leaf has one out-edge, which the reference takes without a draw), so a walker of 200 steps makes
+    100 draws from the hub's table.  Long walks on purpose: the reference seeds one XORWOW generator per
+    thread with the thread id, and the very first outputs of generators seeded 0, 1, 2, ... are
+    measurably non-uniform (400,000 single first draws from a 2-slot table failed this test with
+    p = 3e-26), a property of that seeding, not of the table."""
+    from scipy import stats
+    rng = np.random.default_rng(3)
+    for n in (2, 7, 33, 300):
+        w = rng.uniform(1, 10, n).astype(np.float32)
+        xadj, adj, wgt = _two_way_star(w)
+        ctx.upload(xadj, adj, wgt)
+        ctx.alias_build_offline()
+        table = ctx.alias_export()
+        N, hop = 4096, 201
+        paths, lens, _ = ref.offline_walk(xadj, adj, table, np.zeros(N, np.uint32), hop)
+        assert (lens == hop - 1).all()
+        assert (paths[:, 0::2] == 0).all()
+        leaves = paths[:, 1::2].astype(np.int64).reshape(-1) - 1
+        counts = np.bincount(leaves, minlength=n)
+        wf = w.astype(np.float64)
+        chi, pval = stats.chisquare(counts, f_exp=wf / wf.sum() * len(leaves))
+        assert pval > 0.01, (n, pval)
+        # the same check on this library's walk kernel over the same table
+        ours, olens, _, _ = ctx.walk(np.zeros(N, np.uint32), hop, seed=n)
+        oleaves = ours[:, 1::2].astype(np.int64).reshape(-1) - 1
+        chi, pval = stats.chisquare(np.bincount(oleaves, minlength=n), f_exp=wf / wf.sum() * len(oleaves))
+        assert pval > 0.01, (n, pval)
+
+
+def test_reference_walks_and_ours_have_the_same_statistics(ctx, oracle, ref, rmat12):
+    """Same graph, same table, 200,000 walkers x 20 steps: the two implementations draw from different
+    random streams, so rows differ, but the walk-length histogram and the visit counts of the most
+    visited vertices must agree (two-sample chi-square, p > 0.01)."""
+    from scipy import stats
+    g = rmat12
+    ctx.upload(g.xadj, g.adjncy, g.adjwgt)
+    ctx.alias_build_offline()
+    table = ctx.alias_export()
+    N, hop = 200000, 21
+    starts = oracle.gen_starts(N, g.V, 77)
+    ours_p, ours_l, _, _ = ctx.walk(starts, hop, seed=5)
+    ref_p, ref_l, sec = ref.offline_walk(g.xadj, g.adjncy, table, starts, hop)
+    assert sec > 0
+    # every step of the reference walk follows an edge of the graph
+    for s in range(3):
+        alive = ref_l > s
+        src, dst = ref_p[alive, s].astype(np.int64), ref_p[alive, s + 1]
+        lo, hi = g.xadj[src], g.xadj[src + 1]
+        ok = np.fromiter((d in g.adjncy[a:b] for a, b, d in zip(lo[:2000], hi[:2000], dst[:2000])), bool)
+        assert ok.all()
+    # walk lengths: a walk ends early only at a vertex without out-edges
+    ha = np.bincount(ours_l, minlength=hop)
+    hb = np.bincount(ref_l, minlength=hop)
+    keep = (ha + hb) >= 20
+    _, p_len, _, _ = stats.chi2_contingency(np.vstack([ha[keep], hb[keep]]))
+    assert p_len > 0.01, p_len
+    # visit counts after 3 steps, 40 most visited vertices (by the pooled count) + the rest
+    def visits(paths, lens):
+        v = paths[lens >= 3, 3].astype(np.int64)
+        return np.bincount(v, minlength=g.V)
+    va, vb = visits(ours_p, ours_l), visits(ref_p, ref_l)
+    top = np.argsort(-(va + vb))[:40]
+    ta = np.append(va[top], va.sum() - va[top].sum())
+    tb = np.append(vb[top], vb.sum() - vb[top].sum())
+    _, p_vis, _, _ = stats.chi2_contingency(np.vstack([ta, tb]))
+    assert p_vis > 0.01, p_vis
