@@ -233,29 +233,25 @@ __device__ __forceinline__ void coop_scan_u64(u64& v, u64& total, u64* s_tmp) {
   }
 }
 
-// The same for three values at once (s_tmp: 3 * (NT/32 + 1) entries).
+// The same for a 64-bit and a 32-bit value at once (s_tmp: 2 * (NT/32 + 1) entries).
 template <int NT>
-__device__ __forceinline__ void coop_scan3(u64& a, u64& b, u32& c, u64& ta, u64& tb, u32& tc, u64* s_tmp) {
+__device__ __forceinline__ void coop_scan2(u64& a, u32& c, u64& ta, u32& tc, u64* s_tmp) {
   const u32 lane = threadIdx.x & 31;
-  u64 ia = a, ib = b;
+  u64 ia = a;
   u32 ic = c;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const u64 xa = __shfl_up_sync(0xFFFFFFFFu, ia, o);
-    const u64 xb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
     const u32 xc = __shfl_up_sync(0xFFFFFFFFu, ic, o);
     if (lane >= (u32)o) {
       ia += xa;
-      ib += xb;
       ic += xc;
     }
   }
   if constexpr (NT == 32) {
     ta = __shfl_sync(0xFFFFFFFFu, ia, 31);
-    tb = __shfl_sync(0xFFFFFFFFu, ib, 31);
     tc = __shfl_sync(0xFFFFFFFFu, ic, 31);
     a = ia - a;
-    b = ib - b;
     c = ic - c;
   } else {
     constexpr int NW = NT / 32, ST = NW + 1;
@@ -263,44 +259,37 @@ __device__ __forceinline__ void coop_scan3(u64& a, u64& b, u32& c, u64& ta, u64&
     __syncthreads();
     if (lane == 31) {
       s_tmp[warp] = ia;
-      s_tmp[ST + warp] = ib;
-      s_tmp[2 * ST + warp] = ic;
+      s_tmp[ST + warp] = ic;
     }
     __syncthreads();
     if (warp == 0) {
-      u64 xa = lane < NW ? s_tmp[lane] : 0, xb = lane < NW ? s_tmp[ST + lane] : 0;
-      u32 xc = lane < NW ? (u32)s_tmp[2 * ST + lane] : 0;
-      u64 ya = xa, yb = xb;
+      u64 xa = lane < NW ? s_tmp[lane] : 0;
+      u32 xc = lane < NW ? (u32)s_tmp[ST + lane] : 0;
+      u64 ya = xa;
       u32 yc = xc;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const u64 pa = __shfl_up_sync(0xFFFFFFFFu, ya, o);
-        const u64 pb = __shfl_up_sync(0xFFFFFFFFu, yb, o);
         const u32 pc = __shfl_up_sync(0xFFFFFFFFu, yc, o);
         if (lane >= (u32)o) {
           ya += pa;
-          yb += pb;
           yc += pc;
         }
       }
       if (lane < NW) {
         s_tmp[lane] = ya - xa;
-        s_tmp[ST + lane] = yb - xb;
-        s_tmp[2 * ST + lane] = yc - xc;
+        s_tmp[ST + lane] = yc - xc;
       }
       if (lane == 31) {
         s_tmp[NW] = ya;
-        s_tmp[ST + NW] = yb;
-        s_tmp[2 * ST + NW] = yc;
+        s_tmp[ST + NW] = yc;
       }
     }
     __syncthreads();
     ta = s_tmp[NW];
-    tb = s_tmp[ST + NW];
-    tc = (u32)s_tmp[2 * ST + NW];
+    tc = (u32)s_tmp[ST + NW];
     a = s_tmp[warp] + ia - a;
-    b = s_tmp[ST + warp] + ib - b;
-    c = (u32)s_tmp[2 * ST + warp] + ic - c;
+    c = (u32)s_tmp[ST + warp] + ic - c;
   }
 }
 
@@ -347,44 +336,60 @@ __device__ __forceinline__ void merge_window(u32 t, u32 nl, u32 Sl, const u64* s
     j = k0 - lo;
   }
   u64 dsx = i ? sA[i - 1] : dsx_in;  // deficit of the smalls before small i
+  // the heads of both lists stay in registers: one pair of shared-memory loads per output
+  u64 sk = 0, lk = 0;
+  u32 sp = 0, lp = next_pos;  // a small left over after the window's last large belongs to the first
+  bool lhave = j < Ll;        // large of the next window
+  if (i < Sl) {
+    sk = sA[i];
+    sp = sP[i];
+  }
+  if (lhave) {
+    lk = sA[nl - 1 - j];
+    lp = sP[nl - 1 - j];
+  }
   for (u32 k = k0; k < k1; ++k) {
     Slot out;
     u32 p;
-    const u64 xl = j < Ll ? sA[nl - 1 - j] : 0;
-    // a small left over after the window's last large belongs to the first large of the next window
-    if (i < Sl && (j >= Ll || dsx <= xl)) {
-      p = sP[i];
-      const u64 dincl = sA[i];
-      u32 donor = j < Ll ? sP[nl - 1 - j] : next_pos;
-      if (donor == kNoNext) {
+    if (i < Sl && (!lhave || dsx <= lk)) {
+      p = sp;
+      if (lp == kNoNext) {
         dev_fail(err, DEV_ERR_INTERNAL, v, p, 10);
-        donor = p;
+        out.alias = p;
+      } else {
+        out.alias = lp;
       }
-      out.alias = donor;
-      out.prob = mass_to_prob_fast(C - (dincl - dsx), B);
-      dsx = dincl;
-      ++i;
+      out.prob = mass_to_prob_fast(C - (sk - dsx), B);
+      dsx = sk;
+      if (++i < Sl) {
+        sk = sA[i];
+        sp = sP[i];
+      }
     } else {
-      if (j >= Ll) {  // cannot happen: a window's share of larges is fixed by its boundaries
+      if (!lhave) {  // cannot happen: a window's share of larges is fixed by its boundaries
         dev_fail(err, DEV_ERR_INTERNAL, v, k, 9);
         break;
       }
-      p = sP[nl - 1 - j];
+      p = lp;
+      const u64 xl = lk;
+      ++j;
+      lhave = j < Ll;
+      lp = next_pos;
+      if (lhave) {
+        lk = sA[nl - 1 - j];
+        lp = sP[nl - 1 - j];
+      }
       if (dsx <= xl) {  // only possible once every small is placed: the large owns one full bucket
         out.alias = p;
         out.prob = 1.0f;
+      } else if (lp == kNoNext) {
+        dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
+        out.alias = p;
+        out.prob = 1.0f;
       } else {
-        const u32 nx = j + 1 < Ll ? sP[nl - 2 - j] : next_pos;
-        if (nx == kNoNext) {
-          dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
-          out.alias = p;
-          out.prob = 1.0f;
-        } else {
-          out.alias = nx;
-          out.prob = mass_to_prob_fast(xl + C - dsx, B);
-        }
+        out.alias = lp;
+        out.prob = mass_to_prob_fast(xl + C - dsx, B);
       }
-      ++j;
     }
     slots[(u64)off + p] = out;
   }
@@ -420,7 +425,9 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
   const u64 nC = (u64)n << B;
   const double K = mass_factor(n, B, W);
 
-  u64 cQ = 0, cD = 0, cX = 0;  // carries between tiles (the same value in every thread)
+  // Only the deficit prefix D and the count of larges are scanned; the excess prefix follows from the
+  // cumulative mass: sum over k <= p of (M_k - C) = X(p) - D(p), so X(p) = D(p) + g(Q_(p+1)) - (p + 1) * C.
+  u64 cQ = 0, cD = 0;  // carries between tiles (the same value in every thread)
   u32 cL = 0;
   for (u32 base = 0; base < n; base += NT * EPT) {
     const u32 p0 = base + t * EPT;
@@ -435,8 +442,9 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
     coop_scan_u64<NT>(Qex, tq, s_tmp);
     Qex += cQ;
     cQ += tq;
-    u64 g_prev = cum_mass(Qex, W, nC, K), Q = Qex;
-    u64 sd = 0, sx = 0;
+    const u64 gex = cum_mass(Qex, W, nC, K);
+    u64 g_prev = gex, Q = Qex;
+    u64 sd = 0;
     u32 sl = 0;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
@@ -446,33 +454,29 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
         m[k] = g - g_prev;
         g_prev = g;
         if (m[k] < C) sd += C - m[k];
-        else {
-          sx += m[k] - C;
-          ++sl;
-        }
+        else ++sl;
       }
     }
-    u64 td, tx;
+    u64 td;
     u32 tl;
-    coop_scan3<NT>(sd, sx, sl, td, tx, tl, s_tmp);
-    u64 Dr = sd + cD, Xr = sx + cX;
+    coop_scan2<NT>(sd, sl, td, tl, s_tmp);
+    u64 Dr = sd + cD, gc = gex;
     u32 Lr = sl + cL;
     cD += td;
-    cX += tx;
     cL += tl;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
       const u32 p = p0 + k;
       if (p < n) {
+        gc += m[k];
         if (m[k] < C) {
           Dr += C - m[k];
           const u32 i = p - Lr;  // smalls before p
           A[i] = Dr;
           P[i] = p;
         } else {
-          Xr += m[k] - C;
           const u32 j = Lr++;    // larges before p
-          A[n - 1 - j] = Xr;
+          A[n - 1 - j] = Dr + gc - ((u64)(p + 1) << B);
           P[n - 1 - j] = p;
         }
       }
@@ -480,7 +484,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
   }
   coop_sync<NT>();
   const u32 L = cL, S = n - L;
-  if (L == 0 || cD != cX) {  // mass conservation guarantees both
+  if (L == 0) {  // mass conservation guarantees a large
     if (t == 0) dev_fail(err, DEV_ERR_INTERNAL, v, L, 7);
     for (u32 p = t; p < n; p += NT) slots[(u64)off + p] = Slot{1.0f, p};
     if (t == 0) valid[v] = 1;
@@ -893,7 +897,7 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
                                                              unsigned char* __restrict__ scratch,
                                                              u64 cap, u32* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ u64 s_tmp[3 * (NT / 32 + 1)];
+  __shared__ u64 s_tmp[2 * (NT / 32 + 1)];
   unsigned char* store = WIN ? scratch + (u64)blockIdx.x * cap * 12ull : smem;
   u64* A = reinterpret_cast<u64*>(store);
   u32* P = reinterpret_cast<u32*>(A + cap);

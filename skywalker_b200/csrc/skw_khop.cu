@@ -10,6 +10,8 @@
 // (seed id, child cell, hop) and stores one coalesced word; no queues and no atomics on the data
 // path.  Online mode first builds the tables of the distinct vertices of the hop's frontier with
 // the degree-bucketed builders, then runs the same draw kernel.
+#include <algorithm>
+
 #include "skw_ctx.h"
 
 namespace skw {
@@ -205,24 +207,30 @@ int skw_khop_layout(const skw_khop_params* prm, uint32_t* cells_per_seed, uint32
   return SKW_OK;
 }
 
-int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds,
-                           uint64_t n, uint32_t* d_data, uint32_t* d_sample_lengths, float* ms,
-                           uint64_t* sampled_edges) {
-  if (!ctx || !prm) return SKW_ERR_ARG;
+// Argument and state checks of the k-hop entry points.
+static int khop_validate(skw_ctx* ctx, const skw_khop_params* prm) {
   int rc = khop_check(ctx, prm);
   if (rc != SKW_OK) return rc;
-  if (n && (!d_seeds || !d_data || !d_sample_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: null buffer");
   if (!ctx->xadj) return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: no graph resident");
   const bool unbiased = (prm->flags & SKW_KHOP_UNBIASED) != 0;
   const bool online = prm->mode == SKW_MODE_ONLINE && !unbiased;
   if (!online && !unbiased && !ctx->table_ready)
     return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: offline mode needs skw_alias_build_offline or skw_alias_import first");
   if (online && !ctx->adjwgt) return fail(ctx, SKW_ERR_STATE, "skw_sample_khop: online mode needs the edge weights");
-  DeviceGuard g(ctx->device);
+  return SKW_OK;
+}
+
+// Queue the kernels of one batch of seeds on the context's stream (sampled edges add up in d_sum[0]).
+static int khop_launch(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds, uint64_t n,
+                       uint32_t* d_data, uint32_t* d_sample_lengths, uint64_t instance_base) {
+  const bool unbiased = (prm->flags & SKW_KHOP_UNBIASED) != 0;
+  const bool online = prm->mode == SKW_MODE_ONLINE && !unbiased;
+  int rc;
   if (online) {
     drop_records(ctx);  // online builds overwrite table slots
     if ((rc = alloc_table(ctx)) != SKW_OK) return rc;
   }
+  if (!n) return SKW_OK;
   uint32_t width[6], offs[6], cells = 0, w = 1;
   for (uint32_t h = 0; h <= prm->nhops; ++h) {
     if (h) w *= prm->fanout[h - 1];
@@ -240,39 +248,50 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
   a.err = ctx->d_err;
   a.n = n;
   a.seed = prm->seed;
-  a.instance_base = prm->instance_base;
+  a.instance_base = instance_base;
   a.instance_stride = prm->instance_stride ? prm->instance_stride : 1;
   a.V = ctx->V;
   a.cells = cells;
   a.lens_per = offs[prm->nhops];
   a.flags = prm->flags;
   cudaStream_t st = ctx->stream;
+  const uint64_t cap = (uint64_t)ctx->sm_count * 16;
+  uint64_t want = (n + 255) / 256;
+  khop_init_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(d_seeds, n, cells, d_data);
+  SKW_LAUNCHED(ctx);
+  for (uint32_t h = 0; h < prm->nhops; ++h) {
+    if (online && (rc = frontier_collect(ctx, d_data, n * width[h], width[h], cells, offs[h], nullptr, true)) != SKW_OK)
+      return rc;
+    a.offs_parent = offs[h];
+    a.offs_child = offs[h + 1];
+    a.width_parent = width[h];
+    a.fanout = prm->fanout[h];
+    a.hop = h + 1;
+    if ((prm->flags & SKW_KHOP_DISTINCT) && !unbiased) {
+      want = (n * width[h] + 7) / 8;  // one warp per parent vertex
+      khop_distinct_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
+    } else {
+      want = (n * width[h + 1] + 255) / 256;
+      khop_hop_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
+    }
+    SKW_LAUNCHED(ctx);
+  }
+  return SKW_OK;
+}
+
+int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds,
+                           uint64_t n, uint32_t* d_data, uint32_t* d_sample_lengths, float* ms,
+                           uint64_t* sampled_edges) {
+  if (!ctx || !prm) return SKW_ERR_ARG;
+  if (n && (!d_seeds || !d_data || !d_sample_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: null buffer");
+  int rc = khop_validate(ctx, prm);
+  if (rc != SKW_OK) return rc;
+  DeviceGuard g(ctx->device);
+  cudaStream_t st = ctx->stream;
   if ((rc = err_reset(ctx)) != SKW_OK) return rc;
   SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
-  if (n) {
-    const uint64_t cap = (uint64_t)ctx->sm_count * 16;
-    uint64_t want = (n + 255) / 256;
-    khop_init_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(d_seeds, n, cells, d_data);
-    SKW_LAUNCHED(ctx);
-    for (uint32_t h = 0; h < prm->nhops; ++h) {
-      if (online && (rc = frontier_collect(ctx, d_data, n * width[h], width[h], cells, offs[h], nullptr, true)) != SKW_OK)
-        return rc;
-      a.offs_parent = offs[h];
-      a.offs_child = offs[h + 1];
-      a.width_parent = width[h];
-      a.fanout = prm->fanout[h];
-      a.hop = h + 1;
-      if ((prm->flags & SKW_KHOP_DISTINCT) && !unbiased) {
-        want = (n * width[h] + 7) / 8;  // one warp per parent vertex
-        khop_distinct_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
-      } else {
-        want = (n * width[h + 1] + 255) / 256;
-        khop_hop_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(a);
-      }
-      SKW_LAUNCHED(ctx);
-    }
-  }
+  if ((rc = khop_launch(ctx, prm, d_seeds, n, d_data, d_sample_lengths, prm->instance_base)) != SKW_OK) return rc;
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
   SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
   if ((rc = err_check(ctx, "skw_sample_khop")) != SKW_OK) return rc;
@@ -288,21 +307,53 @@ int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_
   int rc = skw_khop_layout(prm, &cells, &lens);
   if (rc != SKW_OK) return fail(ctx, rc, "skw_sample_khop: bad hop description");
   if (n && (!h_seeds || !h_data || !h_sample_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop: null buffer");
+  if ((rc = khop_validate(ctx, prm)) != SKW_OK) return rc;
   DeviceGuard g(ctx->device);
   const size_t nb = sizeof(uint32_t) * (size_t)n;
   if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], nb)) != SKW_OK) return rc;
   if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], nb * cells)) != SKW_OK) return rc;
   if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], nb * lens)) != SKW_OK) return rc;
-  if (n) SKW_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0], h_seeds, nb, cudaMemcpyHostToDevice, ctx->stream));
-  rc = skw_sample_khop_device(ctx, prm, static_cast<uint32_t*>(ctx->stage[0]), n,
-                              static_cast<uint32_t*>(ctx->stage[1]), static_cast<uint32_t*>(ctx->stage[2]),
-                              ms, sampled_edges);
-  if (rc != SKW_OK) return rc;
-  if (n) {
-    SKW_CUDA(ctx, cudaMemcpyAsync(h_data, ctx->stage[1], nb * cells, cudaMemcpyDeviceToHost, ctx->stream));
-    SKW_CUDA(ctx, cudaMemcpyAsync(h_sample_lengths, ctx->stage[2], nb * lens, cudaMemcpyDeviceToHost, ctx->stream));
+  uint32_t* d_seeds = static_cast<uint32_t*>(ctx->stage[0]);
+  uint32_t* d_data = static_cast<uint32_t*>(ctx->stage[1]);
+  uint32_t* d_lens = static_cast<uint32_t*>(ctx->stage[2]);
+  cudaStream_t st = ctx->stream, side = ctx->side_stream;
+  // A result tree is dense (every cell crosses the bus), so a large batch runs as up to four slices of
+  // seeds: while the kernels of slice c run on the context's stream, the tree of slice c - 1 goes home
+  // on the side stream.  Seed ids, hence samples, do not depend on the slicing; online mode builds the
+  // tables of a vertex once per slice and hop instead of once per batch and hop.
+  const uint64_t tree_bytes = (uint64_t)n * cells * sizeof(uint32_t);
+  const uint32_t slices = (n >= 4096 && tree_bytes >= (32ull << 20)) ? 4 : (n >= 2048 && tree_bytes >= (8ull << 20) ? 2 : 1);
+  const uint64_t per = (n + slices - 1) / slices;
+  const uint64_t stride = prm->instance_stride ? prm->instance_stride : 1;
+  if ((rc = err_reset(ctx)) != SKW_OK) return rc;
+  SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
+  if (n) SKW_CUDA(ctx, cudaMemcpyAsync(d_seeds, h_seeds, nb, cudaMemcpyHostToDevice, st));
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+  for (uint32_t c = 0; c < slices; ++c) {
+    const uint64_t base = (uint64_t)c * per;
+    if (base >= n) break;
+    const uint64_t nc = std::min<uint64_t>(per, n - base);
+    rc = khop_launch(ctx, prm, d_seeds + base, nc, d_data + base * cells, d_lens + base * lens,
+                     prm->instance_base + base * stride);
+    if (rc != SKW_OK) {
+      cudaStreamSynchronize(side);
+      cudaStreamSynchronize(st);
+      return rc;
+    }
+    SKW_CUDA(ctx, cudaEventRecord(ctx->pk_ready[c], st));
+    SKW_CUDA(ctx, cudaStreamWaitEvent(side, ctx->pk_ready[c], 0));
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_data + base * cells, d_data + base * cells, sizeof(uint32_t) * (size_t)nc * cells,
+                                  cudaMemcpyDeviceToHost, side));
+    SKW_CUDA(ctx, cudaMemcpyAsync(h_sample_lengths + base * lens, d_lens + base * lens,
+                                  sizeof(uint32_t) * (size_t)nc * lens, cudaMemcpyDeviceToHost, side));
   }
-  SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+  SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
+  const int rc_side = cudaStreamSynchronize(side) == cudaSuccess ? SKW_OK : SKW_ERR_CUDA;
+  if ((rc = err_check(ctx, "skw_sample_khop")) != SKW_OK) return rc;
+  if (rc_side != SKW_OK) return fail(ctx, SKW_ERR_CUDA, "skw_sample_khop: copying the result failed");
+  if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+  if (sampled_edges) *sampled_edges = *ctx->h_sum;
   return SKW_OK;
 }
 

@@ -976,9 +976,11 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
     return SKW_OK;
   };
   auto body = [&]() -> int {
-    SKW_CUDA(ctx, cudaMemcpyAsync(d_starts, h_starts, sizeof(u32) * (size_t)n, cudaMemcpyHostToDevice, st));
     for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
       const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+      // the start vertices of a slice come in right before its walk: a quarter of the input at a time,
+      // on the bus together with the results of the slice before
+      SKW_CUDA(ctx, cudaMemcpyAsync(d_starts + base, h_starts + base, sizeof(u32) * (size_t)nc, cudaMemcpyHostToDevice, st));
       skw_walk_params p = *prm;
       p.walker_base = prm->walker_base + base * stride;
       SKW_CUDA(ctx, cudaEventRecord(ctx->pk_t0[c], st));

@@ -791,3 +791,56 @@ def test_walk_over_a_partly_built_table_ends_at_unbuilt_vertices(ctx, oracle, rm
     op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, (prob, alias, valid2), starts, 21, seed=3)
     _cmp_walks(paths, lens, op, ol)
     assert (ol == 0).any() and (ol > 0).any()
+
+
+@pytest.mark.parametrize("mode", [MODE_OFFLINE, MODE_ONLINE])
+def test_khop_distinct_bit_exact(ctx, oracle, rmat16, rmat12, mode):
+    """SKW_KHOP_DISTINCT (the rule of the reference's online sampler, src/online_sample_new.cu:73-111):
+    bit-exact against the oracle, children of one parent are distinct, a parent whose degree is at most
+    the fan-out hands over all of its neighbours."""
+    from skywalker_b200 import KHOP_DISTINCT
+    for g, fanout, nseeds in ((rmat16, [25, 10], 1500), (rmat12, [6, 5], 800), (rmat12, [40], 500)):
+        _upload(ctx, g)
+        ctx.alias_build_offline()
+        table = oracle.alias_build(g.xadj, g.adjwgt)
+        seeds = oracle.gen_starts(nseeds, g.V, 12)
+        data, sl, _, edges = ctx.sample_khop(seeds, fanout, mode=mode, flags=KHOP_DISTINCT, seed=9)
+        odata, osl = oracle.khop(g.xadj, g.adjncy, g.adjwgt, table, seeds, fanout, online=(mode == MODE_ONLINE),
+                                 flags=KHOP_DISTINCT, seed=9)
+        assert np.array_equal(sl, osl)
+        assert np.array_equal(data, odata)
+        assert edges == int(sl.sum())
+        deg = np.diff(g.xadj.astype(np.int64))
+        f1 = fanout[0]
+        for s in range(0, nseeds, 7):                      # hop 1 of a sample of the seeds
+            d = int(deg[seeds[s]])
+            kids = data[s, 1:1 + f1]
+            got = int(sl[s, 0])
+            assert got == min(d, f1) or (d > f1 and got <= f1)
+            assert (kids[got:] == 0xFFFFFFFF).all()
+            lo, hi = int(g.xadj[seeds[s]]), int(g.xadj[seeds[s] + 1])
+            if d <= f1:
+                assert np.array_equal(kids[:got], g.adjncy[lo:hi])
+            else:
+                assert len(set(kids[:got].tolist())) == got   # adjacency lists hold no duplicates
+
+
+def test_khop_distinct_runs_out_of_trials(ctx, oracle):
+    """One neighbour carries almost all the weight: most trials repeat it, so fewer than fan-out
+    distinct neighbours are found within the 352 trials, and the length says how many."""
+    from skywalker_b200 import KHOP_DISTINCT
+    n = 64
+    w = np.full(n, 1e-6, np.float32)
+    w[5] = 1.0
+    xadj = np.asarray([0, n] + [n] * n, np.uint32)
+    adj = np.arange(1, n + 1, dtype=np.uint32)
+    ctx.upload(xadj, adj, w)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(xadj, w)
+    seeds = np.zeros(300, np.uint32)
+    data, sl, _, _ = ctx.sample_khop(seeds, [20], flags=KHOP_DISTINCT, seed=4)
+    odata, osl = oracle.khop(xadj, adj, w, table, seeds, [20], flags=KHOP_DISTINCT, seed=4)
+    assert np.array_equal(sl, osl) and np.array_equal(data, odata)
+    assert (sl[:, 0] >= 1).all() and (sl[:, 0] < 20).any()
+    with pytest.raises(Exception):                          # fan-outs above 256 are refused with the flag
+        ctx.sample_khop(seeds, [300], flags=KHOP_DISTINCT, seed=4)

@@ -214,3 +214,27 @@ def test_alias_denormal_and_huge_weights_reconstruct(oracle):
         want = w.astype(np.float64) / w.astype(np.float64).sum()
         # quantisation keeps 2^-39 of the largest weight: weights far below that may round to zero mass
         assert np.allclose(got, want, rtol=1e-6, atol=2.0 ** -38)
+
+
+def test_khop_distinct_rule(oracle):
+    """flags = 4: children of a parent are distinct columns, in trial order; degree <= fan-out copies
+    the whole neighbour list; with a fan-out the degree covers, every neighbour appears exactly once."""
+    x, a = oracle.gen_rmat(10, 12 << 10, seed=4)
+    w = oracle.gen_weights(len(a), 2)
+    table = oracle.alias_build(x, w)
+    seeds = oracle.gen_starts(400, len(x) - 1, 6)
+    data, sl = oracle.khop(x, a, w, table, seeds, [8, 3], flags=4, seed=1)
+    data_on, sl_on = oracle.khop(x, a, w, None, seeds, [8, 3], online=True, flags=4, seed=1)
+    assert np.array_equal(data, data_on) and np.array_equal(sl, sl_on)
+    deg = np.diff(x.astype(np.int64))
+    for s in range(len(seeds)):
+        d, got = int(deg[seeds[s]]), int(sl[s, 0])
+        kids = data[s, 1:9]
+        assert (kids[got:] == 0xFFFFFFFF).all()
+        if d <= 8:
+            assert got == d and np.array_equal(kids[:got], a[x[seeds[s]]:x[seeds[s] + 1]])
+        else:
+            assert got <= 8 and len(set(kids[:got].tolist())) == got
+    # with replacement (flags = 0) repeats do occur somewhere
+    rdata, _ = oracle.khop(x, a, w, table, seeds, [8, 3], flags=0, seed=1)
+    assert any(len(set(r[1:9].tolist())) < 8 for r in rdata if r[1] != 0xFFFFFFFF)
