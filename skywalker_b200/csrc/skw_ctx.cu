@@ -1,4 +1,5 @@
 // Context, resident graph, table import/export and the Galois .gr reader.
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -77,6 +78,9 @@ static void free_graph(skw_ctx* ctx) {
   cudaFree(ctx->slots);
   cudaFree(ctx->valid);
   cudaFree(ctx->stamp);
+  cudaFree(ctx->prep_memo);
+  ctx->prep_memo = nullptr;
+  ctx->prep_stamp = 0;
   cudaFree(ctx->records);
   cudaFree(ctx->vinfo);
   cudaFree(ctx->vbits);
@@ -511,7 +515,72 @@ int skw_graph_free_weights(skw_ctx* ctx) {
   return SKW_OK;
 }
 
-// Galois .gr version 1 (include/graph.cuh:164-327 of the reference).
+// Galois .gr version 1 (include/graph.cuh:164-327 of the reference), ingested on the GPU: the file
+// is read in 64 MB pieces into two pinned buffers that alternate, each piece goes to the device while
+// the next one is being read, and what the reference does per element on the host happens there --
+// 64-bit end offsets narrowed to 32 bits (and checked against numEdge), 32-bit edge data converted to
+// float by value; destinations need no conversion and land in place.  No full-size host array exists
+// at any time, and the structural checks (offsets non-decreasing, destinations below V) are the
+// device pass every upload goes through.
+__global__ void __launch_bounds__(256) narrow_offsets_kernel(const uint64_t* __restrict__ ends, size_t n,
+                                                             uint64_t num_edge, uint32_t* __restrict__ xadj_from1,
+                                                             uint32_t first_node, uint32_t* __restrict__ err) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint64_t e = ends[i];
+    if (e > num_edge) dev_fail(err, DEV_ERR_INDEX, first_node + (uint32_t)i, (uint32_t)(e >> 32), (uint32_t)e);
+    xadj_from1[i] = (uint32_t)(e > num_edge ? num_edge : e);
+  }
+}
+__global__ void __launch_bounds__(256) edge_data_to_float_kernel(const uint32_t* __restrict__ raw, size_t n,
+                                                                 float* __restrict__ w) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    w[i] = (float)raw[i];
+}
+
+namespace {
+// Two pinned buffers and two device buffers of kPiece bytes, used alternately: piece k may be read
+// from the file while piece k - 1 is still on its way to the device.
+struct GrPipe {
+  static constexpr size_t kPiece = 64u << 20;
+  skw_ctx* ctx;
+  unsigned char* h[2] = {nullptr, nullptr};
+  unsigned char* d[2] = {nullptr, nullptr};
+  cudaEvent_t done[2] = {nullptr, nullptr};
+  bool busy[2] = {false, false};
+  int cur = 0;
+  explicit GrPipe(skw_ctx* c) : ctx(c) {}
+  ~GrPipe() {
+    cudaStreamSynchronize(ctx->stream);
+    for (int i = 0; i < 2; ++i) {
+      if (h[i]) cudaFreeHost(h[i]);
+      if (d[i]) cudaFree(d[i]);
+      if (done[i]) cudaEventDestroy(done[i]);
+    }
+  }
+  int init() {
+    for (int i = 0; i < 2; ++i) {
+      SKW_CUDA(ctx, cudaMallocHost(&h[i], kPiece));
+      SKW_CUDA(ctx, cudaMalloc(&d[i], kPiece));
+      SKW_CUDA(ctx, cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
+    }
+    return SKW_OK;
+  }
+  // The next free pair of buffers (waits until the device is done with its previous piece).
+  int next(int* slot) {
+    cur ^= 1;
+    if (busy[cur]) SKW_CUDA(ctx, cudaEventSynchronize(done[cur]));
+    busy[cur] = false;
+    *slot = cur;
+    return SKW_OK;
+  }
+  int submitted(int slot) {
+    SKW_CUDA(ctx, cudaEventRecord(done[slot], ctx->stream));
+    busy[slot] = true;
+    return SKW_OK;
+  }
+};
+}  // namespace
+
 int skw_graph_load_gr(skw_ctx* ctx, const char* path, int weight_mode, uint32_t weightrange,
                       uint64_t weight_seed) {
   if (!ctx || !path) return SKW_ERR_ARG;
@@ -534,55 +603,100 @@ int skw_graph_load_gr(skw_ctx* ctx, const char* path, int weight_mode, uint32_t 
                 path, (unsigned long long)size_edge_ty);
   if (weight_mode == 0 && size_edge_ty != 4)
     return fail(ctx, SKW_ERR_IO, "%s: file carries no edge data but weights were requested", path);
-  std::vector<uint64_t> ends(num_node);
-  if (num_node && fread(ends.data(), 8, num_node, f) != num_node)
-    return fail(ctx, SKW_ERR_IO, "%s: short offset array", path);
-  std::vector<uint32_t> xadj(num_node + 1);
-  xadj[0] = 0;
-  uint64_t prev = 0;
-  for (uint64_t i = 0; i < num_node; ++i) {
-    if (ends[i] < prev || ends[i] > num_edge)
-      return fail(ctx, SKW_ERR_IO, "%s: offset of node %llu is not monotone / exceeds numEdge",
-                  path, (unsigned long long)i);
-    prev = ends[i];
-    xadj[i + 1] = (uint32_t)ends[i];
-  }
-  if (prev != num_edge)
-    return fail(ctx, SKW_ERR_IO, "%s: last offset %llu differs from numEdge %llu", path,
-                (unsigned long long)prev, (unsigned long long)num_edge);
-  std::vector<uint64_t>().swap(ends);
-  std::vector<uint32_t> adj(num_edge ? num_edge : 1);
-  if (num_edge && fread(adj.data(), 4, num_edge, f) != num_edge)
-    return fail(ctx, SKW_ERR_IO, "%s: short destination array", path);
-  for (uint64_t i = 0; i < num_edge; ++i)
-    if (adj[i] >= num_node)
-      return fail(ctx, SKW_ERR_IO, "%s: destination %u of edge %llu is out of range", path, adj[i],
-                  (unsigned long long)i);
-  std::vector<float> wgt;
-  if (weight_mode == 0) {
-    if (num_edge & 1) {
-      uint32_t pad;
-      if (fread(&pad, 4, 1, f) != 1) return fail(ctx, SKW_ERR_IO, "%s: short padding", path);
-    }
-    std::vector<uint32_t> raw(num_edge ? num_edge : 1);
-    if (num_edge && fread(raw.data(), 4, num_edge, f) != num_edge)
-      return fail(ctx, SKW_ERR_IO, "%s: short edge-data array", path);
-    wgt.resize(num_edge);
-    for (uint64_t i = 0; i < num_edge; ++i) wgt[i] = (float)raw[i];
-  }
-  int rc = skw_graph_upload(ctx, (uint32_t)num_node, num_edge, xadj.data(), adj.data(),
-                            weight_mode == 0 ? wgt.data() : nullptr);
-  if (rc != SKW_OK) return rc;
   DeviceGuard g(ctx->device);
+  free_graph(ctx);
+  const uint32_t V = (uint32_t)num_node;
+  const uint64_t E = num_edge;
+  // on any failure below the half-filled arrays are released again
+  auto body = [&]() -> int {
+    SKW_CUDA(ctx, cudaMalloc(&ctx->xadj, sizeof(uint32_t) * ((size_t)V + 1)));
+    SKW_CUDA(ctx, cudaMalloc(&ctx->adjncy, sizeof(uint32_t) * (E ? E : 1)));
+    SKW_CUDA(ctx, cudaMalloc(&ctx->adjwgt, sizeof(float) * (E ? E : 1)));
+    ctx->owns_graph = ctx->owns_weights = true;
+    ctx->V = V;
+    ctx->E = E;
+    cudaStream_t st = ctx->stream;
+    int rc = err_reset(ctx);
+    if (rc != SKW_OK) return rc;
+    SKW_CUDA(ctx, cudaMemsetAsync(ctx->xadj, 0, sizeof(uint32_t), st));
+    GrPipe pipe(ctx);
+    if ((rc = pipe.init()) != SKW_OK) return rc;
+    const int grid = ctx->sm_count * 4;
+    // numNode x u64 end offsets -> xadj[1 ..]
+    for (uint64_t i = 0; i < num_node;) {
+      const size_t cnt = (size_t)std::min<uint64_t>(num_node - i, GrPipe::kPiece / 8);
+      int s;
+      if ((rc = pipe.next(&s)) != SKW_OK) return rc;
+      if (fread(pipe.h[s], 8, cnt, f) != cnt) return fail(ctx, SKW_ERR_IO, "%s: short offset array", path);
+      SKW_CUDA(ctx, cudaMemcpyAsync(pipe.d[s], pipe.h[s], cnt * 8, cudaMemcpyHostToDevice, st));
+      narrow_offsets_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint64_t*>(pipe.d[s]), cnt, num_edge,
+                                                 ctx->xadj + 1 + i, (uint32_t)i, ctx->d_err);
+      SKW_LAUNCHED(ctx);
+      if ((rc = pipe.submitted(s)) != SKW_OK) return rc;
+      i += cnt;
+    }
+    // numEdge x u32 destinations -> adjncy, in place
+    for (uint64_t i = 0; i < num_edge;) {
+      const size_t cnt = (size_t)std::min<uint64_t>(num_edge - i, GrPipe::kPiece / 4);
+      int s;
+      if ((rc = pipe.next(&s)) != SKW_OK) return rc;
+      if (fread(pipe.h[s], 4, cnt, f) != cnt) return fail(ctx, SKW_ERR_IO, "%s: short destination array", path);
+      SKW_CUDA(ctx, cudaMemcpyAsync(ctx->adjncy + i, pipe.h[s], cnt * 4, cudaMemcpyHostToDevice, st));
+      if ((rc = pipe.submitted(s)) != SKW_OK) return rc;
+      i += cnt;
+    }
+    if (weight_mode == 0) {
+      if (num_edge & 1) {
+        uint32_t pad;
+        if (fread(&pad, 4, 1, f) != 1) return fail(ctx, SKW_ERR_IO, "%s: short padding", path);
+      }
+      // numEdge x u32 edge data -> float weights
+      for (uint64_t i = 0; i < num_edge;) {
+        const size_t cnt = (size_t)std::min<uint64_t>(num_edge - i, GrPipe::kPiece / 4);
+        int s;
+        if ((rc = pipe.next(&s)) != SKW_OK) return rc;
+        if (fread(pipe.h[s], 4, cnt, f) != cnt) return fail(ctx, SKW_ERR_IO, "%s: short edge-data array", path);
+        SKW_CUDA(ctx, cudaMemcpyAsync(pipe.d[s], pipe.h[s], cnt * 4, cudaMemcpyHostToDevice, st));
+        edge_data_to_float_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint32_t*>(pipe.d[s]), cnt,
+                                                       ctx->adjwgt + i);
+        SKW_LAUNCHED(ctx);
+        if ((rc = pipe.submitted(s)) != SKW_OK) return rc;
+        i += cnt;
+      }
+    } else if (weight_mode == 2 && num_edge) {
+      // filled after the structure has been checked (the kernel walks the offsets)
+    } else if (weight_mode == 3 && num_edge) {
+      fill_random_weights_kernel<<<grid, 256, 0, st>>>(ctx->adjwgt, num_edge, weight_seed, (float)weightrange);
+      SKW_LAUNCHED(ctx);
+    } else if (num_edge) {
+      fill_ones_kernel<<<grid, 256, 0, st>>>(ctx->adjwgt, num_edge);
+      SKW_LAUNCHED(ctx);
+    }
+    rc = err_check(ctx, "skw_graph_load_gr");  // an end offset beyond numEdge
+    if (rc == SKW_ERR_DEVICE) {
+      const std::string why = ctx->err;
+      return fail(ctx, SKW_ERR_IO, "%s: an end offset exceeds numEdge -- %s", path, why.c_str());
+    }
+    if (rc != SKW_OK) return rc;
+    return SKW_OK;
+  };
+  int rc = body();
+  if (rc != SKW_OK) {
+    const std::string why = ctx->err;
+    cudaStreamSynchronize(ctx->stream);
+    free_graph(ctx);
+    ctx->err = why;
+    return rc;
+  }
+  // offsets non-decreasing and ending at numEdge, destinations below numNode: the device pass every
+  // upload goes through (it releases the graph when it refuses it)
+  rc = validate_graph(ctx, "skw_graph_load_gr");
+  if (rc != SKW_OK) return rc == SKW_ERR_ARG ? fail(ctx, SKW_ERR_IO, "%s", std::string(ctx->err).c_str()) : rc;
   if (weight_mode == 2 && num_edge) {
-    fill_degree_weights_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(ctx->xadj, ctx->V,
-                                                                            ctx->adjwgt);
-    SKW_LAUNCHED(ctx);
-  } else if (weight_mode == 3 && num_edge) {
-    fill_random_weights_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(
-        ctx->adjwgt, num_edge, weight_seed, (float)weightrange);
+    fill_degree_weights_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(ctx->xadj, ctx->V, ctx->adjwgt);
     SKW_LAUNCHED(ctx);
   }
+  if ((rc = finish_graph(ctx)) != SKW_OK) return rc;
   SKW_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return SKW_OK;
 }

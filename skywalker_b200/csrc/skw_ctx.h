@@ -28,7 +28,7 @@ struct skw_ctx {
   cudaStream_t side_stream = nullptr;  // result copies that overlap kernels of `stream`
   cudaStream_t copy_stream = nullptr;  // skw_walk_packed: the packed rows of each slice
   // skw_walk_packed, per slice: rows packed; cell count on the host; start and end of the walk
-  static constexpr int kPackSlices = 4;
+  static constexpr int kPackSlices = 8;
   cudaEvent_t pk_ready[kPackSlices] = {}, pk_tot[kPackSlices] = {}, pk_t0[kPackSlices] = {}, pk_t1[kPackSlices] = {};
   uint64_t* d_tot = nullptr;  // cells each slice's packed result needs
   uint64_t* h_tot = nullptr;  // pinned mirror
@@ -84,9 +84,12 @@ struct skw_ctx {
   uint32_t* frontier_cls = nullptr;  // same layout as cls_counts
   uint32_t* stamp = nullptr;         // V entries, last round that claimed the vertex
   uint32_t stamp_round = 0;
+  // online direct walks: per-vertex memo of {call stamp, largest weight, total quantised weight}
+  void* prep_memo = nullptr;
+  uint32_t prep_stamp = 0;
 
   // staging buffers of the host-pointer entry points, grown on demand
-  static constexpr int kStages = 8;
+  static constexpr int kStages = 12;
   void* stage[kStages] = {};
   size_t stage_bytes[kStages] = {};
 };

@@ -911,13 +911,14 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
   if (!n) return SKW_OK;
   DeviceGuard g(ctx->device);
   cudaStream_t st = ctx->stream, side = ctx->side_stream;
-  // Large batches run as up to four slices.  Everything a slice needs on the device (walk, prefix sum
+  // Large batches run as up to eight slices.  Everything a slice needs on the device (walk, prefix sum
   // of its row sizes, packing) is queued for ALL slices before the host waits for anything; the side
   // stream brings each slice's cell count, lengths and packed rows home as soon as they exist, while
   // the context's stream is already walking the next slice (the bus carries both directions at once).
   // Walker ids, hence walks, do not depend on the slicing.
   const uint64_t kSliceMin = 1u << 19;
-  const uint32_t slices = n >= 4 * kSliceMin ? 4 : (n >= 2 * kSliceMin ? 2 : 1);
+  const uint32_t slices = n >= 8 * kSliceMin ? 8 : (n >= 4 * kSliceMin ? 4 : (n >= 2 * kSliceMin ? 2 : 1));
+  static_assert(skw_ctx::kPackSlices >= 8 && skw_ctx::kStages >= 4 + 8, "one event set and one packing buffer per slice");
   const uint64_t per = (n + slices - 1) / slices;
   const uint64_t stride = prm->walker_stride ? prm->walker_stride : 1;
   const size_t offs_bytes = (sizeof(u64) * (size_t)per + 255) & ~(size_t)255;
@@ -939,7 +940,7 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
   // other lengths), so a buffer that exists is kept as it is and only a result that outgrows it makes
   // it grow (by an eighth more than needed): steady-state calls do not allocate.  First guess: every
   // walk at full length, or the expected PPR length with room to spare.
-  uint64_t cap[4] = {0, 0, 0, 0}, nc_of[4] = {0, 0, 0, 0};
+  uint64_t cap[skw_ctx::kPackSlices] = {}, nc_of[skw_ctx::kPackSlices] = {};
   for (uint32_t c = 0; c < slices; ++c) {
     const uint64_t base = (uint64_t)c * per;
     if (base >= n) break;

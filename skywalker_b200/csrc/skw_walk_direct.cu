@@ -65,6 +65,69 @@ __device__ __forceinline__ bool list_prepare(const float* __restrict__ w, u32 n,
   return true;
 }
 
+// The largest weight and the total quantised weight of a list depend on the weights only, which do
+// not change while a call runs.  For lists of kMemoMinDegree weights and more the first walker that
+// stands on a vertex during a call leaves the two numbers in a per-vertex memo (16 bytes, tagged with
+// the call's stamp) and later visitors -- the same walker coming back, or others -- read them instead
+// of making the two passes over the list again.  Nothing of the table itself is kept: the drawn slot
+// is still computed from the weights at every step.  Publication order: values, fence, stamp; a
+// reader that sees the stamp fences and then reads the values.
+struct PrepMemo {
+  u32 stamp;
+  float wmax;
+  u64 W;
+};
+constexpr u32 kMemoMinDegree = 512;
+
+__device__ __forceinline__ bool list_prepare_memo(const float* __restrict__ w, u32 n, u32 lane, ListPrep& L,
+                                                  PrepMemo* __restrict__ memo, u32 stamp) {
+  if (memo == nullptr || n < kMemoMinDegree) return list_prepare(w, n, lane, L);
+  u32 seen = 0;
+  if (lane == 0) seen = *reinterpret_cast<volatile u32*>(&memo->stamp);
+  seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+  if (seen == stamp) {
+    float wmax = 0.0f;
+    u64 W = 0;
+    if (lane == 0) {
+      __threadfence();
+      wmax = *reinterpret_cast<volatile float*>(&memo->wmax);
+      W = *reinterpret_cast<volatile u64*>(&memo->W);
+    }
+    wmax = __shfl_sync(0xFFFFFFFFu, wmax, 0);
+    W = __shfl_sync(0xFFFFFFFFu, W, 0);
+    if (!(wmax > 0.0f)) return false;
+    L.B = bucket_bits(n);
+    L.C = (u64)1 << L.B;
+    L.sh = weight_shift(wmax, L.B);
+    L.W = W;
+    L.nC = (u64)n << L.B;
+    L.K = mass_factor(n, L.B, L.W);
+    return true;
+  }
+  float wmax = 0.0f;
+  for (u32 i = lane; i < n; i += 32) wmax = fmaxf(wmax, sane_weight(__ldg(w + i)));
+#pragma unroll
+  for (int o = 16; o; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xFFFFFFFFu, wmax, o));
+  bool usable = wmax > 0.0f;
+  if (usable) {
+    L.B = bucket_bits(n);
+    L.C = (u64)1 << L.B;
+    L.sh = weight_shift(wmax, L.B);
+    u64 acc = 0;
+    for (u32 i = lane; i < n; i += 32) acc += quantise_bits(sane_weight(__ldg(w + i)), L.sh);
+    L.W = warp_sum_u64(acc);
+    L.nC = (u64)n << L.B;
+    L.K = mass_factor(n, L.B, L.W);
+  }
+  if (lane == 0) {  // several warps may publish the same values at once: harmless
+    *reinterpret_cast<volatile float*>(&memo->wmax) = usable ? wmax : 0.0f;
+    *reinterpret_cast<volatile u64*>(&memo->W) = usable ? L.W : 0;
+    __threadfence();
+    *reinterpret_cast<volatile u32*>(&memo->stamp) = stamp;
+  }
+  return usable;
+}
+
 constexpr u32 kDirectEpt = 4, kDirectTile = 32 * kDirectEpt;
 // masses of elements base + lane * 4 + k of the list (0 beyond its end); carryQ = quantised weight
 // before `base`, advanced to the end of the tile
@@ -233,7 +296,8 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
 
 // One warp per walker, all steps in one launch.  Same draws and rules as walk_step.
 template <int APP>
-__global__ void __launch_bounds__(256, 4) walk_online_direct_kernel(const WalkArgs a, const float* __restrict__ wgt) {
+__global__ void __launch_bounds__(256, 4) walk_online_direct_kernel(const WalkArgs a, const float* __restrict__ wgt,
+                                                                    PrepMemo* __restrict__ memo, u32 stamp) {
   const u32 lane = threadIdx.x & 31;
   const u64 nwarps = ((u64)gridDim.x * blockDim.x) >> 5;
   u64 edges = 0;
@@ -254,7 +318,7 @@ __global__ void __launch_bounds__(256, 4) walk_online_direct_kernel(const WalkAr
       if (deg == 0) break;
       const float* wl = wgt + off;
       ListPrep L;
-      if (!list_prepare(wl, deg, lane, L)) break;  // vertex without usable weight
+      if (!list_prepare_memo(wl, deg, lane, L, memo ? memo + cur : nullptr, stamp)) break;  // no usable weight
       u32 next;
       if (APP == SKW_APP_NODE2VEC && prev != kNoVertex) {
         for (u32 trial = 0;;) {
@@ -289,10 +353,26 @@ int launch_walk_online_direct(skw_ctx* ctx, const WalkArgs& a, uint32_t app) {
   const u64 want = (a.n + 7) / 8;  // one warp per walker
   const int grid = (int)std::min<u64>(std::max<u64>(want, 1), (u64)ctx->sm_count * 32);
   cudaStream_t st = ctx->stream;
+  // the per-vertex memo of (largest weight, total): allocated on first use when the graph has lists long
+  // enough to use it, valid for one call (a new stamp per call; zero never names a call)
+  PrepMemo* memo = nullptr;
+  if (ctx->max_degree >= kMemoMinDegree) {
+    if (!ctx->prep_memo) {
+      SKW_CUDA(ctx, cudaMalloc(&ctx->prep_memo, sizeof(PrepMemo) * ((size_t)ctx->V + 1)));
+      SKW_CUDA(ctx, cudaMemsetAsync(ctx->prep_memo, 0, sizeof(PrepMemo) * ((size_t)ctx->V + 1), st));
+      ctx->prep_stamp = 0;
+    }
+    if (++ctx->prep_stamp == 0) {  // wrapped: forget every old entry
+      SKW_CUDA(ctx, cudaMemsetAsync(ctx->prep_memo, 0, sizeof(PrepMemo) * ((size_t)ctx->V + 1), st));
+      ctx->prep_stamp = 1;
+    }
+    memo = static_cast<PrepMemo*>(ctx->prep_memo);
+  }
+  const u32 stamp = ctx->prep_stamp;
   switch (app) {
-    case SKW_APP_DEEPWALK: walk_online_direct_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, ctx->adjwgt); break;
-    case SKW_APP_PPR: walk_online_direct_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, ctx->adjwgt); break;
-    default: walk_online_direct_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a, ctx->adjwgt); break;
+    case SKW_APP_DEEPWALK: walk_online_direct_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp); break;
+    case SKW_APP_PPR: walk_online_direct_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp); break;
+    default: walk_online_direct_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp); break;
   }
   SKW_LAUNCHED(ctx);
   return SKW_OK;

@@ -844,3 +844,23 @@ def test_khop_distinct_runs_out_of_trials(ctx, oracle):
     assert (sl[:, 0] >= 1).all() and (sl[:, 0] < 20).any()
     with pytest.raises(Exception):                          # fan-outs above 256 are refused with the flag
         ctx.sample_khop(seeds, [300], flags=KHOP_DISTINCT, seed=4)
+
+
+@pytest.mark.parametrize("mode", [MODE_OFFLINE, MODE_ONLINE])
+def test_khop_host_entry_sliced_pipeline(ctx, oracle, rmat16, mode):
+    """Batches of 2^18 seeds and more run as slices whose result copies overlap the next slice's
+    kernels: the host entry point returns what the oracle computes, slice boundaries included."""
+    g = rmat16
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    n = (1 << 18) + 1234
+    seeds = oracle.gen_starts(n, g.V, 21)
+    data, sl, _, edges = ctx.sample_khop(seeds, [3, 2], mode=mode, seed=13, instance_base=5)
+    assert edges == int(sl.sum())
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    pick = np.concatenate([np.arange(0, 2000), np.arange(n // 2 - 1000, n // 2 + 1000), np.arange(n - 2000, n)])
+    for lo in (0, n // 2 - 1000, n - 2000):
+        sel = np.arange(lo, lo + 2000)
+        odata, osl = oracle.khop(g.xadj, g.adjncy, g.adjwgt, table, seeds[sel], [3, 2], online=(mode == MODE_ONLINE),
+                                 seed=13, instance_base=5 + lo)
+        assert np.array_equal(data[sel], odata) and np.array_equal(sl[sel], osl)

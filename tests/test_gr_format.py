@@ -60,3 +60,23 @@ def test_gr_malformed_files(ctx, tmp_path):
     with pytest.raises(SkwError):
         ctx.load_gr(str(tmp_path / "missing.gr"))
     ctx.load_gr(str(good))      # context still usable
+
+
+@pytest.mark.gpu
+def test_gr_library_reader_many_pieces(ctx, tmp_path):
+    """A file larger than the reader's 64 MB pieces (offsets, destinations and edge data each span
+    several of them, the last piece is ragged): what comes out of the pipelined device ingest equals
+    what went into the file."""
+    from skywalker_b200.gr import write_gr
+    ctx.generate_rmat(21, 18 << 21, graph_seed=5, weight_seed=6)
+    x, a, w = ctx.download()
+    assert len(a) * 4 > 2 * (64 << 20)
+    data = np.floor(w * 100).astype(np.uint32)
+    p = str(tmp_path / "big.gr")
+    write_gr(p, x, a, data)
+    ctx.load_gr(p, weight_mode=0)
+    x2, a2, w2 = ctx.download()
+    assert np.array_equal(x2, x) and np.array_equal(a2, a)
+    assert np.array_equal(w2, data.astype(np.float32))
+    V, E, md = ctx.graph_info()
+    assert (V, E, md) == (len(x) - 1, len(a), int(np.diff(x.astype(np.int64)).max()))
