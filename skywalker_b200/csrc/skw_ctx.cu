@@ -350,8 +350,6 @@ int skw_ctx_create(int device, skw_ctx** out) {
   CK(cudaMalloc(&ctx->d_sum, 4 * sizeof(uint64_t)));
   CK(cudaMemset(ctx->d_sum, 0, 4 * sizeof(uint64_t)));
   CK(cudaMallocHost(&ctx->h_sum, 4 * sizeof(uint64_t)));
-  CK(cudaMalloc(&ctx->d_cursor, 4 * sizeof(uint32_t)));
-  CK(cudaMemset(ctx->d_cursor, 0, 4 * sizeof(uint32_t)));
   CK(cudaMalloc(&ctx->cls_counts, 64 * sizeof(uint32_t)));
   CK(cudaMalloc(&ctx->frontier_cls, 64 * sizeof(uint32_t)));
 #undef CK
@@ -368,7 +366,6 @@ void skw_ctx_destroy(skw_ctx* ctx) {
   cudaFreeHost(ctx->h_err);
   cudaFree(ctx->d_sum);
   cudaFreeHost(ctx->h_sum);
-  cudaFree(ctx->d_cursor);
   cudaFree(ctx->worklist);
   cudaFree(ctx->cls_counts);
   cudaFree(ctx->cta_scratch);

@@ -67,8 +67,6 @@ struct skw_ctx {
   // pinned scalar for 64-bit reductions read back after a launch
   uint64_t* d_sum = nullptr;
   uint64_t* h_sum = nullptr;
-  // work cursor of the persistent walk kernels: {next chunk, finished warps}, zero between launches
-  uint32_t* d_cursor = nullptr;
 
   // builder scratch, grown on demand
   uint32_t* worklist = nullptr;      // V entries, vertices grouped by degree class

@@ -310,7 +310,6 @@ struct RecordWalkArgs {
   u32 V;
   u32 hop_num;
   float tp;
-  u32* cursor;  // chunked PPR kernel: {next chunk, warps that have finished}; both zero between launches
 };
 
 // Same lane-owns-a-stride loop as walk_offline_kernel; a step is one record load.
@@ -388,121 +387,108 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
 // at the end, with default or streaming stores; padding the prefixes to whole 32-byte sectors
 // (so that no partly written sector leaves L2) made the launch 12 % slower.  Chunks of 64 walkers
 // with 8 warps per CTA were the best of {64, 128, 256} x {4, 8, 16}.
-constexpr u32 kChunk = 64, kStage = 8, kStagePitch = kStage + 1;
-// The grid is persistent: warps take chunks from a global cursor until none is left, so the launch has
-// no waves (1 M walkers are 1,954 CTAs' worth of chunks, 1.65 waves of the 1,184 resident CTAs) and
-// every SM runs out of work at about the same time.  A warp asks for its next chunk before it starts
-// on the current one, which hides the atomic's latency.  The last warp to finish puts the cursor back
-// to zero for the next launch (launches of one context are ordered on its stream).
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) walk_records_ppr_kernel(const RecordWalkArgs a) {
-  __shared__ u32 s_buf[WARPS][kChunk * kStagePitch];
-  __shared__ uint16_t s_len[WARPS][kChunk];
+// A batch of 1 M walkers is 1.65 waves of resident CTAs.  Two ways of avoiding the second wave were
+// built and compared with this kernel on one GPU, back to back (1 M walkers on the scale-22 graph /
+// 8 M on scale 26): chunks handed out from a global atomic cursor to a persistent grid, 0.185 / 0.996 ms
+// against 0.174 / 0.973 ms here; chunks of 128 walkers, so that every CTA is resident at once, 0.172 /
+// 1.049 ms against 0.173 / 0.971 ms.  Neither helps: the hardware's CTA backfill already keeps the SMs
+// loaded, and a small batch is bounded by its longest walks -- with tp = 0.15 the longest of a million
+// walks makes 80 to 100 dependent steps, slow ones while the memory system is saturated (300 K lanes in
+// flight at 43 G accesses/s are 7 us per access) and 0.6-0.9 us each once it has drained.
+constexpr u32 kChunk = 64, kStage = 8;
+template <int WARPS, int CHUNK, int STAGE>
+__global__ void __launch_bounds__(WARPS * 32, 2048 / (WARPS * 32)) walk_records_ppr_kernel(const RecordWalkArgs a) {
+  constexpr u32 kPitch = STAGE + 1;
+  __shared__ u32 s_buf[WARPS][CHUNK * kPitch];
+  __shared__ uint16_t s_len[WARPS][CHUNK];
   const u32 lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const u64 nchunks = (a.n + kChunk - 1) / kChunk;
+  const u64 w_begin = ((u64)blockIdx.x * WARPS + wib) * CHUNK;
+  if (w_begin >= a.n) return;  // the whole warp leaves; nothing below synchronises the CTA
+  const u32 cnt = (u32)min((u64)CHUNK, a.n - w_begin);
   u32* buf = s_buf[wib];
   uint16_t* len = s_len[wib];
+  {
+    u32 st[CHUNK / 32];
+    bool live[CHUNK / 32];
+#pragma unroll
+    for (int k = 0; k < (int)(CHUNK / 32); ++k) {
+      const u32 i = k * 32 + lane;
+      st[k] = i < cnt ? __ldg(a.starts + w_begin + i) : 0u;
+    }
+#pragma unroll
+    for (int k = 0; k < (int)(CHUNK / 32); ++k) {
+      const u32 i = k * 32 + lane;
+      live[k] = false;
+      if (i < cnt) {
+        if (st[k] >= a.V) dev_fail(a.err, DEV_ERR_INDEX, st[k], 0, (u32)(w_begin + i));
+        else live[k] = (__ldg(a.vbits + (st[k] >> 5)) >> (st[k] & 31)) & 1u;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < (int)(CHUNK / 32); ++k) {
+      const u32 i = k * 32 + lane;
+      uint2 vi = make_uint2(0u, 0u);
+      if (live[k]) vi = ldg_once(a.vinfo + st[k]);
+      if (i < cnt) {
+        buf[i * kPitch] = st[k];
+        buf[i * kPitch + 1] = vi.x;
+        buf[i * kPitch + 2] = vi.y;
+      }
+    }
+  }
+  __syncwarp();
   const u32 lt = (1u << lane) - 1u;
+  u32 next = 0;  // walkers of the chunk handed out so far (the same in every lane)
+  bool active = false;
+  u32 local = 0, off = 0, deg = 0, step = 0;
   u64 edges = 0;
-  u32 chunk = 0;
-  if (lane == 0) chunk = atomicAdd(a.cursor, 1u);
-  chunk = __shfl_sync(0xFFFFFFFFu, chunk, 0);
-  while (chunk < nchunks) {
-    u32 chunk_next = 0;
-    if (lane == 0) chunk_next = atomicAdd(a.cursor, 1u);  // used only after this chunk is done
-    const u64 w_begin = (u64)chunk * kChunk;
-    const u32 cnt = (u32)min((u64)kChunk, a.n - w_begin);
-    {
-      u32 st[kChunk / 32];
-      bool live[kChunk / 32];
-#pragma unroll
-      for (int k = 0; k < (int)(kChunk / 32); ++k) {
-        const u32 i = k * 32 + lane;
-        st[k] = i < cnt ? __ldg(a.starts + w_begin + i) : 0u;
+  for (;;) {
+    const u32 need = __ballot_sync(0xFFFFFFFFu, !active);
+    if (need && next < cnt) {
+      const u32 mine = next + __popc(need & lt);
+      if (!active && mine < cnt) {
+        local = mine;
+        off = buf[local * kPitch + 1];
+        deg = buf[local * kPitch + 2];
+        step = 0;
+        active = true;
       }
-#pragma unroll
-      for (int k = 0; k < (int)(kChunk / 32); ++k) {
-        const u32 i = k * 32 + lane;
-        live[k] = false;
-        if (i < cnt) {
-          if (st[k] >= a.V) dev_fail(a.err, DEV_ERR_INDEX, st[k], 0, (u32)(w_begin + i));
-          else live[k] = (__ldg(a.vbits + (st[k] >> 5)) >> (st[k] & 31)) & 1u;
-        }
+      next = min(cnt, next + (u32)__popc(need));
+    }
+    if (!__any_sync(0xFFFFFFFFu, active)) break;
+    if (active) {
+      bool go = step + 1 < a.hop_num && deg != 0;
+      Rand4 r{0, 0, 0, 0};
+      if (go) {
+        r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, step, 0);
+        if (u01(r.z) < a.tp) go = false;
       }
-#pragma unroll
-      for (int k = 0; k < (int)(kChunk / 32); ++k) {
-        const u32 i = k * 32 + lane;
-        uint2 vi = make_uint2(0u, 0u);
-        if (live[k]) vi = ldg_once(a.vinfo + st[k]);
-        if (i < cnt) {
-          buf[i * kStagePitch] = st[k];
-          buf[i * kStagePitch + 1] = vi.x;
-          buf[i * kStagePitch + 2] = vi.y;
-        }
+      if (go) {
+        u32 rw[8];
+        load_record(a.rec + (u64)off + __umulhi(r.x, deg), rw);
+        const bool keep = u01(r.y) < __uint_as_float(rw[0]);
+        ++step;
+        const u32 nv = keep ? rw[1] : rw[4];
+        if (step < (u32)STAGE) buf[local * kPitch + step] = nv;
+        else a.paths[(w_begin + local) * a.hop_num + step] = nv;
+        off = keep ? rw[2] : rw[5];
+        deg = keep ? rw[3] : rw[6];
+      } else {
+        len[local] = (uint16_t)step;
+        edges += step;
+        active = false;
       }
     }
-    __syncwarp();
-    u32 next = 0;  // walkers of the chunk handed out so far (the same in every lane)
-    bool active = false;
-    u32 local = 0, off = 0, deg = 0, step = 0;
-    for (;;) {
-      const u32 need = __ballot_sync(0xFFFFFFFFu, !active);
-      if (need && next < cnt) {
-        const u32 mine = next + __popc(need & lt);
-        if (!active && mine < cnt) {
-          local = mine;
-          off = buf[local * kStagePitch + 1];
-          deg = buf[local * kStagePitch + 2];
-          step = 0;
-          active = true;
-        }
-        next = min(cnt, next + (u32)__popc(need));
-      }
-      if (!__any_sync(0xFFFFFFFFu, active)) break;
-      if (active) {
-        bool go = step + 1 < a.hop_num && deg != 0;
-        Rand4 r{0, 0, 0, 0};
-        if (go) {
-          r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, step, 0);
-          if (u01(r.z) < a.tp) go = false;
-        }
-        if (go) {
-          u32 rw[8];
-          load_record(a.rec + (u64)off + __umulhi(r.x, deg), rw);
-          const bool keep = u01(r.y) < __uint_as_float(rw[0]);
-          ++step;
-          const u32 nv = keep ? rw[1] : rw[4];
-          if (step < kStage) buf[local * kStagePitch + step] = nv;
-          else a.paths[(w_begin + local) * a.hop_num + step] = nv;
-          off = keep ? rw[2] : rw[5];
-          deg = keep ? rw[3] : rw[6];
-        } else {
-          len[local] = (uint16_t)step;
-          edges += step;
-          active = false;
-        }
-      }
-    }
-    __syncwarp();
-    // write-out: 8 lanes per row, four neighbouring rows per pass; then the lengths, coalesced
-    for (u32 r = lane >> 3; r < cnt; r += 4) {
-      const u32 c = lane & 7;
-      const u32 cells = min((u32)len[r] + 1u, kStage);
-      if (c < cells) a.paths[(w_begin + r) * a.hop_num + c] = buf[r * kStagePitch + c];
-    }
-    for (u32 i = lane; i < cnt; i += 32) a.lengths[w_begin + i] = len[i];
-    __syncwarp();  // the staging rows are reused by the next chunk
-    chunk = __shfl_sync(0xFFFFFFFFu, chunk_next, 0);
   }
+  __syncwarp();
+  // write-out: 8 lanes per row, four neighbouring rows per pass; then the lengths, coalesced
+  for (u32 r = lane >> 3; r < cnt; r += 4) {
+    const u32 c = lane & 7;
+    const u32 cells = min((u32)len[r] + 1u, (u32)STAGE);
+    if (c < cells) a.paths[(w_begin + r) * a.hop_num + c] = buf[r * kPitch + c];
+  }
+  for (u32 i = lane; i < cnt; i += 32) a.lengths[w_begin + i] = len[i];
   add_edges(a.sum, edges);
-  if (lane == 0) {
-    const u32 total = gridDim.x * WARPS;
-    if (atomicAdd(a.cursor + 1, 1u) + 1u == total) {  // every warp has stopped asking: rewind
-      a.cursor[0] = 0;
-      a.cursor[1] = 0;
-      __threadfence();
-    }
-  }
 }
 
 // Copy the written part of every path row (cells 0..length) from the device matrix into a host
@@ -792,13 +778,11 @@ static int walk_launch(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t*
     ra.V = a.V;
     ra.hop_num = a.hop_num;
     ra.tp = a.tp;
-    ra.cursor = ctx->d_cursor;
     const int grid = walk_grid(prm->app, n);
+    // (the chunked kernel stages lengths as 16-bit values and has no grid-stride loop)
     const u64 ctas = (n + 8 * kChunk - 1) / (8 * kChunk);
-    const u64 resident = (u64)ctx->sm_count * 8;
-    // (the chunked kernel stages lengths as 16-bit values and counts chunks in 32 bits)
-    if (prm->app == SKW_APP_PPR && prm->hop_num <= 65535 && (n + kChunk - 1) / kChunk < 0x7FFFFFFFull - 8 * resident) {
-      walk_records_ppr_kernel<8><<<(unsigned)(ctas < resident ? ctas : resident), 256, 0, st>>>(ra);
+    if (prm->app == SKW_APP_PPR && prm->hop_num <= 65535 && ctas <= 0x7FFFFFFFull) {
+      walk_records_ppr_kernel<8, kChunk, kStage><<<(unsigned)ctas, 256, 0, st>>>(ra);
     } else if (prm->app == SKW_APP_PPR) walk_records_walk_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(ra);
     else walk_records_walk_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(ra);
     SKW_LAUNCHED(ctx);
