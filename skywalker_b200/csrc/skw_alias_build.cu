@@ -430,12 +430,15 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
   u64 cQ = 0, cD = 0;  // carries between tiles (the same value in every thread)
   u32 cL = 0;
   for (u32 base = 0; base < n; base += NT * EPT) {
-    const u32 p0 = base + t * EPT;
+    // a ragged last tile spreads its elements over all threads (ept each) instead of filling the first ones
+    const u32 ept = min((u32)EPT, (n - base + NT - 1) / NT);
+    const u32 p0 = base + t * ept;
     u64 m[EPT];
     u64 Qex = 0;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
-      m[k] = p0 + k < n ? quantise_bits(weight(p0 + k), sh) : 0;
+      m[k] = 0;
+      if ((u32)k < ept && p0 + k < n) m[k] = quantise_bits(weight(p0 + k), sh);
       Qex += m[k];
     }
     u64 tq;
@@ -448,7 +451,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
     u32 sl = 0;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
-      if (p0 + k < n) {
+      if ((u32)k < ept && p0 + k < n) {
         Q += m[k];
         const u64 g = cum_mass(Q, W, nC, K);
         m[k] = g - g_prev;
@@ -467,7 +470,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
       const u32 p = p0 + k;
-      if (p < n) {
+      if ((u32)k < ept && p < n) {
         gc += m[k];
         if (m[k] < C) {
           Dr += C - m[k];
@@ -728,12 +731,17 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
   const double K = mass_factor(n, B, W);
   u64 cQ = 0, cPK = 0;  // carries between tiles (the same value in every thread)
   for (u32 base = 0; base < (SINGLE ? 1u : n); base += NT * EPT) {
-    const u32 p0 = base + t * EPT;
+    // A ragged last tile spreads its elements over all threads (ept of them each, the same in every
+    // thread) instead of filling the first threads with EPT each: a list of 278 weights then costs a
+    // warp one tile of 8 elements per lane plus one of 1, not two of 8.
+    const u32 ept = SINGLE ? (u32)EPT : min((u32)EPT, (n - base + NT - 1) / NT);
+    const u32 p0 = base + t * ept;
     if constexpr (!SINGLE) {
       Qex = 0;
 #pragma unroll
       for (int k = 0; k < EPT; ++k) {
-        m[k] = p0 + k < n ? quantise_bits(weight(p0 + k), sh) : 0;
+        m[k] = 0;
+        if ((u32)k < ept && p0 + k < n) m[k] = quantise_bits(weight(p0 + k), sh);
         Qex += m[k];
       }
       u64 tq;
@@ -745,7 +753,7 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
     u64 g_prev = gex, Q = Qex, pk = 0;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
-      if (p0 + k < n) {
+      if ((u32)k < ept && p0 + k < n) {
         Q += m[k];
         const u64 g = cum_mass(Q, W, nC, K);
         m[k] = g - g_prev;
@@ -762,7 +770,7 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
       const u32 p = p0 + k;
-      if (p < n) {
+      if ((u32)k < ept && p < n) {
         gc += m[k];
         if (m[k] < C) {
           Dr += C - m[k];
