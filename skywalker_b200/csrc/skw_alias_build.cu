@@ -43,11 +43,12 @@ namespace skw {
 // degree classes: groups of 4/8/16/32 lanes; one warp per vertex (two capacities); one CTA of
 // 256 threads with its lists in shared memory; one CTA of 1024 threads with its lists in a
 // global scratch slab, merged through shared-memory windows
-enum { K_G1 = 0, K_G2, K_G4, K_G8, K_G16, K_G32, K_W1K, K_C, K_C2, K_H, K_CLASSES };
+enum { K_G1 = 0, K_G2, K_G4, K_G8, K_G16, K_G32, K_W1K, K_C, K_C2A, K_C2, K_H, K_CLASSES };
 constexpr u32 kGroupEpt = 8;          // list elements a lane of a sub-warp group keeps in registers
 constexpr u32 kWarpSmallMax = 32 * kGroupEpt;  // 256: the largest list a whole warp holds in registers
 constexpr u32 kWarpMax = 1024;
 constexpr u32 kLargeMax = kCtaSmemMaxDegree;  // 4096: 12 bytes of list state per edge, 4 CTAs per SM
+constexpr u32 kMidSmemMax = 8192;             // two 512-thread CTAs per SM with 96 KB of lists each
 constexpr u32 kHugeSmemMax = 16384;           // one 1024-thread CTA per SM with 192 KB of lists
 
 __device__ __forceinline__ int degree_class(u32 deg) {
@@ -57,6 +58,7 @@ __device__ __forceinline__ int degree_class(u32 deg) {
   }
   if (deg <= kWarpMax) return K_W1K;
   if (deg <= kLargeMax) return K_C;
+  if (deg <= kMidSmemMax) return K_C2A;
   if (deg <= kHugeSmemMax) return K_C2;
   return K_H;
 }
@@ -1179,24 +1181,27 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   static_assert(kLargeMax <= kPackedMax, "the 1025+ CTA class uses packed list entries");
   constexpr int kCtaSmem = kLargeMax * 8;
   constexpr int kCta2Smem = kHugeSmemMax * 12;
+  constexpr int kCta2aSmem = kMidSmemMax * 12;
   constexpr int kCtaStagedSmem = kLargeMax * 8 + (kLargeMax + 8) * 4;
   constexpr int kW1KSmem = 8 * kWarpMax * 8;
   constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
-  constexpr int kWinSmem = kWin * 12 + (1024 + 1) * 4;
+  constexpr int kWinSmem = kWin * 12 + (512 + 1) * 4;
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
-    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<512, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCta2Smem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<512, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCta2aSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_staged_kernel<256, kLargeMax>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kCtaStagedSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_warp_packed_kernel<kWarpMax, 8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kW1KSmem));
     attr_set[ctx->device & 63] = true;
   }
-  // one slab per CTA of the scratch class, sized by the largest degree; fewer CTAs when a giant
-  // hub would make the slabs exceed 4 GB in total
+  // one slab per CTA of the scratch class (two CTAs of 512 threads per SM: two vertices in flight hide
+  // each other's barriers and global-memory latency), sized by the largest degree; fewer CTAs when a
+  // giant hub would make the slabs exceed 4 GB in total
   const uint64_t slab_elems = ctx->max_degree > kHugeSmemMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
-  int gmem_ctas = ctx->sm_count;
+  int gmem_ctas = ctx->sm_count * 2;
   if (slab_elems) {
     const uint64_t fit = (4ull << 30) / (slab_elems * 12ull);
     if (fit < (uint64_t)gmem_ctas) gmem_ctas = (int)(fit < 8 ? 8 : fit);
@@ -1210,7 +1215,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   // otherwise leave most SMs idle) start first on streams of their own, the small classes fill in
   // on the caller's stream.
   const bool fork = ctx->max_degree > kWarpSmallMax;
-  cudaStream_t s_w1k = st, s_c = st, s_c2 = st, s_h = st;
+  cudaStream_t s_w1k = st, s_c = st, s_c2 = st, s_c2a = st, s_h = st;
   if (fork) {
     SKW_CUDA(ctx, cudaEventRecord(ctx->bfork, st));
     for (int i = 0; i < skw_ctx::kBuilderStreams; ++i) SKW_CUDA(ctx, cudaStreamWaitEvent(ctx->bstream[i], ctx->bfork, 0));
@@ -1218,14 +1223,15 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
     s_c2 = ctx->bstream[1];
     s_c = ctx->bstream[2];
     s_w1k = ctx->bstream[3];
+    s_c2a = ctx->bstream[3];  // behind the 257-1024 class on its stream
   }
   if (slab_elems) {
-    build_cta_merge_kernel<1024, kWin><<<gmem_ctas, 1024, kWinSmem, s_h>>>(
+    build_cta_merge_kernel<512, kWin><<<gmem_ctas, 512, kWinSmem, s_h>>>(
         worklist, cls, K_H, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid,
         static_cast<unsigned char*>(ctx->cta_scratch), slab_elems, ctx->d_err);
     SKW_LAUNCHED(ctx);
   }
-  if (ctx->max_degree > kLargeMax) {
+  if (ctx->max_degree > kMidSmemMax) {
     build_cta_merge_kernel<1024, 0><<<ctx->sm_count, 1024, kCta2Smem, s_c2>>>(
         worklist, cls, K_C2, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kHugeSmemMax, ctx->d_err);
     SKW_LAUNCHED(ctx);
@@ -1243,6 +1249,11 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   if (ctx->max_degree > kWarpSmallMax) {
     build_warp_packed_kernel<kWarpMax, 8><<<ctx->sm_count * 3, 256, kW1KSmem, s_w1k>>>(
         worklist, cls, K_W1K, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, ctx->d_err);
+    SKW_LAUNCHED(ctx);
+  }
+  if (ctx->max_degree > kLargeMax) {
+    build_cta_merge_kernel<512, 0><<<ctx->sm_count * 2, 512, kCta2aSmem, s_c2a>>>(
+        worklist, cls, K_C2A, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid, nullptr, kMidSmemMax, ctx->d_err);
     SKW_LAUNCHED(ctx);
   }
   const int ggrid = ctx->sm_count * 8;
