@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "skw_ctx.h"
+#include "skw_hostpool.h"
 
 namespace skw {
 
@@ -372,6 +373,8 @@ void skw_ctx_destroy(skw_ctx* ctx) {
   cudaFree(ctx->frontier_lists);
   cudaFree(ctx->frontier_cls);
   for (int i = 0; i < skw_ctx::kStages; ++i) cudaFree(ctx->stage[i]);
+  if (ctx->h_pack) cudaFreeHost(ctx->h_pack);
+  delete static_cast<skw::HostPool*>(ctx->host_pool);
   cudaFree(ctx->d_tot);
   cudaFreeHost(ctx->h_tot);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);

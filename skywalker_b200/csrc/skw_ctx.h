@@ -86,6 +86,12 @@ struct skw_ctx {
   void* prep_memo = nullptr;
   uint32_t prep_stamp = 0;
 
+  // skw_walk with host rows, large batches: pinned staging for the packed result and the host threads
+  // that scatter it into the caller's matrix
+  uint32_t* h_pack = nullptr;
+  size_t h_pack_cells = 0;
+  void* host_pool = nullptr;  // skw::HostPool
+
   // staging buffers of the host-pointer entry points, grown on demand
   static constexpr int kStages = 12;
   void* stage[kStages] = {};

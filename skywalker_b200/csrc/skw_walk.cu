@@ -14,12 +14,16 @@
 // word x -> column (multiply-high by the degree), y -> acceptance uniform, z -> PPR stop test,
 // w -> node2vec rejection uniform.
 #include <algorithm>
+#include <cstring>
 #include <string>
+#include <thread>
+#include <vector>
 
 #include <cub/device/device_scan.cuh>
 #include <cub/iterator/transform_input_iterator.cuh>
 
 #include "skw_ctx.h"
+#include "skw_hostpool.h"
 #include "skw_walk_common.cuh"
 
 namespace skw {
@@ -843,12 +847,80 @@ int skw_walk_device(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* d_
   return SKW_OK;
 }
 
+// Large batches into the caller's n x hop_num host matrix: the walks come home packed (contiguous
+// copies, only cells that hold a vertex cross the bus) into pinned staging owned by the context, and
+// host threads scatter them into the rows.  A kernel writing row prefixes straight into mapped host
+// memory sends one small bus write per row (8 M PPR rows: 22 ms); a copy of the whole matrix moves
+// every unused cell as well.  Cells past a walk's end keep what the caller had there.
+static int walk_rows_by_scatter(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+                                uint32_t* h_paths, uint32_t* h_lengths, float* ms, uint64_t* sampled_edges) {
+  const uint64_t full = n * prm->hop_num;
+  uint64_t want = full;
+  if (prm->app == SKW_APP_PPR && prm->tp > 0.0f)
+    want = std::min<uint64_t>(full, (uint64_t)((double)n * (1.0 / prm->tp + 2.0)) + 4096);
+  uint64_t cells = 0;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    if (ctx->h_pack_cells < want) {
+      if (ctx->h_pack) cudaFreeHost(ctx->h_pack);
+      ctx->h_pack = nullptr;
+      ctx->h_pack_cells = 0;
+      SKW_CUDA(ctx, cudaMallocHost(&ctx->h_pack, sizeof(uint32_t) * (size_t)want));
+      ctx->h_pack_cells = want;
+    }
+    const int rc = skw_walk_packed(ctx, prm, h_starts, n, ctx->h_pack, ctx->h_pack_cells, h_lengths, &cells, ms,
+                                   sampled_edges);
+    if (rc == SKW_OK) break;
+    if (rc != SKW_ERR_ARG || cells <= ctx->h_pack_cells || attempt == 1) return rc;
+    want = std::min<uint64_t>(full, cells + (cells >> 3) + 4096);  // the staging was too small: once more
+  }
+  if (!ctx->host_pool) {
+    unsigned hc = std::thread::hardware_concurrency();
+    ctx->host_pool = new HostPool((int)std::min<unsigned>(hc ? hc : 1u, 32u));
+  }
+  HostPool* pool = static_cast<HostPool*>(ctx->host_pool);
+  const int T = pool->size();
+  std::vector<uint64_t> first(T + 1, 0);  // cells before each thread's block of walkers
+  const uint32_t hop = prm->hop_num;
+  pool->run([&](int t, int) {
+    const uint64_t lo = n * t / T, hi = n * (t + 1) / T;
+    uint64_t sum = 0;
+    for (uint64_t w = lo; w < hi; ++w) sum += (uint64_t)std::min<uint32_t>(h_lengths[w] + 1u, hop);
+    first[t + 1] = sum;
+  });
+  for (int t = 0; t < T; ++t) first[t + 1] += first[t];
+  if (first[T] != cells)
+    return fail(ctx, SKW_ERR_DEVICE, "skw_walk: packed result holds %llu cells, the lengths add up to %llu",
+                (unsigned long long)cells, (unsigned long long)first[T]);
+  const uint32_t* packed = ctx->h_pack;
+  pool->run([&](int t, int) {
+    const uint64_t lo = n * t / T, hi = n * (t + 1) / T;
+    uint64_t o = first[t];
+    // every row is a cache miss of its own (rows lie hop_num cells apart): ask for the lines a few rows
+    // ahead, and copy short rows cell by cell (most PPR rows hold a handful of cells)
+    constexpr uint64_t kAhead = 24;
+    for (uint64_t w = lo; w < hi; ++w) {
+      if (w + kAhead < hi) __builtin_prefetch(h_paths + (w + kAhead) * hop, 1, 0);
+      const uint32_t c = std::min<uint32_t>(h_lengths[w] + 1u, hop);
+      uint32_t* row = h_paths + w * hop;
+      const uint32_t* src = packed + o;
+      if (c <= 8) {
+        for (uint32_t k = 0; k < c; ++k) row[k] = src[k];
+      } else {
+        memcpy(row, src, sizeof(uint32_t) * c);
+      }
+      o += c;
+    }
+  });
+  return SKW_OK;
+}
+
 int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
              uint32_t* h_paths, uint32_t* h_lengths, float* ms, uint64_t* sampled_edges) {
   if (!ctx || !prm) return SKW_ERR_ARG;
   if (n && (!h_starts || !h_paths || !h_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_walk: null buffer");
   if (prm->hop_num < 1) return fail(ctx, SKW_ERR_ARG, "skw_walk: hop_num must be >= 1");
   DeviceGuard g(ctx->device);
+  if (n >= (1u << 18)) return walk_rows_by_scatter(ctx, prm, h_starts, n, h_paths, h_lengths, ms, sampled_edges);
   int rc;
   const size_t nb = sizeof(uint32_t) * (size_t)n;
   if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], nb)) != SKW_OK) return rc;

@@ -864,3 +864,23 @@ def test_khop_host_entry_sliced_pipeline(ctx, oracle, rmat16, mode):
         odata, osl = oracle.khop(g.xadj, g.adjncy, g.adjwgt, table, seeds[sel], [3, 2], online=(mode == MODE_ONLINE),
                                  seed=13, instance_base=5 + lo)
         assert np.array_equal(data[sel], odata) and np.array_equal(sl[sel], osl)
+
+
+@pytest.mark.parametrize("app,kw", [(APP_DEEPWALK, {}), (APP_PPR, {"tp": 0.15})])
+def test_walk_host_rows_large_batch_scatter(ctx, oracle, rmat16, app, kw):
+    """Batches of 2^18 walkers and more reach the caller's n x hop_num host matrix as a packed transfer
+    that host threads scatter into the rows: every row equals the oracle's, and cells past a walk's end
+    keep what the caller had there."""
+    g = rmat16
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    n, hop = (1 << 18) + 777, 21
+    starts = oracle.gen_starts(n, g.V, 31)
+    paths = np.full((n, hop), 0xABABABAB, np.uint32)
+    lens = np.zeros(n, np.uint32)
+    _, _, _, edges = ctx.walk(starts, hop, app=app, seed=8, walker_base=11, paths=paths, lengths=lens, **kw)
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    op, ol = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, hop, app=app, seed=8, walker_base=11,
+                         fill=0xABABABAB, **kw)
+    assert np.array_equal(lens, ol) and edges == int(ol.sum())
+    assert np.array_equal(paths, op)
