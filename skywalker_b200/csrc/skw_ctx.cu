@@ -80,6 +80,8 @@ static void free_graph(skw_ctx* ctx) {
   cudaFree(ctx->valid);
   cudaFree(ctx->stamp);
   cudaFree(ctx->prep_memo);
+  cudaFree(ctx->prep_ckpt);
+  ctx->prep_ckpt = nullptr;
   ctx->prep_memo = nullptr;
   ctx->prep_stamp = 0;
   cudaFree(ctx->records);

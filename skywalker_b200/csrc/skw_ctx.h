@@ -85,6 +85,7 @@ struct skw_ctx {
   // online direct walks: per-vertex memo of {call stamp, largest weight, total quantised weight}
   void* prep_memo = nullptr;
   uint32_t prep_stamp = 0;
+  void* prep_ckpt = nullptr;  // prefix-sum checkpoints of long lists, valid together with the memo entry
 
   // skw_walk with host rows, large batches: pinned staging for the packed result and the host threads
   // that scatter it into the caller's matrix

@@ -79,8 +79,27 @@ struct PrepMemo {
 };
 constexpr u32 kMemoMinDegree = 512;
 
+// For lists of kCkMinDegree weights and more the same first visit also leaves CHECKPOINTS of two
+// prefix sums at every kCkChunk-th list position b: the cumulative quantised weight Q_b and the
+// deficit D_b of the smalls before b (the excess of the larges before b follows from them,
+// X_b = D_b + g(Q_b) - b * C).  They are integers and depend on the weights alone, so whoever
+// writes them writes the same values.  A later draw of slot p then sweeps the list from the boundary
+// before p instead of from its start, and finds the chunk that holds the crossing it looks for by
+// bisecting the checkpoints: at most two chunks of weights are visited per step instead of one and a
+// half passes over the list, which is what a walk on a power-law graph spends its time on (a walker
+// stands on a hub most of the time, and the cost of a draw grows with the hub's degree).  Still no
+// slot of a table is kept.  Entry k - 1 of a vertex's checkpoints is boundary k (k >= 1); the vertex
+// with first-edge offset `off` owns entries off / kCkChunk ... of one array of E / kCkChunk + 2
+// entries (consecutive vertices cannot collide: a list of n weights has (n - 1) / kCkChunk entries).
+struct __align__(16) Ckpt {
+  u64 Q, D;
+};
+constexpr u32 kCkChunk = 1024, kCkMinDegree = 2048;
+
+__device__ void record_checkpoints(const float* __restrict__ w, u32 n, u32 lane, const ListPrep& L, Ckpt* ck);
+
 __device__ __forceinline__ bool list_prepare_memo(const float* __restrict__ w, u32 n, u32 lane, ListPrep& L,
-                                                  PrepMemo* __restrict__ memo, u32 stamp) {
+                                                  PrepMemo* __restrict__ memo, u32 stamp, Ckpt* ck) {
   if (memo == nullptr || n < kMemoMinDegree) return list_prepare(w, n, lane, L);
   u32 seen = 0;
   if (lane == 0) seen = *reinterpret_cast<volatile u32*>(&memo->stamp);
@@ -118,6 +137,7 @@ __device__ __forceinline__ bool list_prepare_memo(const float* __restrict__ w, u
     L.W = warp_sum_u64(acc);
     L.nC = (u64)n << L.B;
     L.K = mass_factor(n, L.B, L.W);
+    if (ck != nullptr) record_checkpoints(w, n, lane, L, ck);
   }
   if (lane == 0) {  // several warps may publish the same values at once: harmless
     *reinterpret_cast<volatile float*>(&memo->wmax) = usable ? wmax : 0.0f;
@@ -155,17 +175,54 @@ __device__ __forceinline__ void tile_masses(const float* __restrict__ w, u32 n, 
   }
 }
 
-// (prob, alias) of slot p; every lane returns the same values.  v only labels error records.
-__device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, const ListPrep& L, u32 v,
-                          u32* err) {
+// One full sweep of the list that stores (Q_b, D_b) at every chunk boundary b = k * kCkChunk, k >= 1.
+__device__ void record_checkpoints(const float* __restrict__ w, u32 n, u32 lane, const ListPrep& L, Ckpt* ck) {
+  u64 carryQ = 0, accD = 0;
+  u64 m[kDirectEpt];
+  for (u32 base = 0; base < n; base += kDirectTile) {
+    if (base && base % kCkChunk == 0) {
+      const u64 D = warp_sum_u64(accD);
+      if (lane == 0) {
+        volatile u64* dst = reinterpret_cast<volatile u64*>(ck + (base / kCkChunk - 1));
+        dst[0] = carryQ;
+        dst[1] = D;
+      }
+    }
+    tile_masses(w, n, base, lane, L, carryQ, m);
+#pragma unroll
+    for (u32 k = 0; k < kDirectEpt; ++k)
+      if (base + lane * kDirectEpt + k < n && m[k] < L.C) accD += L.C - m[k];
+  }
+}
+
+// The sums at chunk boundary k (all zero at k = 0): quantised weight, deficit and excess before it.
+__device__ __forceinline__ void ck_load(const Ckpt* ck, u32 k, const ListPrep& L, u64& Q, u64& D, u64& X) {
+  Q = 0;
+  D = 0;
+  X = 0;
+  if (k == 0 || ck == nullptr) return;
+  const ulonglong2 e = __ldcg(reinterpret_cast<const ulonglong2*>(ck + (k - 1)));
+  Q = e.x;
+  D = e.y;
+  X = D + cum_mass(Q, L.W, L.nC, L.K) - (((u64)k * kCkChunk) << L.B);
+}
+
+// (prob, alias) of slot p; every lane returns the same values.  ck: the vertex's checkpoints or
+// nullptr.  v only labels error records.
+__device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, const ListPrep& L,
+                          const Ckpt* __restrict__ ck, u32 v, u32* err) {
   const u64 C = L.C;
+  const u32 nck = ck ? (n - 1) / kCkChunk : 0;  // boundaries 1 .. nck carry checkpoints
   const u32 tp = p / kDirectTile, owner = (p % kDirectTile) / kDirectEpt;
-  // sweep 1: masses up to p; per-lane sums of the deficits before p and of the excesses up to and
-  // including p
-  u64 carryQ = 0, accD = 0, accX = 0, Mp = 0;
+  // sweep 1: masses from the boundary before p up to p; per-lane sums (on top of the boundary's) of
+  // the deficits before p and of the excesses up to and including p
+  const u32 kb = min(p / kCkChunk, nck);
+  u64 baseQ, baseD, baseX;
+  ck_load(ck, kb, L, baseQ, baseD, baseX);
+  u64 carryQ = baseQ, accD = 0, accX = 0, Mp = 0;
   u64 saveQ = 0, saveD = 0, saveX = 0;  // the same sums at the start of p's tile
   u64 m[kDirectEpt];
-  for (u32 t = 0; t <= tp; ++t) {
+  for (u32 t = kb * (kCkChunk / kDirectTile); t <= tp; ++t) {
     const u32 base = t * kDirectTile;
     if (t == tp) {
       saveQ = carryQ;
@@ -187,16 +244,30 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
   Slot out;
   if (Mp < C) {
     // small: its donor is the first large whose running excess reaches the deficit before p
-    const u64 T = warp_sum_u64(accD);
+    const u64 T = baseD + warp_sum_u64(accD);
     out.prob = mass_to_prob_fast(Mp, L.B);
     out.alias = p;
-    // if the larges before p do not reach T the donor lies after p: resume at p's tile
-    u64 cq = 0, carryX = 0;
-    u32 start = 0;
-    if (warp_sum_u64(accX) < T) {
+    // The second sweep starts at the last chunk boundary whose excess is still below T (the donor lies
+    // in that chunk) ...
+    u64 cq, carryX, dummy;
+    u32 start;
+    {
+      u32 lo = 0, hi = nck;
+      while (lo < hi) {
+        const u32 mid = (lo + hi + 1) >> 1;
+        u64 q2, d2, x2;
+        ck_load(ck, mid, L, q2, d2, x2);
+        if (x2 < T) lo = mid;
+        else hi = mid - 1;
+      }
+      ck_load(ck, lo, L, cq, dummy, carryX);
+      start = lo * kCkChunk;
+    }
+    // ... or at p's tile, when the larges up to p do not reach T (the donor lies after p) and that is later
+    if (baseX + warp_sum_u64(accX) < T && tp * kDirectTile > start) {
       start = tp * kDirectTile;
       cq = saveQ;
-      carryX = warp_sum_u64(saveX);
+      carryX = baseX + warp_sum_u64(saveX);
     }
     bool found = false;
     for (u32 base = start; base < n && !found; base += kDirectTile) {
@@ -227,7 +298,7 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
     return out;
   }
   // large: first small whose running deficit exceeds the excess up to and including p
-  const u64 T = warp_sum_u64(accX);
+  const u64 T = baseX + warp_sum_u64(accX);
   // the first large after p, from the tile already in registers and the tiles after it
   u32 next_large = kNoVertex;
   {
@@ -254,13 +325,27 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
   out.prob = 1.0f;
   out.alias = p;
   if (next_large == kNoVertex) return out;  // the last large: no small can be left for it (D_total = X_total)
-  // if the smalls before p do not exceed T the crossing lies after p: resume at p's tile
-  u64 cq = 0, carryD = 0;
-  u32 start = 0;
-  if (warp_sum_u64(accD) <= T) {
+  // The second sweep starts at the last chunk boundary whose deficit does not exceed T (the crossing
+  // lies in that chunk, or nowhere) ...
+  u64 cq, carryD, dummy;
+  u32 start;
+  {
+    u32 lo = 0, hi = nck;
+    while (lo < hi) {
+      const u32 mid = (lo + hi + 1) >> 1;
+      u64 q2, d2, x2;
+      ck_load(ck, mid, L, q2, d2, x2);
+      if (d2 <= T) lo = mid;
+      else hi = mid - 1;
+    }
+    ck_load(ck, lo, L, cq, carryD, dummy);
+    start = lo * kCkChunk;
+  }
+  // ... or at p's tile, when the smalls before p do not exceed T (the crossing lies after p) and that is later
+  if (baseD + warp_sum_u64(accD) <= T && tp * kDirectTile > start) {
     start = tp * kDirectTile;
     cq = saveQ;
-    carryD = warp_sum_u64(saveD);
+    carryD = baseD + warp_sum_u64(saveD);
   }
   for (u32 base = start; base < n; base += kDirectTile) {
     tile_masses(w, n, base, lane, L, cq, m);
@@ -297,7 +382,8 @@ __device__ Slot eval_slot(const float* __restrict__ w, u32 n, u32 p, u32 lane, c
 // One warp per walker, all steps in one launch.  Same draws and rules as walk_step.
 template <int APP>
 __global__ void __launch_bounds__(256, 4) walk_online_direct_kernel(const WalkArgs a, const float* __restrict__ wgt,
-                                                                    PrepMemo* __restrict__ memo, u32 stamp) {
+                                                                    PrepMemo* __restrict__ memo, u32 stamp,
+                                                                    Ckpt* __restrict__ ck_all) {
   const u32 lane = threadIdx.x & 31;
   const u64 nwarps = ((u64)gridDim.x * blockDim.x) >> 5;
   u64 edges = 0;
@@ -318,12 +404,13 @@ __global__ void __launch_bounds__(256, 4) walk_online_direct_kernel(const WalkAr
       if (deg == 0) break;
       const float* wl = wgt + off;
       ListPrep L;
-      if (!list_prepare_memo(wl, deg, lane, L, memo ? memo + cur : nullptr, stamp)) break;  // no usable weight
+      Ckpt* ck = (ck_all != nullptr && memo != nullptr && deg >= kCkMinDegree) ? ck_all + off / kCkChunk : nullptr;
+      if (!list_prepare_memo(wl, deg, lane, L, memo ? memo + cur : nullptr, stamp, ck)) break;  // no usable weight
       u32 next;
       if (APP == SKW_APP_NODE2VEC && prev != kNoVertex) {
         for (u32 trial = 0;;) {
           const u32 col = __umulhi(r.x, deg);
-          const Slot s = eval_slot(wl, deg, col, lane, L, cur, a.err);
+          const Slot s = eval_slot(wl, deg, col, lane, L, ck, cur, a.err);
           const u32 cand = u01(r.y) < s.prob ? col : s.alias;
           next = __ldg(a.adjncy + (u64)off + cand);
           const float f = next == prev ? a.inv_p : (connected(a.xadj, a.adjncy, prev, next) ? 1.0f : a.inv_q);
@@ -333,7 +420,7 @@ __global__ void __launch_bounds__(256, 4) walk_online_direct_kernel(const WalkAr
         }
       } else {
         const u32 col = __umulhi(r.x, deg);
-        const Slot s = eval_slot(wl, deg, col, lane, L, cur, a.err);
+        const Slot s = eval_slot(wl, deg, col, lane, L, ck, cur, a.err);
         const u32 cand = u01(r.y) < s.prob ? col : s.alias;
         next = __ldg(a.adjncy + (u64)off + cand);
       }
@@ -368,11 +455,16 @@ int launch_walk_online_direct(skw_ctx* ctx, const WalkArgs& a, uint32_t app) {
     }
     memo = static_cast<PrepMemo*>(ctx->prep_memo);
   }
+  Ckpt* ck_all = nullptr;
+  if (memo != nullptr && ctx->max_degree >= kCkMinDegree) {
+    if (!ctx->prep_ckpt) SKW_CUDA(ctx, cudaMalloc(&ctx->prep_ckpt, sizeof(Ckpt) * ((size_t)(ctx->E / kCkChunk) + 2)));
+    ck_all = static_cast<Ckpt*>(ctx->prep_ckpt);  // validated by the memo's stamp: no clearing needed
+  }
   const u32 stamp = ctx->prep_stamp;
   switch (app) {
-    case SKW_APP_DEEPWALK: walk_online_direct_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp); break;
-    case SKW_APP_PPR: walk_online_direct_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp); break;
-    default: walk_online_direct_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp); break;
+    case SKW_APP_DEEPWALK: walk_online_direct_kernel<SKW_APP_DEEPWALK><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp, ck_all); break;
+    case SKW_APP_PPR: walk_online_direct_kernel<SKW_APP_PPR><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp, ck_all); break;
+    default: walk_online_direct_kernel<SKW_APP_NODE2VEC><<<grid, 256, 0, st>>>(a, ctx->adjwgt, memo, stamp, ck_all); break;
   }
   SKW_LAUNCHED(ctx);
   return SKW_OK;

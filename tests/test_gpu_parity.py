@@ -650,6 +650,17 @@ def test_online_direct_slots_every_degree_class(ctx, oracle):
     lists.append(np.asarray([1e-40, 2e-40, 3e-41, 0, 1e-45], np.float32))           # denormals only
     lists.append(np.asarray([1e-38, 1e-40, 1.0, 3e-39] * 20, np.float32))           # denormals beside normals
     lists.append(np.asarray([3.0e38, 1.0, 2.9e38, 1e-30] * 10, np.float32))         # near the largest float
+    # long lists whose crossings lie far from the drawn slot (the prefix checkpoints of lists of 2,048
+    # weights and more decide where a sweep starts)
+    lists.append(np.concatenate([np.full(5000, 1e-3), rng.uniform(1, 2, 5000)]).astype(np.float32))   # smalls, then larges
+    lists.append(np.concatenate([rng.uniform(1, 2, 5000), np.full(5000, 1e-3)]).astype(np.float32))   # larges, then smalls
+    lists.append(np.full(5000, 2.5, np.float32))                                                       # no small at all
+    lists.append(np.asarray([1000.0] + [1e-3] * 6000, np.float32))                                     # one donor for 6000 smalls
+    lists.append(np.asarray([1e-3] * 6000 + [1000.0], np.float32))
+    lists.append(np.tile(np.asarray([1.0, 3.0], np.float32), 1500))                                    # ties between the prefixes
+    lists.append(rng.uniform(1, 10, 2048).astype(np.float32))                                          # exactly one checkpoint
+    lists.append(rng.uniform(1, 10, 2049).astype(np.float32))
+    lists.append(rng.uniform(1, 10, 3073).astype(np.float32))
     xadj, adj, w = _star_graph(lists)
     ctx.upload(xadj, adj, w)
     starts = np.concatenate([np.full(min(4 * len(l), 6000), i, np.uint32) for i, l in enumerate(lists)])
