@@ -467,24 +467,65 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
     coop_scan2<NT>(sd, sl, td, tl, s_tmp);
     u64 Dr = sd + cD, gc = gex;
     u32 Lr = sl + cL;
+    const u32 L0 = cL;  // larges before this tile
     cD += td;
     cL += tl;
+    if constexpr (WIN == 0) {
 #pragma unroll
-    for (int k = 0; k < EPT; ++k) {
-      const u32 p = p0 + k;
-      if ((u32)k < ept && p < n) {
-        gc += m[k];
-        if (m[k] < C) {
-          Dr += C - m[k];
-          const u32 i = p - Lr;  // smalls before p
-          A[i] = Dr;
-          P[i] = p;
-        } else {
-          const u32 j = Lr++;    // larges before p
-          A[n - 1 - j] = Dr + gc - ((u64)(p + 1) << B);
-          P[n - 1 - j] = p;
+      for (int k = 0; k < EPT; ++k) {
+        const u32 p = p0 + k;
+        if ((u32)k < ept && p < n) {
+          gc += m[k];
+          if (m[k] < C) {
+            Dr += C - m[k];
+            const u32 i = p - Lr;  // smalls before p
+            A[i] = Dr;
+            P[i] = p;
+          } else {
+            const u32 j = Lr++;    // larges before p
+            A[n - 1 - j] = Dr + gc - ((u64)(p + 1) << B);
+            P[n - 1 - j] = p;
+          }
         }
       }
+    } else {
+      // The lists live in global memory.  A thread's eight entries would go out as eight scattered
+      // 8-byte stores per warp instruction; instead the tile's entries are laid out in shared memory
+      // first (its smalls from the front, its larges from the back, as in the lists themselves) and
+      // copied out with consecutive lanes on consecutive addresses.
+      static_assert(WIN == 0 || WIN >= NT * EPT, "the window buffer doubles as the tile's staging area");
+      u64* tA = reinterpret_cast<u64*>(win_smem);
+      u32* tP = reinterpret_cast<u32*>(tA + WIN);
+      const u32 tile_n = min((u32)(NT * EPT), n - base);
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) {
+        const u32 p = p0 + k;
+        if ((u32)k < ept && p < n) {
+          gc += m[k];
+          if (m[k] < C) {
+            Dr += C - m[k];
+            const u32 i = (p - base) - (Lr - L0);  // smalls of this tile before p
+            tA[i] = Dr;
+            tP[i] = p;
+          } else {
+            const u32 j = Lr++ - L0;               // larges of this tile before p
+            tA[tile_n - 1 - j] = Dr + gc - ((u64)(p + 1) << B);
+            tP[tile_n - 1 - j] = p;
+          }
+        }
+      }
+      coop_sync<NT>();
+      const u32 ts = tile_n - tl;          // smalls in this tile
+      const u32 S0 = base - L0;            // smalls before this tile
+      for (u32 x = t; x < ts; x += NT) {
+        A[S0 + x] = tA[x];
+        P[S0 + x] = tP[x];
+      }
+      for (u32 x = t; x < tl; x += NT) {   // large L0 + x sits at n - 1 - (L0 + x)
+        A[n - 1 - (L0 + x)] = tA[tile_n - 1 - x];
+        P[n - 1 - (L0 + x)] = tP[tile_n - 1 - x];
+      }
+      coop_sync<NT>();
     }
   }
   coop_sync<NT>();
@@ -1185,10 +1226,10 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   constexpr int kCtaStagedSmem = kLargeMax * 8 + (kLargeMax + 8) * 4;
   constexpr int kW1KSmem = 8 * kWarpMax * 8;
   constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
-  constexpr int kWinSmem = kWin * 12 + (512 + 1) * 4;
+  constexpr int kWinSmem = kWin * 12 + (1024 + 1) * 4;
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
-    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<512, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
+    SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCta2Smem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<512, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCta2aSmem));
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_staged_kernel<256, kLargeMax>,
@@ -1197,11 +1238,13 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kW1KSmem));
     attr_set[ctx->device & 63] = true;
   }
-  // one slab per CTA of the scratch class (two CTAs of 512 threads per SM: two vertices in flight hide
-  // each other's barriers and global-memory latency), sized by the largest degree; fewer CTAs when a
-  // giant hub would make the slabs exceed 4 GB in total
+  // one slab per CTA of the scratch class, sized by the largest degree; fewer CTAs when a giant hub
+  // would make the slabs exceed 4 GB in total.  (Two 512-thread CTAs per SM instead of one of 1024 were
+  // measured: 4.61 against 4.70 ms for this class at scale 26, where thousands of such vertices keep
+  // every SM busy either way, but 0.23 ms instead of about 0.15 ms for the largest vertex of an online
+  // frontier, which a hop has to wait for; so one vertex gets the 1024 threads.)
   const uint64_t slab_elems = ctx->max_degree > kHugeSmemMax ? (((uint64_t)ctx->max_degree + 1) & ~1ull) : 0;
-  int gmem_ctas = ctx->sm_count * 2;
+  int gmem_ctas = ctx->sm_count;
   if (slab_elems) {
     const uint64_t fit = (4ull << 30) / (slab_elems * 12ull);
     if (fit < (uint64_t)gmem_ctas) gmem_ctas = (int)(fit < 8 ? 8 : fit);
@@ -1226,7 +1269,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
     s_c2a = ctx->bstream[3];  // behind the 257-1024 class on its stream
   }
   if (slab_elems) {
-    build_cta_merge_kernel<512, kWin><<<gmem_ctas, 512, kWinSmem, s_h>>>(
+    build_cta_merge_kernel<1024, kWin><<<gmem_ctas, 1024, kWinSmem, s_h>>>(
         worklist, cls, K_H, ctx->xadj, ctx->adjwgt, ctx->slots, ctx->valid,
         static_cast<unsigned char*>(ctx->cta_scratch), slab_elems, ctx->d_err);
     SKW_LAUNCHED(ctx);
