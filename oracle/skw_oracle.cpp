@@ -4,16 +4,21 @@
 // by the smoke check and by the benchmark's cpu-baseline / reference legs, as the checker and
 // as the timed CPU implementation.
 //
-// Parity status: PARITY UNPINNED by the reference.  wpybtw/Skywalker is CUDA-only (no CPU code
+// Parity status: PARITY UNPINNED at the bit level.  wpybtw/Skywalker is CUDA-only (no CPU code
 // for this path), ships no golden vectors or runnable tests (test/alias_table.cu and
 // test/tmp.cu target an API that no longer exists), seeds cuRAND XORWOW by thread id and builds
 // its tables with unordered float atomics, so its outputs are not reproducible even against
-// itself.  What is pinned instead:
+// itself and no output of it can be compared with this file bit for bit.  What is pinned instead:
 //   * Philox4x32-10 against the published Random123 known-answer vectors (tests/golden);
 //   * the alias construction against the closed-form properties every alias table must have
 //     (exact mass conservation in integers, reconstruction of w_i / sum(w) to 1e-6) and against
 //     the hand-checkable vectors the reference's smoke programs use (test/tmp.cu:31-42);
-//   * the draw / walk / k-hop rules against the reference kernels they restate, cited below.
+//   * the draw / walk / k-hop rules against the reference kernels they restate, cited below;
+//   * statistically, against the reference's OWN offline walk kernel run on the GPU
+//     (oracle/ref_cuda builds OfflineWalk / sample_kernel_static from the reference sources):
+//     fed with tables of this construction its transitions follow the edge weights, and its
+//     walks have the same length and visit statistics as the walks defined here
+//     (tests/test_reference_kernel.py).
 //
 // Each function cites the reference code it follows (paths inside the reference tree).
 // Everything here is deliberately sequential and naive: it is the definition the GPU kernels

@@ -1398,8 +1398,9 @@ int frontier_collect(skw_ctx* ctx, const u32* verts, u64 units, u32 width, u32 c
   frontier_reset_kernel<<<1, 32, 0, st>>>(ctx->frontier_cls, cap);
   SKW_LAUNCHED(ctx);
   if (units) {
+    // the claim is a chain of dependent accesses (vertex, offsets, stamp): fill every thread slot of the GPU
     const u64 want = (units + 255) / 256;
-    const int grid = (int)(want < (u64)ctx->sm_count * 8 ? want : (u64)ctx->sm_count * 8);
+    const int grid = (int)(want < (u64)ctx->sm_count * 16 ? want : (u64)ctx->sm_count * 16);
     frontier_collect_kernel<<<grid, 256, 0, st>>>(verts, units, width, cells, offs, alive_lengths,
                                                   ctx->xadj, ctx->V, ctx->stamp, ctx->stamp_round,
                                                   ctx->frontier_cls, ctx->frontier_lists, cap, ctx->d_err);

@@ -717,6 +717,15 @@ def test_packed_result_sliced_pipeline(ctx, oracle, rmat16):
         with pytest.raises(SkwError) as e:
             ctx.walk_packed(starts, 21, app=APP_PPR, tp=0.3, seed=8, walker_base=11, packed=small, lengths=lens2)
         assert str(cells) in str(e.value) and np.array_equal(lens2, olens)
+    # the packing buffers keep the size the PPR calls gave them; fixed-length walks of the same batch
+    # outgrow them, so every slice is packed a second time into a larger buffer
+    n = (1 << 20) + 5
+    starts = oracle.gen_starts(n, g.V, 6)
+    opaths, olens = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts, 11, seed=9)
+    live = np.arange(11)[None, :] <= olens[:, None]
+    out, lens, cells, _, edges = ctx.walk_packed(starts, 11, seed=9)
+    assert cells == int(live.sum()) and edges == int(olens.sum())
+    assert np.array_equal(lens, olens) and np.array_equal(out[:cells], opaths[live])
 
 
 def test_malformed_csr_is_refused(ctx, rmat12):
