@@ -167,14 +167,17 @@ def host_memory_available():
                 avail = int(line.split()[1]) * 1024
     except Exception:
         pass
-    try:
-        lim = open("/sys/fs/cgroup/memory.max").read().strip()
-        cur = int(open("/sys/fs/cgroup/memory.current").read().strip())
-        if lim != "max":
-            left = int(lim) - cur
-            avail = left if avail is None else min(avail, left)
-    except Exception:
-        pass
+    for lim_path, cur_path in (("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory.current"),
+                               ("/sys/fs/cgroup/memory/memory.limit_in_bytes",
+                                "/sys/fs/cgroup/memory/memory.usage_in_bytes")):
+        try:
+            lim = open(lim_path).read().strip()
+            cur = int(open(cur_path).read().strip())
+            if lim != "max" and int(lim) < (1 << 60):
+                left = int(lim) - cur
+                avail = left if avail is None else min(avail, left)
+        except Exception:
+            pass
     return avail
 
 
@@ -647,7 +650,7 @@ def main():
             probe_gacc = None
 
     # Parity at the workload's own size, on every rank: the first K units of the rank's shard against the
-    # CPU oracle (bit for bit), verdicts AND-reduced.  The oracle needs the graph (and table) on the host;
+    # CPU oracle (bit for bit), results AND-reduced.  The oracle needs the graph (and table) on the host;
     # ranks take turns in waves sized by the host memory that is free.
     cpu, parity, ref_cuda = None, None, None
     need = host_copy_bytes(V, E, online) + (4 * E if world == 1 and not online else 0)
@@ -699,7 +702,7 @@ def main():
             bytes_note = ("16 + 4*deg(v) bytes per walk step" if not khop else
                           "8 + 4*deg(v) per distinct frontier vertex of a hop + 8 per sample") + ", summed over the last step's frontier"
             achieved = online_bytes / (per_step_ms * 1e-3) / 1e9 * (edges_per_step_rank / max(last_edges, 1.0))
-            direct = (not khop) and n_local * max_deg <= 8 * E   # the library's own rule (skw_walk_device)
+            direct = not khop      # online walks compute drawn slots directly unless a flag asks for tables
             kernel_name = ("walk_online_direct_kernel" if direct else
                            "frontier_collect + degree-class builders + " + ("khop_hop_kernel" if khop else
                                                                             "walk_online_step_kernel"))

@@ -223,8 +223,9 @@ typedef struct skw_walk_params {
  * (src/online_walk.cu:82-166), and the walkers draw from them.  DIRECT_SLOTS: every walker computes
  * the one slot it draws straight from the weight list of its vertex (one warp per walker, all steps
  * in one launch, no table memory touched) -- the same (prob, alias) bits a built table holds, so
- * the walks are identical.  With neither flag the library picks: direct when few walkers share a
- * vertex (n * max_degree <= 8 * E), tables otherwise.  SKW_WALK_CACHE_TABLES implies BUILD_TABLES. */
+ * the walks are identical.  With neither flag the library computes slots directly (for the duration
+ * of a call it memoises, per vertex, the largest weight, the total and prefix sums at every 256th list
+ * position -- never a table entry).  SKW_WALK_CACHE_TABLES implies BUILD_TABLES. */
 #define SKW_WALK_BUILD_TABLES 4u
 #define SKW_WALK_DIRECT_SLOTS 8u
 

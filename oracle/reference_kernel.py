@@ -23,9 +23,13 @@ f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
-def build(reference_root="/root/reference"):
-    """Compile the harness against the reference tree when that tree is present; returns the path of
-    the library or None.  A machine without the tree uses the library built earlier."""
+def build(reference_root=None):
+    """Compile the harness against the reference tree when that tree is present (by default a directory
+    named `reference` beside this repository, or $SKYWALKER_REFERENCE); returns the path of the library
+    or None.  A machine without the tree uses the library built earlier."""
+    if reference_root is None:
+        reference_root = os.environ.get("SKYWALKER_REFERENCE") or os.path.join(
+            os.path.dirname(os.path.dirname(_HERE)), "reference")
     if os.path.isdir(os.path.join(reference_root, "src")):
         subprocess.check_call(["make", "-C", os.path.join(_HERE, "ref_cuda"), "-s", "REF=" + reference_root])
     return _SO if os.path.exists(_SO) else None

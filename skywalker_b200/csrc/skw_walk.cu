@@ -728,17 +728,13 @@ static int walk_launch(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t*
   const bool unbiased = (prm->flags & SKW_WALK_UNBIASED) != 0;
   const bool online = prm->mode == SKW_MODE_ONLINE && !unbiased;
   int rc;
-  // online walks evaluate the slot they draw straight from the weights; on request they build the
-  // tables of the frontier at every step instead (same walks)
-  // Which is cheaper depends on how many walkers share a vertex: a table is built once per distinct
-  // frontier vertex (at about four times the per-edge cost of one slot evaluation), a slot is
-  // evaluated once per walker.  The busiest vertex holds about n * max_degree / E walkers.
+  // Online walks evaluate the slot they draw straight from the weights; on request they build the
+  // tables of the frontier at every step instead (same walks).  With the per-vertex memo and the
+  // prefix checkpoints a slot evaluation costs two or three tiles of weights whatever the degree,
+  // while a table costs its whole list once per distinct frontier vertex and step, so the direct path
+  // is the default for every batch shape.
   bool build_tables = false;
-  if (online) {
-    if (prm->flags & (SKW_WALK_CACHE_TABLES | SKW_WALK_BUILD_TABLES)) build_tables = true;
-    else if (prm->flags & SKW_WALK_DIRECT_SLOTS) build_tables = false;
-    else build_tables = (double)n * (double)ctx->max_degree > 8.0 * (double)(ctx->E ? ctx->E : 1);
-  }
+  if (online) build_tables = (prm->flags & (SKW_WALK_CACHE_TABLES | SKW_WALK_BUILD_TABLES)) != 0;
   if (build_tables) {
     drop_records(ctx);  // online builds overwrite table slots
     if ((rc = alloc_table(ctx)) != SKW_OK) return rc;
