@@ -349,8 +349,14 @@ def main():
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip the reference's own CUDA walk kernel")
     ap.add_argument("--no-records", action="store_true", help="walk over the 8-byte slot table only")
     ap.add_argument("--cpu-threads", type=int, default=0)
+    ap.add_argument("--units", type=int, default=0,
+                    help="walkers / seeds in the whole job instead of the workload's own count, e.g. one "
+                         "GPU's share of an N-GPU run; the line's config says so")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.units > 0:
+        wl["units"] = args.units
+        wl["desc"] = wl["desc"] + " [--units %d instead of the configuration's own count]" % args.units
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

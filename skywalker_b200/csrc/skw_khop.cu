@@ -222,7 +222,8 @@ static int khop_validate(skw_ctx* ctx, const skw_khop_params* prm) {
 
 // Queue the kernels of one batch of seeds on the context's stream (sampled edges add up in d_sum[0]).
 static int khop_launch(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds, uint64_t n,
-                       uint32_t* d_data, uint32_t* d_sample_lengths, uint64_t instance_base) {
+                       uint32_t* d_data, uint32_t* d_sample_lengths, uint64_t instance_base,
+                       bool first_of_call) {
   const bool unbiased = (prm->flags & SKW_KHOP_UNBIASED) != 0;
   const bool online = prm->mode == SKW_MODE_ONLINE && !unbiased;
   int rc;
@@ -260,7 +261,11 @@ static int khop_launch(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t*
   khop_init_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(d_seeds, n, cells, d_data);
   SKW_LAUNCHED(ctx);
   for (uint32_t h = 0; h < prm->nhops; ++h) {
-    if (online && (rc = frontier_collect(ctx, d_data, n * width[h], width[h], cells, offs[h], nullptr, true)) != SKW_OK)
+    // A table built earlier in this call (an earlier hop, an earlier slice of the seeds) stays good:
+    // only the first collection of a call opens a new round of claims, every later one skips the
+    // vertices that already hold one.
+    if (online && (rc = frontier_collect(ctx, d_data, n * width[h], width[h], cells, offs[h], nullptr,
+                                         first_of_call && h == 0)) != SKW_OK)
       return rc;
     a.offs_parent = offs[h];
     a.offs_child = offs[h + 1];
@@ -291,7 +296,7 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
   if ((rc = err_reset(ctx)) != SKW_OK) return rc;
   SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
-  if ((rc = khop_launch(ctx, prm, d_seeds, n, d_data, d_sample_lengths, prm->instance_base)) != SKW_OK) return rc;
+  if ((rc = khop_launch(ctx, prm, d_seeds, n, d_data, d_sample_lengths, prm->instance_base, true)) != SKW_OK) return rc;
   SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
   SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
   if ((rc = err_check(ctx, "skw_sample_khop")) != SKW_OK) return rc;
@@ -317,15 +322,13 @@ int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_
   uint32_t* d_data = static_cast<uint32_t*>(ctx->stage[1]);
   uint32_t* d_lens = static_cast<uint32_t*>(ctx->stage[2]);
   cudaStream_t st = ctx->stream, side = ctx->side_stream;
-  // A result tree is dense (every cell crosses the bus), so a very large batch runs as two or four
-  // slices of seeds: while the kernels of slice c run on the context's stream, the tree of slice c - 1
-  // goes home on the side stream.  Seed ids, hence samples, do not depend on the slicing.  Slices pay
-  // for themselves only when they are large: every slice launches the whole per-hop kernel sequence
-  // again and online mode builds the tables of a hub once per slice instead of once per batch (measured
-  // on B200, online 2-hop 25 x 10 with 65,536 seeds: 3.4 ms per call in four slices against 2.6 ms
-  // unsliced), hence the threshold of 2^17 seeds per slice.
-  const uint64_t kSliceSeeds = 1u << 17;
-  const uint32_t slices = n >= 4 * kSliceSeeds ? 4 : (n >= 2 * kSliceSeeds ? 2 : 1);
+  // A result tree is dense (every cell crosses the bus), so a large batch runs as two or four slices
+  // of seeds: while the kernels of slice c run on the context's stream, the tree of slice c - 1 goes
+  // home on the side stream.  Seed ids, hence samples, do not depend on the slicing, and in online mode
+  // a vertex whose table an earlier slice built is not built again.  What a slice still costs is the
+  // per-hop launch sequence over a smaller frontier (measured on B200, online 2-hop 25 x 10 with 65,536
+  // seeds: 2.52 ms per call unsliced, 2.29 ms in two slices, 2.45 ms in four), so slices stay large.
+  const uint32_t slices = n >= (1u << 19) ? 4 : (n >= (1u << 16) ? 2 : 1);
   const uint64_t per = (n + slices - 1) / slices;
   const uint64_t stride = prm->instance_stride ? prm->instance_stride : 1;
   if ((rc = err_reset(ctx)) != SKW_OK) return rc;
@@ -337,7 +340,7 @@ int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_
     if (base >= n) break;
     const uint64_t nc = std::min<uint64_t>(per, n - base);
     rc = khop_launch(ctx, prm, d_seeds + base, nc, d_data + base * cells, d_lens + base * lens,
-                     prm->instance_base + base * stride);
+                     prm->instance_base + base * stride, c == 0);
     if (rc != SKW_OK) {
       cudaStreamSynchronize(side);
       cudaStreamSynchronize(st);

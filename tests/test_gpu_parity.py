@@ -866,14 +866,15 @@ def test_khop_distinct_runs_out_of_trials(ctx, oracle):
         ctx.sample_khop(seeds, [300], flags=KHOP_DISTINCT, seed=4)
 
 
+@pytest.mark.parametrize("n", [(1 << 16) + 1234, (1 << 19) + 77])     # two slices, four slices
 @pytest.mark.parametrize("mode", [MODE_OFFLINE, MODE_ONLINE])
-def test_khop_host_entry_sliced_pipeline(ctx, oracle, rmat16, mode):
-    """Batches of 2^18 seeds and more run as slices whose result copies overlap the next slice's
-    kernels: the host entry point returns what the oracle computes, slice boundaries included."""
+def test_khop_host_entry_sliced_pipeline(ctx, oracle, rmat16, mode, n):
+    """Batches of 2^16 seeds and more run as slices whose result copies overlap the next slice's
+    kernels (online: a table built for an earlier slice or hop is not built again): the host entry
+    point returns what the oracle computes, slice boundaries included."""
     g = rmat16
     _upload(ctx, g)
     ctx.alias_build_offline()
-    n = (1 << 18) + 1234
     seeds = oracle.gen_starts(n, g.V, 21)
     data, sl, _, edges = ctx.sample_khop(seeds, [3, 2], mode=mode, seed=13, instance_base=5)
     assert edges == int(sl.sum())
