@@ -660,10 +660,15 @@ struct CtaCoop {
 
 // Merge of the packed lists: S smalls at A[0 .. S) with key = inclusive deficit prefix, L = n - S
 // larges from the back (large j at A[n - 1 - j]) with key = inclusive excess prefix.  Thread t emits
-// an equal share of the merged order.
+// an equal share of the merged order.  Keys are compared and subtracted where they sit, in bits 12
+// and up of an entry (a mass times 2^12 rounds to the same float as the mass, the scale being a
+// power of two).  A step of the loop has no branch: the entry that leaves, the entry that names the
+// alias and the two keys that make up the mass are selected, and one load refills the window of
+// three entries (the small at the head, the large at the head, the large behind it).
 template <int NT>
 __device__ __forceinline__ void merge_packed(u32 t, u32 n, u32 S, const u64* A, u64 C, int B, u32 off,
                                              Slot* __restrict__ slots, u32 v, u32* err) {
+  constexpr u64 kKeyBits = ~kPosMask;
   const u32 L = n - S;
   const u32 VT = (n + NT - 1) / NT;
   const u32 k0 = min(t * VT, n), k1 = min(k0 + VT, n);
@@ -673,57 +678,52 @@ __device__ __forceinline__ void merge_packed(u32 t, u32 n, u32 S, const u64* A, 
     u32 lo = k0 > L ? k0 - L : 0, hi = min(k0, S);
     while (lo < hi) {  // small mid precedes large k0-1-mid iff its key (deficit before it) <= that large's key
       const u32 mid = (lo + hi) >> 1;
-      const u64 a = mid ? (A[mid - 1] >> kPosBits) : 0;
-      const u64 b = A[n - 1 - (k0 - 1 - mid)] >> kPosBits;
+      const u64 a = mid ? (A[mid - 1] & kKeyBits) : 0;
+      const u64 b = A[n - 1 - (k0 - 1 - mid)] & kKeyBits;
       if (a <= b) lo = mid + 1;
       else hi = mid;
     }
     i = lo;
   }
+  // i <= S and j <= L hold from here on, and i + j = k < n: the entry that leaves always exists
   u32 j = k0 - i;
-  u64 dsx = i ? (A[i - 1] >> kPosBits) : 0;  // deficit of the smalls before small i
-  u64 hs = i < S ? A[i] : kListEnd;          // heads of the two lists
+  u64 dsx = i ? (A[i - 1] & kKeyBits) : 0;  // deficit of the smalls before small i
+  u64 hs = i < S ? A[i] : kListEnd;
   u64 hl = j < L ? A[n - 1 - j] : kListEnd;
+  u64 hl2 = j + 1 < L ? A[n - 2 - j] : kListEnd;
+  const u64 Cs = C << kPosBits;
+  const int Bs = B + kPosBits;
+  Slot* __restrict__ out = slots + off;
+  bool bad = false;
   for (u32 k = k0; k < k1; ++k) {
-    Slot out;
-    u32 p;
-    if (i < S && dsx <= (hl >> kPosBits)) {
-      p = (u32)(hs & kPosMask);
-      const u64 dincl = hs >> kPosBits;
-      if (j >= L) {  // mass conservation: the last large is emitted after every small
-        dev_fail(err, DEV_ERR_INTERNAL, v, p, 10);
-        out.alias = p;
-      } else {
-        out.alias = (u32)(hl & kPosMask);
-      }
-      out.prob = mass_to_prob_fast(C - (dincl - dsx), B);
-      dsx = dincl;
-      ++i;
-      hs = i < S ? A[i] : kListEnd;
-    } else {
-      if (j >= L) {  // cannot happen: k < n outputs remain, so one of the lists has an entry
-        dev_fail(err, DEV_ERR_INTERNAL, v, k, 9);
-        break;
-      }
-      p = (u32)(hl & kPosMask);
-      const u64 xl = hl >> kPosBits;
-      const u64 nx = j + 1 < L ? A[n - 2 - j] : kListEnd;
-      if (dsx <= xl) {  // only once every small is placed: the large owns one full bucket
-        out.alias = p;
-        out.prob = 1.0f;
-      } else if (nx == kListEnd) {
-        dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
-        out.alias = p;
-        out.prob = 1.0f;
-      } else {
-        out.alias = (u32)(nx & kPosMask);
-        out.prob = mass_to_prob_fast(xl + C - dsx, B);
-      }
-      ++j;
-      hl = nx;
-    }
-    slots[(u64)off + p] = out;
+    const u64 ks = hs & kKeyBits, kl = hl & kKeyBits;
+    const bool fits = dsx <= kl;           // the large at the head still has room for a small
+    const bool take = i < S && fits;       // a small leaves; else a large
+    const bool full = !take && fits;       // only once every small is placed: the large owns its bucket
+    const u64 e = take ? hs : hl;
+    const u64 a = take ? hl : hl2;         // a small's alias is the large at the head, a large's the next one
+    const u32 p = (u32)e & (u32)kPosMask;
+    // mass conservation puts the last large after every small and leaves no large short of a
+    // successor; an entry that is missing all the same is recorded and the slot made self-contained
+    const bool none = (u32)(a >> 32) == 0xFFFFFFFFu;  // a key stays below 2^52 - 2^40: only kListEnd has these bits
+    bad |= none && !full;
+    const bool self = full || none;
+    const u64 x = take ? dsx : kl, y = take ? ks : dsx;  // small: C - (ks - dsx); large: kl + C - dsx
+    Slot o;
+    o.prob = self ? 1.0f : mass_to_prob_fast(Cs + x - y, Bs);
+    o.alias = self ? p : ((u32)a & (u32)kPosMask);
+    out[p] = o;
+    i += take ? 1u : 0u;
+    j += take ? 0u : 1u;
+    const u32 idx = take ? i : n - 2 - j;
+    const bool more = take ? i < S : j + 1 < L;
+    const u64 nx = more ? A[idx] : kListEnd;
+    dsx = take ? ks : dsx;
+    hl = take ? hl : hl2;
+    hl2 = take ? hl2 : nx;
+    hs = take ? nx : hs;
   }
+  if (bad) dev_fail(err, DEV_ERR_INTERNAL, v, k0, 8);
 }
 
 // Table of one vertex (degree n <= 4096) by the threads of `co`; A holds n packed list entries.
@@ -779,12 +779,13 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
     // warp one tile of 8 elements per lane plus one of 1, not two of 8.
     const u32 ept = SINGLE ? (u32)EPT : min((u32)EPT, (n - base + NT - 1) / NT);
     const u32 p0 = base + t * ept;
+    const u32 cnt = p0 < n ? min(ept, n - p0) : 0u;  // elements of this thread in this tile
     if constexpr (!SINGLE) {
       Qex = 0;
 #pragma unroll
       for (int k = 0; k < EPT; ++k) {
         m[k] = 0;
-        if ((u32)k < ept && p0 + k < n) m[k] = quantise_bits(weight(p0 + k), sh);
+        if ((u32)k < cnt) m[k] = quantise_bits(weight(p0 + k), sh);
         Qex += m[k];
       }
       u64 tq;
@@ -796,7 +797,7 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
     u64 g_prev = gex, Q = Qex, pk = 0;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
-      if ((u32)k < ept && p0 + k < n) {
+      if ((u32)k < cnt) {
         Q += m[k];
         const u64 g = cum_mass(Q, W, nC, K);
         m[k] = g - g_prev;
@@ -813,15 +814,15 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
       const u32 p = p0 + k;
-      if ((u32)k < ept && p < n) {
+      if ((u32)k < cnt) {
         gc += m[k];
-        if (m[k] < C) {
-          Dr += C - m[k];
-          A[Sr++] = (Dr << kPosBits) | p;
-        } else {
-          const u64 X = Dr + gc - ((u64)(p + 1) << B);  // inclusive excess prefix
-          A[n - 1 - (p - Sr)] = (X << kPosBits) | p;
-        }
+        const bool small = m[k] < C;
+        Dr += small ? C - m[k] : 0ull;
+        // a small carries the inclusive deficit prefix, a large the inclusive excess prefix
+        const u64 key = small ? Dr : Dr + gc - ((u64)(p + 1) << B);
+        const u32 at = small ? Sr : n - 1 - (p - Sr);
+        Sr += small ? 1u : 0u;
+        A[at] = (key << kPosBits) | p;
       }
     }
   }

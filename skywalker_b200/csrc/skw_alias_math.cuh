@@ -29,16 +29,19 @@ __device__ __forceinline__ double weight_scale(float wmax, int B) {
 __device__ __forceinline__ u64 quantise(float w, double scale) {
   return __double2ull_rz(__dmul_rn((double)w, scale));
 }
-// The same value as quantise(w, 2^s) from the bits of w (w > 0 finite or 0), without the
-// fp64 conversions: trunc(w * 2^s) = mantissa shifted by (exponent + s).
+// The same value as quantise(w, 2^s) from the bits of w (w > 0 finite or 0), without the fp64
+// conversions: w = M * 2^(max(ew, 1) - 150) with M the 24-bit significand (no hidden bit when the
+// exponent field ew is 0), so trunc(w * 2^s) = (M * 2^40) >> (190 - s - max(ew, 1)).  The shift
+// count is at least 24 for every weight up to the one s was derived from, and the PTX shift gives 0
+// for counts of 64 and more (weights too small to register), which C++ leaves undefined.
 __device__ __forceinline__ u64 quantise_bits(float w, int s) {
   const u32 b = __float_as_uint(w);
   const u32 ew = b >> 23;
-  const u32 mant = b & 0x7FFFFFu;
-  const u64 M = ew ? (u64)(mant | 0x800000u) : (u64)mant;
-  const int sh = s + (ew ? (int)ew - 150 : -149);
-  if (sh >= 0) return sh < 64 ? M << sh : 0;  // sh < 40 by construction
-  return sh > -64 ? M >> (-sh) : 0;
+  const u32 M = (b & 0x7FFFFFu) | (ew ? 0x800000u : 0u);
+  const u32 r = (u32)(190 - s) - max(ew, 1u);
+  u64 q;
+  asm("shr.b64 %0, %1, %2;" : "=l"(q) : "l"((u64)(M << 8) << 32), "r"(r));
+  return q;
 }
 // s of quantise_bits for the largest weight wmax (> 0): B - 1 - floor(log2 wmax)
 __device__ __forceinline__ int weight_shift(float wmax, int B) {
