@@ -337,64 +337,57 @@ __device__ __forceinline__ void merge_window(u32 t, u32 nl, u32 Sl, const u64* s
     i = lo;
     j = k0 - lo;
   }
+  // i <= Sl and j <= Ll hold from here on, and i + j = k < nl: the entry that leaves always exists.
+  // A step has no branch (see merge_packed): a window of three entries stays in registers, the
+  // small at the head, the large at the head and the large behind it; past the window's last large
+  // the key is "never full" and the position that of the next window's first large.
+  constexpr u64 kNever = ~0ull;
   u64 dsx = i ? sA[i - 1] : dsx_in;  // deficit of the smalls before small i
-  // the heads of both lists stay in registers: one pair of shared-memory loads per output
-  u64 sk = 0, lk = 0;
-  u32 sp = 0, lp = next_pos;  // a small left over after the window's last large belongs to the first
-  bool lhave = j < Ll;        // large of the next window
+  u64 sk = 0, lk = kNever, lk2 = kNever;
+  u32 sp = 0, lp = next_pos, lp2 = next_pos;
   if (i < Sl) {
     sk = sA[i];
     sp = sP[i];
   }
-  if (lhave) {
+  if (j < Ll) {
     lk = sA[nl - 1 - j];
     lp = sP[nl - 1 - j];
   }
-  for (u32 k = k0; k < k1; ++k) {
-    Slot out;
-    u32 p;
-    if (i < Sl && (!lhave || dsx <= lk)) {
-      p = sp;
-      if (lp == kNoNext) {
-        dev_fail(err, DEV_ERR_INTERNAL, v, p, 10);
-        out.alias = p;
-      } else {
-        out.alias = lp;
-      }
-      out.prob = mass_to_prob_fast(C - (sk - dsx), B);
-      dsx = sk;
-      if (++i < Sl) {
-        sk = sA[i];
-        sp = sP[i];
-      }
-    } else {
-      if (!lhave) {  // cannot happen: a window's share of larges is fixed by its boundaries
-        dev_fail(err, DEV_ERR_INTERNAL, v, k, 9);
-        break;
-      }
-      p = lp;
-      const u64 xl = lk;
-      ++j;
-      lhave = j < Ll;
-      lp = next_pos;
-      if (lhave) {
-        lk = sA[nl - 1 - j];
-        lp = sP[nl - 1 - j];
-      }
-      if (dsx <= xl) {  // only possible once every small is placed: the large owns one full bucket
-        out.alias = p;
-        out.prob = 1.0f;
-      } else if (lp == kNoNext) {
-        dev_fail(err, DEV_ERR_INTERNAL, v, p, 8);
-        out.alias = p;
-        out.prob = 1.0f;
-      } else {
-        out.alias = lp;
-        out.prob = mass_to_prob_fast(xl + C - dsx, B);
-      }
-    }
-    slots[(u64)off + p] = out;
+  if (j + 1 < Ll) {
+    lk2 = sA[nl - 2 - j];
+    lp2 = sP[nl - 2 - j];
   }
+  Slot* __restrict__ out = slots + off;
+  bool bad = false;
+  for (u32 k = k0; k < k1; ++k) {
+    const bool fits = dsx <= lk;
+    const bool take = i < Sl && fits;              // a small leaves; else a large
+    const bool full = !take && fits;               // only once every small is placed
+    const u32 p = take ? sp : lp;
+    const u32 a = take ? lp : lp2;                 // a small's alias: the large at the head; a large's: the next one
+    const bool none = a == kNoNext;
+    bad |= none && !full;                          // mass conservation rules it out
+    const bool self = full || none;
+    const u64 x = take ? dsx : lk, y = take ? sk : dsx;  // small: C - (sk - dsx); large: lk + C - dsx
+    Slot o;
+    o.prob = self ? 1.0f : mass_to_prob_fast(C + x - y, B);
+    o.alias = self ? p : a;
+    out[p] = o;
+    i += take ? 1u : 0u;
+    j += take ? 0u : 1u;
+    const u32 idx = take ? i : nl - 2 - j;
+    const bool more = take ? i < Sl : j + 1 < Ll;
+    const u64 nk = more ? sA[idx] : kNever;
+    const u32 np = more ? sP[idx] : next_pos;
+    dsx = take ? sk : dsx;
+    lk = take ? lk : lk2;
+    lp = take ? lp : lp2;
+    lk2 = take ? lk2 : nk;
+    lp2 = take ? lp2 : np;
+    sk = take ? nk : sk;
+    sp = take ? np : sp;
+  }
+  if (bad) dev_fail(err, DEV_ERR_INTERNAL, v, k0, 8);
 }
 
 // WIN == 0: the lists A / P are in shared memory and are merged in place.  WIN > 0: they are in
@@ -737,11 +730,14 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
   auto weight = [&](u32 p) { return sane_weight(STAGED ? w[p] : __ldg(w + p)); };
   float wr[EPT];
   float wmax = 0.0f;
+  // SINGLE: the list is one tile, spread evenly over the threads (ceil(n / NT) <= EPT elements each)
+  const u32 ept1 = (n + NT - 1) / NT;
   if constexpr (SINGLE) {
+    const u32 p1 = t * ept1;
+    const u32 cnt1 = p1 < n ? min(ept1, n - p1) : 0u;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
-      const u32 p = t * EPT + k;
-      wr[k] = p < n ? weight(p) : 0.0f;
+      wr[k] = (u32)k < cnt1 ? weight(p1 + k) : 0.0f;
       wmax = fmaxf(wmax, wr[k]);
     }
   } else {
@@ -777,7 +773,7 @@ __device__ __forceinline__ void build_vertex_packed(const Coop& co, u32 v, u32 o
     // A ragged last tile spreads its elements over all threads (ept of them each, the same in every
     // thread) instead of filling the first threads with EPT each: a list of 278 weights then costs a
     // warp one tile of 8 elements per lane plus one of 1, not two of 8.
-    const u32 ept = SINGLE ? (u32)EPT : min((u32)EPT, (n - base + NT - 1) / NT);
+    const u32 ept = SINGLE ? ept1 : min((u32)EPT, (n - base + NT - 1) / NT);
     const u32 p0 = base + t * ept;
     const u32 cnt = p0 < n ? min(ept, n - p0) : 0u;  // elements of this thread in this tile
     if constexpr (!SINGLE) {
