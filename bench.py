@@ -310,9 +310,10 @@ def parity_sample(ctx, wl, host, lo, n_local, d_starts, d_result, d_lengths, mod
     live = np.arange(hop)[None, :] <= want_l[:, None]
     ok = ok and bool(np.array_equal(got_l, want_l)) and bool(np.array_equal(got_p[live], want_p[live]))
     # the packed host entry point on the same walkers
-    packed, pl, cells, _, _ = ctx.walk_packed(h_starts, hop, mode=mode, **kw)
-    ok = ok and bool(np.array_equal(pl, want_l)) and cells == int(want_l.sum()) + K
-    ok = ok and bool(np.array_equal(packed[:cells], want_p[live]))
+    for u8 in ((False, True) if hop <= 256 else (False,)):
+        packed, pl, cells, _, _ = ctx.walk_packed(h_starts, hop, mode=mode, lengths_u8=u8, **kw)
+        ok = ok and bool(np.array_equal(pl, want_l)) and cells == int(want_l.sum()) + K
+        ok = ok and bool(np.array_equal(packed[:cells], want_p[live]))
     return K, ok
 
 
@@ -615,18 +616,31 @@ def main():
         if not khop:
             # the same walks returned packed (lengths + the walks back to back): only result cells cross
             # the bus, as one contiguous stream instead of one small write per row
-            def packed_call(i):
+            def packed_call(i, u8=False):
                 return ctx.walk_packed(np_s, hop, app=app_id(wl), mode=mode, tp=wl.get("tp", 0.0), p=wl.get("p", 2.0),
                                        q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, packed=np_r,
-                                       lengths=np_l, n=n_local)[4]
+                                       lengths=np_l.view(np.uint8)[:n_local] if u8 else np_l, n=n_local,
+                                       lengths_u8=u8)[4]
             p_ms, p_edges, p_calls = timed_host_calls(packed_call)
-            e2e = {"ms_per_call_this_rank": p_calls, "ms_per_call_median": float(np.median(p_calls)), "value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
-                   "ms_per_step": p_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
-                   "d2h_bytes_per_step": int(4 * (p_edges / e_steps / world + 2 * n_local)),
-                   "note": "host-buffer entry point skw_walk_packed with pinned memory: start vertices H2D, walk "
+            packed32 = {"ms_per_call_this_rank": p_calls, "ms_per_call_median": float(np.median(p_calls)),
+                        "value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+                        "ms_per_step": p_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
+                        "d2h_bytes_per_step": int(4 * (p_edges / e_steps / world + 2 * n_local)),
+                        "note": "skw_walk_packed: the same with 32-bit lengths"}
+            e2e = packed32
+            if hop <= 256:
+                # lengths of at most 255 travel as bytes: the result is bound by the bus
+                p_ms, p_edges, p_calls = timed_host_calls(lambda i: packed_call(i, True))
+                e2e = {"ms_per_call_this_rank": p_calls, "ms_per_call_median": float(np.median(p_calls)),
+                       "value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+                       "ms_per_step": p_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
+                       "d2h_bytes_per_step": int(4 * (p_edges / e_steps / world + n_local) + n_local),
+                       "packed_u32_lengths": packed32}
+            e2e["note"] = ("host-buffer entry point skw_walk_packed_u8 with pinned memory: start vertices H2D, walk "
                            "kernel, prefix sum of the lengths, pack kernel writing lengths[w] + 1 vertices per walk "
-                           "back to back into the pinned result buffer, lengths D2H",
-                   "row_layout": rows}
+                           "back to back, one contiguous copy per slice into the pinned result buffer, lengths "
+                           "D2H as bytes")
+            e2e["row_layout"] = rows
 
     # NCCL gather of the results to rank 0 (outside the timed region): the per-unit lengths, and the
     # result arrays themselves when the shards are equal and fit beside the graph on rank 0
@@ -696,7 +710,8 @@ def main():
             t = mn
         parity = {"units": int(t[1].item()), "equal": bool(t[0].item()), "ranks": world,
                   "what": "first K %s of every rank's shard, row layout%s, against the CPU oracle bit for bit"
-                          % ("seeds" if khop else "walkers", "" if khop else " and packed layout")}
+                          % ("seeds" if khop else "walkers",
+                             "" if khop else " and packed layout (32-bit and byte lengths)")}
     config["parity_sample"] = parity
     if sliced is not None:
         config["alias_build_sliced_equals_replicated"] = sliced["equals_replicated_build"]

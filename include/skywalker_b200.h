@@ -275,6 +275,12 @@ int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts,
 int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
                     uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_lengths, uint64_t* cells,
                     float* ms, uint64_t* sampled_edges);
+/* The same with one byte per length (h_lengths8[w] = lengths[w]); prm->hop_num must not exceed 256,
+ * so that every length fits.  The lengths are a sixth of what a PPR batch sends home (about 2.6
+ * vertices per walk at tp = 0.15), and the result is bound by the bus. */
+int skw_walk_packed_u8(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+                       uint32_t* h_packed, uint64_t capacity_cells, uint8_t* h_lengths8, uint64_t* cells,
+                       float* ms, uint64_t* sampled_edges);
 
 /* ---------------------------------------------------------------- k-hop sampling --------- */
 

@@ -72,6 +72,8 @@ SIGNATURES = {
                            C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "skw_walk_packed": (C.c_int, [C.c_void_p, C.POINTER(WalkParams), C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64,
                                   C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
+    "skw_walk_packed_u8": (C.c_int, [C.c_void_p, C.POINTER(WalkParams), C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64,
+                                     C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "skw_khop_layout": (C.c_int, [C.POINTER(KhopParams), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "skw_sample_khop_device": (C.c_int, [C.c_void_p, C.POINTER(KhopParams), C.c_void_p, C.c_uint64, C.c_void_p,
                                          C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),

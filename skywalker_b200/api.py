@@ -236,22 +236,23 @@ class Context:
         return paths, lengths, ms.value, edges.value
 
     def walk_packed(self, starts, hop_num, app=APP_DEEPWALK, mode=MODE_OFFLINE, tp=0.0, p=2.0, q=0.5, seed=42,
-                    walker_base=0, packed=None, lengths=None, n=None, walker_stride=1, flags=0):
+                    walker_base=0, packed=None, lengths=None, n=None, walker_stride=1, flags=0, lengths_u8=False):
         """Host arrays in, packed result out: returns (packed, lengths, cells, ms, sampled_edges) with the
         walks back to back in packed[:cells] (walk w holds lengths[w] + 1 vertices).  `packed` may be a
-        numpy array or a pinned buffer; without one a buffer of n * hop_num cells is allocated."""
+        numpy array or a pinned buffer; without one a buffer of n * hop_num cells is allocated.
+        lengths_u8: the lengths come back as bytes (skw_walk_packed_u8; hop_num <= 256)."""
         prm = WalkParams(app, mode, hop_num, tp, p, q, seed, walker_base, walker_stride, flags)
         starts = starts if _is_device(starts) else np.ascontiguousarray(starts, np.uint32)
         n = (int(starts.numel()) if _is_device(starts) else len(starts)) if n is None else n
         if packed is None:
             packed = np.empty(max(n * hop_num, 1), np.uint32)
         if lengths is None:
-            lengths = np.zeros(max(n, 1), np.uint32)[:n]
+            lengths = np.zeros(max(n, 1), np.uint8 if lengths_u8 else np.uint32)[:n]
         cap = int(packed.numel()) if hasattr(packed, "numel") else int(packed.size)
         ms, edges, cells = C.c_float(), C.c_uint64(), C.c_uint64()
-        self._ck(self._lib.skw_walk_packed(self._h, C.byref(prm), _ptr(starts) if n else None, n, _ptr(packed), cap,
-                                           _ptr(lengths) if n else None, C.byref(cells), C.byref(ms),
-                                           C.byref(edges)))
+        fn = self._lib.skw_walk_packed_u8 if lengths_u8 else self._lib.skw_walk_packed
+        self._ck(fn(self._h, C.byref(prm), _ptr(starts) if n else None, n, _ptr(packed), cap,
+                    _ptr(lengths) if n else None, C.byref(cells), C.byref(ms), C.byref(edges)))
         return packed, lengths, cells.value, ms.value, edges.value
 
     def take_sampled_edges(self):

@@ -344,6 +344,7 @@ int skw_ctx_create(int device, skw_ctx** out) {
   CK(cudaMallocHost(&ctx->h_err, 8 * sizeof(uint32_t)));
   for (int i = 0; i < skw_ctx::kPackSlices; ++i) {
     CK(cudaEventCreateWithFlags(&ctx->pk_ready[i], cudaEventDisableTiming));
+    CK(cudaEventCreateWithFlags(&ctx->pk_in[i], cudaEventDisableTiming));
     CK(cudaEventCreateWithFlags(&ctx->pk_tot[i], cudaEventDisableTiming));
     CK(cudaEventCreate(&ctx->pk_t0[i]));
     CK(cudaEventCreate(&ctx->pk_t1[i]));
@@ -391,6 +392,7 @@ void skw_ctx_destroy(skw_ctx* ctx) {
   if (ctx->bfork) cudaEventDestroy(ctx->bfork);
   for (int i = 0; i < skw_ctx::kPackSlices; ++i) {
     if (ctx->pk_ready[i]) cudaEventDestroy(ctx->pk_ready[i]);
+    if (ctx->pk_in[i]) cudaEventDestroy(ctx->pk_in[i]);
     if (ctx->pk_tot[i]) cudaEventDestroy(ctx->pk_tot[i]);
     if (ctx->pk_t0[i]) cudaEventDestroy(ctx->pk_t0[i]);
     if (ctx->pk_t1[i]) cudaEventDestroy(ctx->pk_t1[i]);

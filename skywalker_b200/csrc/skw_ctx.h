@@ -29,7 +29,8 @@ struct skw_ctx {
   cudaStream_t copy_stream = nullptr;  // skw_walk_packed: the packed rows of each slice
   // skw_walk_packed, per slice: rows packed; cell count on the host; start and end of the walk
   static constexpr int kPackSlices = 8;
-  cudaEvent_t pk_ready[kPackSlices] = {}, pk_tot[kPackSlices] = {}, pk_t0[kPackSlices] = {}, pk_t1[kPackSlices] = {};
+  cudaEvent_t pk_ready[kPackSlices] = {}, pk_tot[kPackSlices] = {}, pk_t0[kPackSlices] = {}, pk_t1[kPackSlices] = {},
+              pk_in[kPackSlices] = {};
   uint64_t* d_tot = nullptr;  // cells each slice's packed result needs
   uint64_t* h_tot = nullptr;  // pinned mirror
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -94,7 +95,7 @@ struct skw_ctx {
   void* host_pool = nullptr;  // skw::HostPool
 
   // staging buffers of the host-pointer entry points, grown on demand
-  static constexpr int kStages = 12;
+  static constexpr int kStages = 13;
   void* stage[kStages] = {};
   size_t stage_bytes[kStages] = {};
 };

@@ -521,12 +521,15 @@ struct CellsOfRow {
 __global__ void __launch_bounds__(256) pack_rows_kernel(const u32* __restrict__ src, u32* __restrict__ packed,
                                                         const u32* __restrict__ lengths,
                                                         const u64* __restrict__ offs, u64 n, u32 hop_num,
-                                                        u64 capacity, u64* __restrict__ total) {
+                                                        u64 capacity, u64* __restrict__ total,
+                                                        uint8_t* __restrict__ lengths8) {
   const u32 sub = threadIdx.x & 7;
   const u64 rows_per_pass = ((u64)gridDim.x * blockDim.x) >> 3;
   for (u64 w = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 3; w < n; w += rows_per_pass) {
-    const u32 cells = min(__ldg(lengths + w) + 1u, hop_num);
+    const u32 len = __ldg(lengths + w);
+    const u32 cells = min(len + 1u, hop_num);
     const u64 o = __ldg(offs + w);
+    if (lengths8 && sub == 0) lengths8[w] = (uint8_t)len;  // the caller asked for one byte per walk
     if (w == n - 1 && sub == 0) *total = o + cells;  // cells the whole batch needs
     // rows that do not fit are left out: the host compares *total with the capacity and packs again
     // into a larger buffer
@@ -949,17 +952,23 @@ int skw_walk(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts,
   return SKW_OK;
 }
 
-int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
-                    uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_lengths, uint64_t* cells,
-                    float* ms, uint64_t* sampled_edges) {
+}  // extern "C"
+
+// The packed host entry points: lengths come home as 32-bit words (h_lengths) or, for walks of at
+// most 256 vertices, as bytes (h_lengths8); exactly one of the two is given.
+static int walk_packed_impl(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+                            uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_lengths,
+                            uint8_t* h_lengths8, uint64_t* cells, float* ms, uint64_t* sampled_edges) {
   if (!ctx || !prm) return SKW_ERR_ARG;
   if (!cells) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: cells must not be null");
   *cells = 0;
   if (ms) *ms = 0;
   if (sampled_edges) *sampled_edges = 0;
-  if (n && (!h_starts || !h_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: null buffer");
+  if (n && (!h_starts || (!h_lengths && !h_lengths8))) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: null buffer");
   int rc = walk_check(ctx, prm);
   if (rc != SKW_OK) return rc;
+  if (h_lengths8 && prm->hop_num > 256)
+    return fail(ctx, SKW_ERR_ARG, "skw_walk_packed_u8: a length of up to %u does not fit a byte", prm->hop_num - 1);
   if (!n) return SKW_OK;
   DeviceGuard g(ctx->device);
   cudaStream_t st = ctx->stream, side = ctx->side_stream;
@@ -984,6 +993,11 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
     return rc;
   if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], sizeof(u32) * (size_t)n)) != SKW_OK) return rc;
   if ((rc = ensure_bytes(ctx, &ctx->stage[3], &ctx->stage_bytes[3], offs_bytes + tmp_bytes)) != SKW_OK) return rc;
+  constexpr int kLen8Stage = 4 + skw_ctx::kPackSlices;
+  static_assert(skw_ctx::kStages > kLen8Stage, "one more staging buffer for byte lengths");
+  if (h_lengths8 && (rc = ensure_bytes(ctx, &ctx->stage[kLen8Stage], &ctx->stage_bytes[kLen8Stage], (size_t)n)) != SKW_OK)
+    return rc;
+  uint8_t* d_len8 = h_lengths8 ? static_cast<uint8_t*>(ctx->stage[kLen8Stage]) : nullptr;
   u32* d_starts = static_cast<u32*>(ctx->stage[0]);
   u32* d_rows = static_cast<u32*>(ctx->stage[1]);
   u32* d_len = static_cast<u32*>(ctx->stage[2]);
@@ -1020,7 +1034,8 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
     // per row do not merge into full-size bus writes).
     pack_rows_kernel<<<grid_for(ctx, nc * 8, 8), 256, 0, st>>>(d_rows + base * prm->hop_num,
                                                               static_cast<u32*>(ctx->stage[4 + c]), d_len + base, d_offs, nc,
-                                                              prm->hop_num, cap[c], ctx->d_tot + c);
+                                                              prm->hop_num, cap[c], ctx->d_tot + c,
+                                                              d_len8 ? d_len8 + base : nullptr);
     SKW_LAUNCHED(ctx);
     SKW_CUDA(ctx, cudaEventRecord(ctx->pk_ready[c], st));
     SKW_CUDA(ctx, cudaStreamWaitEvent(side, ctx->pk_ready[c], 0));
@@ -1029,11 +1044,16 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
     return SKW_OK;
   };
   auto body = [&]() -> int {
+    // the start vertices come in slice by slice on the side stream, ahead of everything else it will
+    // carry: a walk waits for its own slice only, and no walk waits behind a copy of a later slice
     for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
       const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
-      // the start vertices of a slice come in right before its walk: a quarter of the input at a time,
-      // on the bus together with the results of the slice before
-      SKW_CUDA(ctx, cudaMemcpyAsync(d_starts + base, h_starts + base, sizeof(u32) * (size_t)nc, cudaMemcpyHostToDevice, st));
+      SKW_CUDA(ctx, cudaMemcpyAsync(d_starts + base, h_starts + base, sizeof(u32) * (size_t)nc, cudaMemcpyHostToDevice, side));
+      SKW_CUDA(ctx, cudaEventRecord(ctx->pk_in[c], side));
+    }
+    for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
+      const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+      SKW_CUDA(ctx, cudaStreamWaitEvent(st, ctx->pk_in[c], 0));
       skw_walk_params p = *prm;
       p.walker_base = prm->walker_base + base * stride;
       SKW_CUDA(ctx, cudaEventRecord(ctx->pk_t0[c], st));
@@ -1041,7 +1061,10 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
       if (r != SKW_OK) return r;
       SKW_CUDA(ctx, cudaEventRecord(ctx->pk_t1[c], st));
       if ((r = scan_and_pack(c)) != SKW_OK) return r;
-      SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths + base, d_len + base, sizeof(u32) * (size_t)nc, cudaMemcpyDeviceToHost, side));
+      if (h_lengths8)
+        SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths8 + base, d_len8 + base, (size_t)nc, cudaMemcpyDeviceToHost, side));
+      else
+        SKW_CUDA(ctx, cudaMemcpyAsync(h_lengths + base, d_len + base, sizeof(u32) * (size_t)nc, cudaMemcpyDeviceToHost, side));
     }
     // the host follows the device slice by slice: learn the size, start the copy
     uint64_t total_cells = 0;
@@ -1095,6 +1118,24 @@ int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_
     ctx->err = why;
   }
   return rc;
+}
+
+extern "C" {
+
+int skw_walk_packed(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+                    uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_lengths, uint64_t* cells,
+                    float* ms, uint64_t* sampled_edges) {
+  if (ctx && n && !h_lengths) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed: null buffer");
+  return walk_packed_impl(ctx, prm, h_starts, n, h_packed, capacity_cells, h_lengths, nullptr, cells, ms,
+                          sampled_edges);
+}
+
+int skw_walk_packed_u8(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t* h_starts, uint64_t n,
+                       uint32_t* h_packed, uint64_t capacity_cells, uint8_t* h_lengths8, uint64_t* cells,
+                       float* ms, uint64_t* sampled_edges) {
+  if (ctx && n && !h_lengths8) return fail(ctx, SKW_ERR_ARG, "skw_walk_packed_u8: null buffer");
+  return walk_packed_impl(ctx, prm, h_starts, n, h_packed, capacity_cells, nullptr, h_lengths8, cells, ms,
+                          sampled_edges);
 }
 
 }  // extern "C"

@@ -630,6 +630,18 @@ def test_packed_host_result_matches_rows(ctx, oracle, plaw, pinned):
     out3, lens3, cells3, _, _ = ctx.walk_packed(starts[:100], 11, seed=3)
     p3, l3 = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts[:100], 11, seed=3)
     assert np.array_equal(out3[:cells3], np.concatenate([p3[w, :l3[w] + 1] for w in range(100)]))
+    # lengths as bytes (skw_walk_packed_u8): the same walks, one byte per length
+    packed[:] = 0xABCDEF01
+    out8, lens8, cells8, _, edges8 = ctx.walk_packed(starts, 101, app=APP_PPR, tp=0.15, seed=13, packed=packed,
+                                                     lengths_u8=True)
+    assert lens8.dtype == np.uint8 and np.array_equal(lens8, olens)
+    assert cells8 == cells and edges8 == edges and np.array_equal(out8[:cells8], want)
+    assert (out8[cells8:] == 0xABCDEF01).all()
+    out9, lens9, cells9, _, _ = ctx.walk_packed(starts[:100], 256, seed=3, lengths_u8=True)     # lengths up to 255
+    p9, l9 = oracle.walk(g.xadj, g.adjncy, g.adjwgt, table, starts[:100], 256, seed=3)
+    assert np.array_equal(lens9, l9) and np.array_equal(out9[:cells9], np.concatenate([p9[w, :l9[w] + 1] for w in range(100)]))
+    with pytest.raises(SkwError):                                                            # 256 does not fit a byte
+        ctx.walk_packed(starts[:100], 257, seed=3, lengths_u8=True)
 
 
 def test_online_direct_slots_every_degree_class(ctx, oracle):
@@ -711,6 +723,9 @@ def test_packed_result_sliced_pipeline(ctx, oracle, rmat16):
         assert cells == len(want) and edges == int(olens.sum()) and ms > 0
         assert np.array_equal(lens, olens)
         assert np.array_equal(out[:cells], want)
+        out8, lens8, cells8, _, _ = ctx.walk_packed(starts, 21, app=APP_PPR, tp=0.3, seed=8, walker_base=11,
+                                                    lengths_u8=True)           # byte lengths, slice by slice
+        assert cells8 == cells and np.array_equal(lens8, olens) and np.array_equal(out8[:cells], want)
         # too small by one cell: the overflow shows up in the last slice; lengths and size still come back
         small = np.zeros(cells - 1, np.uint32)
         lens2 = np.zeros(n, np.uint32)
