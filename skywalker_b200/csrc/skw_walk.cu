@@ -980,7 +980,22 @@ static int walk_packed_impl(skw_ctx* ctx, const skw_walk_params* prm, const uint
   const uint64_t kSliceMin = 1u << 19;
   const uint32_t slices = n >= 8 * kSliceMin ? 8 : (n >= 4 * kSliceMin ? 4 : (n >= 2 * kSliceMin ? 2 : 1));
   static_assert(skw_ctx::kPackSlices >= 8 && skw_ctx::kStages >= 4 + 8, "one event set and one packing buffer per slice");
-  const uint64_t per = (n + slices - 1) / slices;
+  // Slice sizes in the ratio 1 : 2 : 4 : 4 ...: the first results are on the bus early (the call is
+  // as long as the time to the first packed slice plus the copy of everything), the later slices are
+  // large enough to walk efficiently.
+  uint64_t base_of[skw_ctx::kPackSlices + 1] = {};
+  uint64_t per = n;  // the largest slice
+  if (slices > 1) {
+    const uint64_t parts = 3 + 4ull * (slices - 2);
+    const uint64_t unit = ((n + parts - 1) / parts + 1023) & ~1023ull;
+    per = (slices == 2 ? 2 : 4) * unit;
+    for (uint32_t c = 0; c <= slices; ++c) {
+      const uint64_t b = c == 0 ? 0 : (c == 1 ? unit : (3 + 4ull * (c - 2)) * unit);
+      base_of[c] = std::min<uint64_t>(b, n);
+    }
+  } else {
+    base_of[1] = n;
+  }
   const uint64_t stride = prm->walker_stride ? prm->walker_stride : 1;
   const size_t offs_bytes = (sizeof(u64) * (size_t)per + 255) & ~(size_t)255;
   size_t tmp_bytes = 0;
@@ -1008,9 +1023,9 @@ static int walk_packed_impl(skw_ctx* ctx, const skw_walk_params* prm, const uint
   // walk at full length, or the expected PPR length with room to spare.
   uint64_t cap[skw_ctx::kPackSlices] = {}, nc_of[skw_ctx::kPackSlices] = {};
   for (uint32_t c = 0; c < slices; ++c) {
-    const uint64_t base = (uint64_t)c * per;
+    const uint64_t base = base_of[c];
     if (base >= n) break;
-    const uint64_t nc = std::min<uint64_t>(per, n - base);
+    const uint64_t nc = base_of[c + 1] - base;
     nc_of[c] = nc;
     const uint64_t full = nc * prm->hop_num;
     uint64_t guess = full;
@@ -1023,7 +1038,7 @@ static int walk_packed_impl(skw_ctx* ctx, const skw_walk_params* prm, const uint
   if ((rc = err_reset(ctx)) != SKW_OK) return rc;
   unsigned long long* scratch_sum = reinterpret_cast<unsigned long long*>(ctx->d_sum) + 2;
   auto scan_and_pack = [&](uint32_t c) -> int {
-    const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+    const uint64_t base = base_of[c], nc = nc_of[c];
     cub::TransformInputIterator<u64, CellsOfRow, const u32*> row_cells(d_len + base, CellsOfRow());
     size_t tb = tmp_bytes;
     SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(reinterpret_cast<char*>(d_offs) + offs_bytes, tb, row_cells, d_offs,
@@ -1047,12 +1062,12 @@ static int walk_packed_impl(skw_ctx* ctx, const skw_walk_params* prm, const uint
     // the start vertices come in slice by slice on the side stream, ahead of everything else it will
     // carry: a walk waits for its own slice only, and no walk waits behind a copy of a later slice
     for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
-      const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+      const uint64_t base = base_of[c], nc = nc_of[c];
       SKW_CUDA(ctx, cudaMemcpyAsync(d_starts + base, h_starts + base, sizeof(u32) * (size_t)nc, cudaMemcpyHostToDevice, side));
       SKW_CUDA(ctx, cudaEventRecord(ctx->pk_in[c], side));
     }
     for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
-      const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+      const uint64_t base = base_of[c], nc = nc_of[c];
       SKW_CUDA(ctx, cudaStreamWaitEvent(st, ctx->pk_in[c], 0));
       skw_walk_params p = *prm;
       p.walker_base = prm->walker_base + base * stride;
