@@ -149,6 +149,47 @@ def test_alias_packed_builders_boundaries(ctx, oracle):
     assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
 
 
+def test_alias_weights_around_the_truncation_threshold(ctx, oracle):
+    """A weight loses bits in the quantisation once it is more than 2^16 below the largest weight of its
+    list (for up to 4096 weights): lists with one weight 2^15, 2^16, 2^17 and 2^24 times the others, with
+    and without the lowest significand bit set, the large weight first, in the middle or everywhere but at
+    the sampled positions; zeros; a largest weight that is barely normal; one near the largest float.  In
+    every class that walks its list in more than one tile."""
+    rng = np.random.default_rng(12)
+    lists = []
+    for n in (300, 1000, 1500, 4000, 6000, 12000, 20000):
+        base = rng.uniform(1, 2, n).astype(np.float32)
+        for ratio_log2 in (15, 16, 17, 24):               # smallest weight 2^-r of the largest
+            w = base.copy()
+            w[0] = 2.0 ** ratio_log2                        # the largest first
+            lists.append(w)
+            w = base.copy()
+            w[n // 3] = np.float32(1.0 + 2.0 ** -23) * 2.0 ** ratio_log2   # lowest significand bit set
+            lists.append(w)
+            w = (base * 2.0 ** ratio_log2).astype(np.float32)
+            w[0] = 1.0                                     # first, middle and last are small, the rest large
+            w[n // 2] = 1.5
+            w[n - 1] = 1.25
+            lists.append(w)
+        w = base.copy()
+        w[5] = 0.0                                         # zeros do not count as small weights
+        w[n - 1] = 0.0
+        lists.append(w)
+        w = base.copy() * np.float32(1e-38)                # the largest weight barely normal, others denormal
+        lists.append(w.astype(np.float32))
+        w = base.copy()
+        w[n // 2] = 3.0e38                                 # near the largest float
+        lists.append(w)
+    xadj, adj, w = _star_graph(lists)
+    ctx.upload(xadj, adj, w)
+    ctx.alias_build_offline()
+    prob, alias, valid = ctx.alias_export()
+    oprob, oalias, ovalid = oracle.alias_build(xadj, w)
+    assert np.array_equal(valid, ovalid)
+    assert np.array_equal(alias, oalias)
+    assert np.array_equal(prob.view(np.uint32), oprob.view(np.uint32))
+
+
 def test_alias_build_partial_range(ctx, oracle, rmat12):
     g = rmat12
     _upload(ctx, g)
