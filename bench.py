@@ -299,7 +299,13 @@ def parity_sample(ctx, wl, host, lo, n_local, d_starts, d_result, d_lengths, mod
         got_l = d_lengths[:K * lens_per].cpu().numpy().view(np.uint32).reshape(K, lens_per)
         want_d, want_l = O.khop(host["xadj"], host["adjncy"], host["wgt"], host["table"], h_starts, wl["fanout"],
                                 online=online, seed=WALK_SEED, instance_base=lo, threads=threads)
-        return K, ok and bool(np.array_equal(got_d, want_d)) and bool(np.array_equal(got_l, want_l))
+        ok = ok and bool(np.array_equal(got_d, want_d)) and bool(np.array_equal(got_l, want_l))
+        # the packed host entry point on the same seeds
+        packed, pl, pcells, _, _ = ctx.sample_khop_packed(h_starts, wl["fanout"], mode=mode, seed=WALK_SEED,
+                                                          instance_base=lo)
+        want_p = want_d[want_d != 0xFFFFFFFF]
+        ok = ok and pcells == len(want_p) and bool(np.array_equal(packed[:pcells], want_p))
+        return K, ok and bool(np.array_equal(pl, want_l))
     kw = dict(app=app_id(wl), tp=wl.get("tp", 0.0), p=wl.get("p", 2.0), q=wl.get("q", 0.5), seed=WALK_SEED,
               walker_base=lo)
     ctx.walk(d_starts, hop, mode=mode, paths=d_result, lengths=d_lengths, n=n_local, **kw)
@@ -613,6 +619,24 @@ def main():
                            "cells 0..length of every path row written into the pinned n x hop_num matrix by a "
                            "kernel, plus the lengths D2H")}
         e2e = rows
+        if khop:
+            # the same trees returned packed: only cells that hold a sample cross the bus
+            flat_r = np_r.reshape(-1)
+
+            def packed_tree_call(i):
+                out = ctx.sample_khop_packed(np_s, wl["fanout"], mode=mode, seed=WALK_SEED + i, instance_base=lo,
+                                             packed=flat_r, sample_lengths=np_l, n=n_local)
+                packed_tree_call.cells = out[2]
+                return out[4]
+            p_ms, p_edges, p_calls = timed_host_calls(packed_tree_call)
+            e2e = {"ms_per_call_this_rank": p_calls, "ms_per_call_median": float(np.median(p_calls)),
+                   "value": p_edges / (p_ms * 1e-3), "unit": "sampled edges/s", "steps": e_steps,
+                   "ms_per_step": p_ms / e_steps, "h2d_bytes_per_step": 4 * n_local,
+                   "d2h_bytes_per_step": int(4 * (packed_tree_call.cells + lengths.numel())),
+                   "note": "host-buffer entry point skw_sample_khop_packed with pinned memory: seed vertices H2D, "
+                           "per-hop kernels, then the cells of the result tree that hold a sample packed back to "
+                           "back on the device and copied slice by slice, plus the per-vertex sample counts",
+                   "dense_tree": rows}
         if not khop:
             # the same walks returned packed (lengths + the walks back to back): only result cells cross
             # the bus, as one contiguous stream instead of one small write per row
@@ -711,7 +735,7 @@ def main():
         parity = {"units": int(t[1].item()), "equal": bool(t[0].item()), "ranks": world,
                   "what": "first K %s of every rank's shard, row layout%s, against the CPU oracle bit for bit"
                           % ("seeds" if khop else "walkers",
-                             "" if khop else " and packed layout (32-bit and byte lengths)")}
+                             " and packed tree" if khop else " and packed layout (32-bit and byte lengths)")}
     config["parity_sample"] = parity
     if sliced is not None:
         config["alias_build_sliced_equals_replicated"] = sliced["equals_replicated_build"]

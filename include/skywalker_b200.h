@@ -312,6 +312,18 @@ int skw_sample_khop_device(skw_ctx* ctx, const skw_khop_params* prm, const uint3
 int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_seeds, uint64_t n,
                     uint32_t* h_data, uint32_t* h_sample_lengths, float* ms,
                     uint64_t* sampled_edges);
+/* Host buffers, packed result.  No counterpart in the reference, which leaves the tree on the device
+ * (include/sampler_result.cuh:334-352).  h_sample_lengths as in skw_sample_khop; h_packed receives,
+ * seed after seed, the cells of the seed's row of `data` that hold a sample, in row order (the seed,
+ * its hop-1 samples, the hop-2 samples of the first of them, of the second ...): the dense tree
+ * without its SKW_INVALID_VERTEX cells, which sample_lengths is enough to rebuild.  *cells = cells
+ * the result needs; when capacity_cells is smaller (or h_packed is NULL) the call fills
+ * h_sample_lengths and *cells, leaves h_packed unspecified (never written past capacity_cells) and
+ * returns SKW_ERR_ARG.  The tree of a power-law graph is sparse (vertices without out-edges have no
+ * children), and the host result is bound by the bus: BASELINE config 4 sends 47 MB instead of 79. */
+int skw_sample_khop_packed(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_seeds, uint64_t n,
+                           uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_sample_lengths,
+                           uint64_t* cells, float* ms, uint64_t* sampled_edges);
 
 /* Measurement aid, no counterpart in the reference: times a dependent chain of random 32-byte loads
  * (the access pattern of a walk step, same load instruction as the record walk) over a scratch

@@ -79,6 +79,9 @@ SIGNATURES = {
                                          C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "skw_sample_khop": (C.c_int, [C.c_void_p, C.POINTER(KhopParams), C.c_void_p, C.c_uint64, C.c_void_p,
                                   C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
+    "skw_sample_khop_packed": (C.c_int, [C.c_void_p, C.POINTER(KhopParams), C.c_void_p, C.c_uint64, C.c_void_p,
+                                         C.c_uint64, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_float),
+                                         C.POINTER(C.c_uint64)]),
     "skw_probe_random_gather": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.POINTER(C.c_double)]),
     "skw_selftest_bounded_wait": (C.c_int, [C.c_void_p]),
     "skw_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),

@@ -295,6 +295,26 @@ class Context:
                     _ptr(sample_lengths) if n else None, C.byref(ms), C.byref(edges)))
         return data, sample_lengths, ms.value, edges.value
 
+    def sample_khop_packed(self, seeds, fanout, mode=MODE_OFFLINE, flags=0, seed=42, instance_base=0, packed=None,
+                           sample_lengths=None, n=None, instance_stride=1):
+        """Host arrays in, packed tree out: returns (packed, sample_lengths[n, lens], cells, ms, sampled_edges);
+        packed[:cells] holds, seed after seed, the cells of the dense tree that are not INVALID_VERTEX."""
+        cells_per, lens = self.khop_layout(fanout)
+        prm = KhopParams(mode, len(fanout), (C.c_uint32 * 4)(*(list(fanout) + [0] * (4 - len(fanout)))),
+                         flags, seed, instance_base, instance_stride)
+        seeds = np.ascontiguousarray(seeds, np.uint32)
+        n = len(seeds) if n is None else n
+        if packed is None:
+            packed = np.empty(max(n * cells_per, 1), np.uint32)
+        if sample_lengths is None:
+            sample_lengths = np.zeros((n, lens), np.uint32)
+        cap = int(packed.numel()) if hasattr(packed, "numel") else int(packed.size)
+        ms, edges, cells = C.c_float(), C.c_uint64(), C.c_uint64()
+        self._ck(self._lib.skw_sample_khop_packed(self._h, C.byref(prm), _ptr(seeds) if n else None, n, _ptr(packed),
+                                                  cap, _ptr(sample_lengths) if n else None, C.byref(cells),
+                                                  C.byref(ms), C.byref(edges)))
+        return packed, sample_lengths, cells.value, ms.value, edges.value
+
 
 # ---------------------------------------------------------------------------------------------
 # Reference-shaped surface (names and return values of include/sampler.cuh:510-529).

@@ -11,6 +11,9 @@
 // path.  Online mode first builds the tables of the distinct vertices of the hop's frontier with
 // the degree-bucketed builders, then runs the same draw kernel.
 #include <algorithm>
+#include <string>
+
+#include <cub/device/device_scan.cuh>
 
 #include "skw_ctx.h"
 
@@ -220,6 +223,45 @@ static int khop_validate(skw_ctx* ctx, const skw_khop_params* prm) {
   return SKW_OK;
 }
 
+// Packed result tree: the cells of a seed's row that hold a sample, in row order (the seed, its hop-1
+// samples, the hop-2 samples of the first of them, of the second ...), seeds back to back.  One warp
+// per seed: count the cells of the row that are not SKW_INVALID_VERTEX ...
+__global__ void __launch_bounds__(256) khop_count_cells_kernel(const u32* __restrict__ data, u64 n, u32 cells,
+                                                               u64* __restrict__ count) {
+  const u32 lane = threadIdx.x & 31;
+  const u64 nwarps = ((u64)gridDim.x * blockDim.x) >> 5;
+  for (u64 s = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < n; s += nwarps) {
+    const u32* row = data + s * cells;
+    u32 c = 0;
+    for (u32 x = lane; x < cells; x += 32) c += ldg_once(row + x) != SKW_INVALID_VERTEX ? 1u : 0u;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+    if (lane == 0) count[s] = c;
+  }
+}
+
+// ... and, once the counts are prefix-summed into offs, copy them out in order.  Cells that do not
+// fit the capacity are left out; *total tells the host what the batch needs.
+__global__ void __launch_bounds__(256) khop_pack_kernel(const u32* __restrict__ data, u64 n, u32 cells,
+                                                        const u64* __restrict__ offs, u32* __restrict__ packed,
+                                                        u64 capacity, u64* __restrict__ total) {
+  const u32 lane = threadIdx.x & 31, below = (1u << lane) - 1u;
+  const u64 nwarps = ((u64)gridDim.x * blockDim.x) >> 5;
+  for (u64 s = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < n; s += nwarps) {
+    const u32* row = data + s * cells;
+    u64 o = __ldg(offs + s);
+    for (u32 x0 = 0; x0 < cells; x0 += 32) {
+      const u32 x = x0 + lane;
+      const u32 v = x < cells ? ldg_once(row + x) : SKW_INVALID_VERTEX;
+      const u32 have = __ballot_sync(0xFFFFFFFFu, v != SKW_INVALID_VERTEX);
+      const u64 at = o + __popc(have & below);
+      if (v != SKW_INVALID_VERTEX && at < capacity) packed[at] = v;
+      o += __popc(have);
+    }
+    if (s == n - 1 && lane == 0) *total = o;
+  }
+}
+
 // Queue the kernels of one batch of seeds on the context's stream (sampled edges add up in d_sum[0]).
 static int khop_launch(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* d_seeds, uint64_t n,
                        uint32_t* d_data, uint32_t* d_sample_lengths, uint64_t instance_base,
@@ -361,6 +403,138 @@ int skw_sample_khop(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_
   if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
   if (sampled_edges) *sampled_edges = *ctx->h_sum;
   return SKW_OK;
+}
+
+// Host buffers, packed result tree (see khop_pack_kernel): only cells that hold a sample cross the
+// bus.  Slices as in skw_sample_khop; per slice the kernels, the count of each row's samples, their
+// prefix sum and the packing are queued for all slices before the host waits for anything, the size of
+// a slice's packed part comes back through a pinned word and its copy starts as soon as that is known.
+int skw_sample_khop_packed(skw_ctx* ctx, const skw_khop_params* prm, const uint32_t* h_seeds, uint64_t n,
+                           uint32_t* h_packed, uint64_t capacity_cells, uint32_t* h_sample_lengths,
+                           uint64_t* cells_out, float* ms, uint64_t* sampled_edges) {
+  if (!ctx || !prm) return SKW_ERR_ARG;
+  if (!cells_out) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop_packed: cells must not be null");
+  *cells_out = 0;
+  if (ms) *ms = 0;
+  if (sampled_edges) *sampled_edges = 0;
+  uint32_t cells = 0, lens = 0;
+  int rc = skw_khop_layout(prm, &cells, &lens);
+  if (rc != SKW_OK) return fail(ctx, rc, "skw_sample_khop_packed: bad hop description");
+  if (n && (!h_seeds || !h_sample_lengths)) return fail(ctx, SKW_ERR_ARG, "skw_sample_khop_packed: null buffer");
+  if ((rc = khop_validate(ctx, prm)) != SKW_OK) return rc;
+  if (!n) return SKW_OK;
+  DeviceGuard g(ctx->device);
+  cudaStream_t st = ctx->stream, side = ctx->side_stream;
+  const uint32_t slices = n >= (1u << 19) ? 4 : (n >= (1u << 16) ? 2 : 1);
+  const uint64_t per = (n + slices - 1) / slices;
+  const uint64_t stride = prm->instance_stride ? prm->instance_stride : 1;
+  const size_t nb = sizeof(uint32_t) * (size_t)n;
+  const size_t offs_bytes = (sizeof(u64) * (size_t)per * 2 + 255) & ~(size_t)255;  // counts, then offsets
+  size_t tmp_bytes = 0;
+  SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, (const u64*)nullptr, (u64*)nullptr, (long long)per, st));
+  if ((rc = ensure_bytes(ctx, &ctx->stage[0], &ctx->stage_bytes[0], nb)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[1], &ctx->stage_bytes[1], nb * cells)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[2], &ctx->stage_bytes[2], nb * lens)) != SKW_OK) return rc;
+  if ((rc = ensure_bytes(ctx, &ctx->stage[3], &ctx->stage_bytes[3], offs_bytes + tmp_bytes)) != SKW_OK) return rc;
+  uint32_t* d_seeds = static_cast<uint32_t*>(ctx->stage[0]);
+  uint32_t* d_data = static_cast<uint32_t*>(ctx->stage[1]);
+  uint32_t* d_lens = static_cast<uint32_t*>(ctx->stage[2]);
+  u64* d_cnt = static_cast<u64*>(ctx->stage[3]);
+  u64* d_offs = d_cnt + per;
+  void* d_tmp = reinterpret_cast<char*>(ctx->stage[3]) + offs_bytes;
+  // one packing buffer per slice, kept at its high-water size; first guess: every cell of the tree
+  uint64_t cap[4] = {}, nc_of[4] = {};
+  for (uint32_t c = 0; c < slices; ++c) {
+    const uint64_t base = (uint64_t)c * per;
+    if (base >= n) break;
+    nc_of[c] = std::min<uint64_t>(per, n - base);
+    const uint64_t full = nc_of[c] * cells;
+    uint64_t guess = full;
+    if (ctx->stage[4 + c] && ctx->stage_bytes[4 + c] >= sizeof(u32) * 1024) guess = ctx->stage_bytes[4 + c] / sizeof(u32);
+    if ((rc = ensure_bytes(ctx, &ctx->stage[4 + c], &ctx->stage_bytes[4 + c], sizeof(u32) * (size_t)guess)) != SKW_OK) return rc;
+    cap[c] = std::min<uint64_t>(ctx->stage_bytes[4 + c] / sizeof(u32), full);
+  }
+  if ((rc = err_reset(ctx)) != SKW_OK) return rc;
+  const uint64_t grid_cap = (uint64_t)ctx->sm_count * 16;
+  auto count_and_pack = [&](uint32_t c, bool recount) -> int {
+    const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+    const uint64_t want = (nc + 7) / 8;  // one warp per seed
+    const int grid = (int)(want < grid_cap ? want : grid_cap);
+    if (recount) {
+      khop_count_cells_kernel<<<grid, 256, 0, st>>>(d_data + base * cells, nc, cells, d_cnt);
+      SKW_LAUNCHED(ctx);
+      size_t tb = tmp_bytes;
+      SKW_CUDA(ctx, cub::DeviceScan::ExclusiveSum(d_tmp, tb, d_cnt, d_offs, (long long)nc, st));
+      SKW_LAUNCHED(ctx);
+    }
+    khop_pack_kernel<<<grid, 256, 0, st>>>(d_data + base * cells, nc, cells, d_offs,
+                                           static_cast<u32*>(ctx->stage[4 + c]), cap[c], ctx->d_tot + c);
+    SKW_LAUNCHED(ctx);
+    SKW_CUDA(ctx, cudaEventRecord(ctx->pk_ready[c], st));
+    SKW_CUDA(ctx, cudaStreamWaitEvent(side, ctx->pk_ready[c], 0));
+    SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_tot + c, ctx->d_tot + c, sizeof(u64), cudaMemcpyDeviceToHost, side));
+    SKW_CUDA(ctx, cudaEventRecord(ctx->pk_tot[c], side));
+    return SKW_OK;
+  };
+  auto body = [&]() -> int {
+    SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum, 0, sizeof(uint64_t), st));
+    SKW_CUDA(ctx, cudaMemcpyAsync(d_seeds, h_seeds, nb, cudaMemcpyHostToDevice, st));
+    SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+    for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
+      const uint64_t base = (uint64_t)c * per, nc = nc_of[c];
+      int r = khop_launch(ctx, prm, d_seeds + base, nc, d_data + base * cells, d_lens + base * lens,
+                          prm->instance_base + base * stride, c == 0);
+      if (r != SKW_OK) return r;
+      if (c + 1 == slices || !nc_of[c + 1]) SKW_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+      if ((r = count_and_pack(c, true)) != SKW_OK) return r;
+      SKW_CUDA(ctx, cudaMemcpyAsync(h_sample_lengths + base * lens, d_lens + base * lens,
+                                    sizeof(uint32_t) * (size_t)nc * lens, cudaMemcpyDeviceToHost, side));
+    }
+    uint64_t total_cells = 0;
+    bool fits = h_packed != nullptr;
+    for (uint32_t c = 0; c < slices && nc_of[c]; ++c) {
+      SKW_CUDA(ctx, cudaEventSynchronize(ctx->pk_tot[c]));
+      uint64_t slice_cells = ctx->h_tot[c];
+      if (fits && total_cells + slice_cells > capacity_cells) fits = false;  // keep going: the caller gets the size
+      if (fits && slice_cells > cap[c]) {
+        // the slice outgrew its packing buffer: grow it and pack again.  The offsets of this slice are
+        // gone once a later slice was counted, so they are computed again unless it is the last one.
+        int r = ensure_bytes(ctx, &ctx->stage[4 + c], &ctx->stage_bytes[4 + c], sizeof(u32) * (size_t)(nc_of[c] * cells));
+        if (r != SKW_OK) return r;
+        cap[c] = nc_of[c] * cells;
+        if ((r = count_and_pack(c, true)) != SKW_OK) return r;
+        SKW_CUDA(ctx, cudaEventSynchronize(ctx->pk_tot[c]));
+        slice_cells = ctx->h_tot[c];
+      }
+      if (fits) {
+        SKW_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->pk_ready[c], 0));
+        SKW_CUDA(ctx, cudaMemcpyAsync(h_packed + total_cells, ctx->stage[4 + c], sizeof(u32) * (size_t)slice_cells,
+                                      cudaMemcpyDeviceToHost, ctx->copy_stream));
+      }
+      total_cells += slice_cells;
+    }
+    SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum, ctx->d_sum, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
+    SKW_CUDA(ctx, cudaStreamSynchronize(side));
+    SKW_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+    int r = err_check(ctx, "skw_sample_khop_packed");  // synchronises the context's stream
+    if (r != SKW_OK) return r;
+    *cells_out = total_cells;
+    if (ms) SKW_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+    if (sampled_edges) *sampled_edges = *ctx->h_sum;
+    if (!fits)
+      return fail(ctx, SKW_ERR_ARG, "skw_sample_khop_packed: the result needs %llu cells, the buffer holds %llu",
+                  (unsigned long long)total_cells, (unsigned long long)(h_packed ? capacity_cells : 0));
+    return SKW_OK;
+  };
+  rc = body();
+  if (rc != SKW_OK && rc != SKW_ERR_ARG) {  // leave nothing in flight that still writes the caller's buffers
+    const std::string why = ctx->err;
+    cudaStreamSynchronize(side);
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamSynchronize(st);
+    ctx->err = why;
+  }
+  return rc;
 }
 
 }  // extern "C"

@@ -7,8 +7,8 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-from skywalker_b200 import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, KHOP_TAKE_ALL, KHOP_UNBIASED, MODE_OFFLINE,
-                            MODE_ONLINE, WALK_UNBIASED)
+from skywalker_b200 import (APP_DEEPWALK, APP_NODE2VEC, APP_PPR, INVALID_VERTEX, KHOP_DISTINCT, KHOP_TAKE_ALL,
+                            KHOP_UNBIASED, MODE_OFFLINE, MODE_ONLINE, WALK_UNBIASED)
 
 
 def _upload(ctx, g):
@@ -920,6 +920,39 @@ def test_khop_distinct_runs_out_of_trials(ctx, oracle):
     assert (sl[:, 0] >= 1).all() and (sl[:, 0] < 20).any()
     with pytest.raises(Exception):                          # fan-outs above 256 are refused with the flag
         ctx.sample_khop(seeds, [300], flags=KHOP_DISTINCT, seed=4)
+
+
+@pytest.mark.parametrize("n", [3000, (1 << 16) + 1234])               # one slice, two slices
+@pytest.mark.parametrize("mode,flags", [(MODE_OFFLINE, 0), (MODE_ONLINE, 0), (MODE_ONLINE, KHOP_DISTINCT),
+                                        (MODE_OFFLINE, KHOP_TAKE_ALL)])
+def test_khop_packed_host_result(ctx, oracle, rmat16, mode, flags, n):
+    """skw_sample_khop_packed: the cells of the dense tree that hold a sample, seed after seed in row order,
+    plus the per-vertex sample counts; a buffer that is too small gets the counts and the needed size."""
+    from skywalker_b200.api import SkwError
+    g = rmat16
+    _upload(ctx, g)
+    ctx.alias_build_offline()
+    table = oracle.alias_build(g.xadj, g.adjwgt)
+    seeds = oracle.gen_starts(n, g.V, 17)
+    fan = [5, 3]
+    odata, osl = oracle.khop(g.xadj, g.adjncy, g.adjwgt, table, seeds, fan, online=(mode == MODE_ONLINE),
+                             seed=29, instance_base=7, flags=flags)
+    want = odata[odata != INVALID_VERTEX]                  # row-major: seeds back to back, rows in order
+    packed = np.full(len(want) + 5, 0xABCDEF01, np.uint32)
+    out, sl, cells, ms, edges = ctx.sample_khop_packed(seeds, fan, mode=mode, flags=flags, seed=29, instance_base=7,
+                                                       packed=packed)
+    assert cells == len(want) and edges == int(osl.sum())
+    assert np.array_equal(sl, osl)
+    assert np.array_equal(out[:cells], want) and (out[cells:] == 0xABCDEF01).all()
+    small = np.full(cells - 1, 0xABCDEF01, np.uint32)
+    sl2 = np.zeros_like(osl)
+    with pytest.raises(SkwError) as e:
+        ctx.sample_khop_packed(seeds, fan, mode=mode, flags=flags, seed=29, instance_base=7, packed=small,
+                               sample_lengths=sl2)
+    assert str(cells) in str(e.value) and np.array_equal(sl2, osl)
+    # the dense entry point still works on the same context afterwards
+    data, sl3, _, _ = ctx.sample_khop(seeds[:100], fan, mode=mode, flags=flags, seed=29, instance_base=7)
+    assert np.array_equal(data, odata[:100]) and np.array_equal(sl3, osl[:100])
 
 
 @pytest.mark.parametrize("n", [(1 << 16) + 1234, (1 << 19) + 77])     # two slices, four slices
