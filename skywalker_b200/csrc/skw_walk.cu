@@ -446,6 +446,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2048 / (WARPS * 32)) walk_records_
   bool active = false;
   u32 local = 0, off = 0, deg = 0, step = 0;
   u64 edges = 0;
+  Rand4 r{0, 0, 0, 0};  // random words of the walker's current step
   for (;;) {
     const u32 need = __ballot_sync(0xFFFFFFFFu, !active);
     if (need && next < cnt) {
@@ -456,21 +457,21 @@ __global__ void __launch_bounds__(WARPS * 32, 2048 / (WARPS * 32)) walk_records_
         deg = buf[local * kPitch + 2];
         step = 0;
         active = true;
+        r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, 0, 0);
       }
       next = min(cnt, next + (u32)__popc(need));
     }
     if (!__any_sync(0xFFFFFFFFu, active)) break;
     if (active) {
-      bool go = step + 1 < a.hop_num && deg != 0;
-      Rand4 r{0, 0, 0, 0};
-      if (go) {
-        r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, step, 0);
-        if (u01(r.z) < a.tp) go = false;
-      }
+      const bool go = step + 1 < a.hop_num && deg != 0 && !(u01(r.z) < a.tp);
       if (go) {
         u32 rw[8];
         load_record(a.rec + (u64)off + __umulhi(r.x, deg), rw);
-        const bool keep = u01(r.y) < __uint_as_float(rw[0]);
+        // the next step's random words do not depend on the record: computing them here overlaps the
+        // load's latency, which is what the end of a pass is made of
+        const u32 ry = r.y;
+        r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, step + 1, 0);
+        const bool keep = u01(ry) < __uint_as_float(rw[0]);
         ++step;
         const u32 nv = keep ? rw[1] : rw[4];
         if (step < (u32)STAGE) buf[local * kPitch + step] = nv;
