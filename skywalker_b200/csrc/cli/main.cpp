@@ -14,6 +14,7 @@
 // --d is honoured when given explicitly together with --deepwalk / --ppr / --node2vec (the
 // reference overrides it with 100).
 #include <algorithm>
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -237,19 +238,23 @@ int run_device(int dev, Shared& sh, DevResult& out) {
     float ms = 0;
     bool sliced = false;
 #ifdef SKW_HAVE_NCCL
-    // More than one GPU: the slot array is cut into ndev equal chunks of S = ceil(E / ndev) slots;
-    // every GPU builds the vertices that overlap its chunk (a vertex straddling a boundary is built
-    // by both neighbours, with identical bits) and one in-place NCCL all-gather completes every
-    // GPU's table (the reference assembles edge-balanced slices through pinned host memory,
+    // More than one GPU: the slot array is cut into ndev * kPieces equal chunks of S slots; GPU d builds
+    // the vertices that overlap chunks d, ndev + d, 2 ndev + d ... (a vertex straddling a boundary is
+    // built by both neighbours, with identical bits), and piece k -- the ndev neighbouring chunks
+    // k * ndev .. k * ndev + ndev - 1 -- is all-gathered in place over NCCL while the GPUs already build
+    // their chunk of piece k + 1; one all-reduce of the per-vertex flags completes every GPU's table
+    // (the reference assembles edge-balanced slices through pinned host memory,
     // include/sampler.cuh:151-158, include/gpu_graph.cuh:282-291).  --dt=0 (one shared host table)
     // has no meaning here.
     if (sh.ndev > 1 && !sh.comms.empty() && E > 0) {
+      constexpr int kPieces = 4;
+      const int parts = sh.ndev * kPieces;
       std::vector<uint32_t> xadj((size_t)V + 1);
       rc = skw_graph_download(ctx, xadj.data(), nullptr, nullptr);
       if (rc) return fail_dev(out, ctx, rc, "skw_graph_download");  // the others learn of it in agree() below
-      const uint64_t S = (E + sh.ndev - 1) / sh.ndev;
-      std::vector<uint32_t> vb(sh.ndev), ve(sh.ndev);
-      for (int r = 0; r < sh.ndev; ++r) {
+      const uint64_t S = (E + parts - 1) / parts;
+      std::vector<uint32_t> vb(parts), ve(parts);
+      for (int r = 0; r < parts; ++r) {
         const uint64_t lo = std::min<uint64_t>((uint64_t)r * S, E), hi = std::min<uint64_t>((uint64_t)(r + 1) * S, E);
         if (hi > lo) {
           vb[r] = (uint32_t)(std::upper_bound(xadj.begin(), xadj.end(), (uint32_t)lo) - xadj.begin()) - 1;
@@ -259,28 +264,13 @@ int run_device(int dev, Shared& sh, DevResult& out) {
         }
       }
       vb[0] = 0;
-      ve[sh.ndev - 1] = V;
-      for (int r = 0; r + 1 < sh.ndev; ++r) {  // vertices without edges between two chunks
+      ve[parts - 1] = V;
+      for (int r = 0; r + 1 < parts; ++r) {  // vertices without edges between two chunks
         ve[r] = std::max(ve[r], std::min(vb[r + 1], V));
         if (vb[r] > ve[r]) vb[r] = ve[r];
       }
-      rc = skw_alias_build_offline(ctx, vb[dev], ve[dev], &ms);
-      if (!sh.rv.agree(rc == 0)) {
-        if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline (slice)");
-        out.rc = SKW_ERR_STATE;
-        out.err = "another device failed before the table all-gather";
-        return out.rc;
-      }
-      const void* slots_c = nullptr;
-      const uint8_t* valid_c = nullptr;
-      skw_alias_device_ptrs(ctx, &slots_c, &valid_c);
-      uint64_t* slots = (uint64_t*)slots_c;  // 8-byte {prob, alias} slots, 1024 spare entries past E
-      uint8_t* valid = (uint8_t*)valid_c;
       cudaStream_t st;
       cudaStreamCreate(&st);
-      cudaEvent_t e0, e1;
-      cudaEventCreate(&e0);
-      cudaEventCreate(&e1);
       {  // the first collective of a communicator pays its connection set-up: keep that out of the table time
         uint32_t* d_one = nullptr;
         cudaMalloc(&d_one, sizeof(uint32_t));
@@ -289,21 +279,38 @@ int run_device(int dev, Shared& sh, DevResult& out) {
         cudaStreamSynchronize(st);
         cudaFree(d_one);
       }
-      cudaEventRecord(e0, st);
-      ncclGroupStart();
-      ncclAllGather(slots + (size_t)dev * S, slots, S, ncclUint64, sh.comms[dev], st);
-      for (int r = 0; r < sh.ndev; ++r)
-        if (ve[r] > vb[r]) ncclBroadcast(valid + vb[r], valid + vb[r], ve[r] - vb[r], ncclUint8, r, sh.comms[dev], st);
-      ncclGroupEnd();
-      cudaEventRecord(e1, st);
+      const auto t0 = std::chrono::steady_clock::now();
+      float build_ms = 0;
+      uint64_t* slots = nullptr;
+      uint8_t* valid = nullptr;
+      for (int k = 0; k < kPieces; ++k) {
+        const int c = k * sh.ndev + dev;
+        float piece_ms = 0;
+        rc = skw_alias_build_offline(ctx, vb[c], ve[c], &piece_ms);  // returns when the chunk is built
+        build_ms += piece_ms;
+        if (!sh.rv.agree(rc == 0)) {  // nobody enters a collective that another device will not join
+          cudaStreamSynchronize(st);
+          cudaStreamDestroy(st);
+          if (rc) return fail_dev(out, ctx, rc, "skw_alias_build_offline (slice)");
+          out.rc = SKW_ERR_STATE;
+          out.err = "another device failed before the table all-gather";
+          return out.rc;
+        }
+        if (!slots) {
+          const void* slots_c = nullptr;
+          const uint8_t* valid_c = nullptr;
+          skw_alias_device_ptrs(ctx, &slots_c, &valid_c);
+          slots = (uint64_t*)slots_c;  // 8-byte {prob, alias} slots, 1024 spare entries past E
+          valid = (uint8_t*)valid_c;
+        }
+        ncclAllGather(slots + (size_t)c * S, slots + (size_t)k * sh.ndev * S, S, ncclUint64, sh.comms[dev], st);
+      }
+      ncclAllReduce(valid, valid, V, ncclUint8, ncclMax, sh.comms[dev], st);  // set by the builders, zero elsewhere
       cudaStreamSynchronize(st);
-      float gms = 0;
-      cudaEventElapsedTime(&gms, e0, e1);
-      LOGV("device %d: vertices [%u,%u) built in %.2f ms, table all-gathered over NCCL in %.2f ms\n", dev, vb[dev],
-           ve[dev], ms, gms);
-      ms += gms;
-      cudaEventDestroy(e0);
-      cudaEventDestroy(e1);
+      const float wall_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+      LOGV("device %d: %d chunks built in %.2f ms of kernel time, table complete after %.2f ms (pieces all-gathered "
+           "over NCCL beside the builds)\n", dev, kPieces, build_ms, wall_ms);
+      ms = wall_ms;
       cudaStreamDestroy(st);
       sliced = true;
     }
