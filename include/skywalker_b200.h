@@ -224,7 +224,7 @@ typedef struct skw_walk_params {
  * the one slot it draws straight from the weight list of its vertex (one warp per walker, all steps
  * in one launch, no table memory touched) -- the same (prob, alias) bits a built table holds, so
  * the walks are identical.  With neither flag the library computes slots directly (for the duration
- * of a call it memoises, per vertex, the largest weight, the total and prefix sums at every 256th list
+ * of a call it memoises, per vertex, the largest weight, the total and prefix sums at every 64th list
  * position -- never a table entry).  SKW_WALK_CACHE_TABLES implies BUILD_TABLES. */
 #define SKW_WALK_BUILD_TABLES 4u
 #define SKW_WALK_DIRECT_SLOTS 8u

@@ -77,11 +77,12 @@ struct PrepMemo {
   float wmax;
   u64 W;
 };
-constexpr u32 kMemoMinDegree = 512;
+constexpr u32 kMemoMinDegree = 256;
 
 // For lists of kCkMinDegree weights and more the same first visit also leaves CHECKPOINTS of two
 // prefix sums at every kCkChunk-th list position b (measured on config 3: 19.4 / 17.5 / 16.4 ms per pass
-// with chunks of 1024 / 512 / 256 weights): the cumulative quantised weight Q_b and the
+// with chunks of 1024 / 512 / 256 weights and tiles of 128; 11.3 ms with chunks of 128, 8.7 ms with chunks
+// and tiles of 64, 8.4 ms with 32, which needs twice the memory again): the cumulative quantised weight Q_b and the
 // deficit D_b of the smalls before b (the excess of the larges before b follows from them,
 // X_b = D_b + g(Q_b) - b * C).  They are integers and depend on the weights alone, so whoever
 // writes them writes the same values.  A later draw of slot p then sweeps the list from the boundary
@@ -95,7 +96,7 @@ constexpr u32 kMemoMinDegree = 512;
 struct __align__(16) Ckpt {
   u64 Q, D;
 };
-constexpr u32 kCkChunk = 256, kCkMinDegree = 2 * kCkChunk;
+constexpr u32 kCkChunk = 64, kCkMinDegree = 256;
 
 __device__ void record_checkpoints(const float* __restrict__ w, u32 n, u32 lane, const ListPrep& L, Ckpt* ck);
 
@@ -149,8 +150,8 @@ __device__ __forceinline__ bool list_prepare_memo(const float* __restrict__ w, u
   return usable;
 }
 
-constexpr u32 kDirectEpt = 4, kDirectTile = 32 * kDirectEpt;
-// masses of elements base + lane * 4 + k of the list (0 beyond its end); carryQ = quantised weight
+constexpr u32 kDirectEpt = 2, kDirectTile = 32 * kDirectEpt;
+// masses of elements base + lane * kDirectEpt + k of the list (0 beyond its end); carryQ = quantised weight
 // before `base`, advanced to the end of the tile
 __device__ __forceinline__ void tile_masses(const float* __restrict__ w, u32 n, u32 base, u32 lane,
                                             const ListPrep& L, u64& carryQ, u64 (&m)[kDirectEpt]) {
