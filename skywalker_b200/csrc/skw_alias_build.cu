@@ -1351,7 +1351,9 @@ __global__ void __launch_bounds__(256) frontier_collect_kernel(
           dev_fail(err, DEV_ERR_INDEX, v, (u32)u, 10);
         } else {
           const u32 deg = xadj[v + 1] - xadj[v];
-          if (deg && atomicExch(&stamp[v], round) != round) c = degree_class(deg);
+          // a hub stands in thousands of cells of one frontier: look before claiming, so that only the
+          // first few of them queue up at its stamp word with an atomic
+          if (deg && __ldcg(stamp + v) != round && atomicExch(&stamp[v], round) != round) c = degree_class(deg);
         }
       }
     }
