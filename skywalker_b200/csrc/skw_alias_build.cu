@@ -162,6 +162,10 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, u32 by
 }
 // Poll (without blocking) for the phase with the given parity, at most `limit` times with a short
 // sleep in between: a few milliseconds in total.  Returns false if the copy did not complete.
+// One arrival without bytes to wait for (a phase that no bulk copy feeds).
+__device__ __forceinline__ void mbar_arrive(u64* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 limit) {
   for (u32 i = 0; i < limit; ++i) {
     u32 done;
@@ -392,11 +396,23 @@ __device__ __forceinline__ void merge_window(u32 t, u32 nl, u32 Sl, const u64* s
 
 // WIN == 0: the lists A / P are in shared memory and are merged in place.  WIN > 0: they are in
 // global scratch and win_smem holds WIN * 12 + (NT + 1) * 4 bytes of shared memory for staging.
+// BULK: the tiles of the weight list come through `pipe` (see TilePipe) instead of global loads.
 // STAGED: w points at a copy of the weight list in shared memory, else at the list in global memory.
-template <int NT, int EPT, int WIN, bool STAGED>
+// Weight tiles of the scratch class brought into shared memory by the bulk-copy engine, one tile
+// ahead of the one being worked on: two buffers of tile + 8 floats and one mbarrier each.  The parity
+// of each barrier's current phase lives in `parity` (bit b for buffer b) across the vertices of a CTA.
+struct TilePipe {
+  float* buf;   // 2 x (tile + 8) floats, 16-byte aligned
+  u64* bars;    // 2 mbarriers, initialised with one arrival
+  u32 parity;
+  bool failed;  // a copy did not report completion in time: the CTA stops taking vertices
+};
+
+template <int NT, int EPT, int WIN, bool STAGED, bool BULK = false>
 __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
                                    Slot* __restrict__ slots, uint8_t* __restrict__ valid, u64* A,
-                                   u32* P, u64* s_tmp, unsigned char* win_smem, u32* err) {
+                                   u32* P, u64* s_tmp, unsigned char* win_smem, u32* err,
+                                   TilePipe* pipe = nullptr) {
   auto weight = [&](u32 p) { return sane_weight(STAGED ? w[p] : __ldg(w + p)); };
   float wmax = 0.0f;
   for (u32 p = t; p < n; p += NT) wmax = fmaxf(wmax, weight(p));
@@ -424,16 +440,62 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
   // cumulative mass: sum over k <= p of (M_k - C) = X(p) - D(p), so X(p) = D(p) + g(Q_(p+1)) - (p + 1) * C.
   u64 cQ = 0, cD = 0;  // carries between tiles (the same value in every thread)
   u32 cL = 0;
+  constexpr u32 kTile = NT * EPT;
+  // BULK: element i of a tile sits at buffer[head + i]; the list starts `head` floats after a 16-byte
+  // boundary and tiles are whole multiples of 16 bytes, so every tile has the same head.  The copy
+  // engine brings the 16-byte groups that lie inside the tile, up to three floats at either end come
+  // with plain loads.
+  const u32 head = BULK ? (u32)((reinterpret_cast<uintptr_t>(w) & 15u) >> 2) : 0u;
+  auto stage_tile = [&](u32 base, u32 b) {
+    if constexpr (BULK) {
+      const u32 tile_n = min(kTile, n - base);
+      const float* src = w + base;
+      float* dst = pipe->buf + b * (kTile + 8);
+      const u32 skip = head ? 4u : 0u;                 // floats from the aligned start to the first boundary inside
+      const u32 body = (head + tile_n) & ~3u;          // ... and to the last boundary inside
+      const u32 lead = head ? min(4u - head, tile_n) : 0u;
+      if (t < lead) dst[head + t] = __ldg(src + t);
+      if (body > skip) {
+        if (t == 0) bulk_copy_g2s(dst + skip, src - head + skip, (body - skip) * 4u, pipe->bars + b);
+        const u32 tail = head + tile_n - body;         // elements after the last boundary
+        if (t < tail) dst[body + t] = __ldg(src + (body - head) + t);
+      } else {
+        for (u32 i = lead + t; i < tile_n; i += NT) dst[head + i] = __ldg(src + i);
+        if (t == 0) mbar_arrive(pipe->bars + b);       // the phase still has to complete
+      }
+    }
+  };
+  if constexpr (BULK) stage_tile(0, 0);
   for (u32 base = 0; base < n; base += NT * EPT) {
     // a ragged last tile spreads its elements over all threads (ept each) instead of filling the first ones
     const u32 ept = min((u32)EPT, (n - base + NT - 1) / NT);
     const u32 p0 = base + t * ept;
+    const float* tw = nullptr;  // BULK: this tile's weights in shared memory, tw[i] = weight base + i
+    if constexpr (BULK) {
+      const u32 b = (base / kTile) & 1u;
+      // the other buffer was last read in the tile before this one, which ended with a barrier
+      if (base + kTile < n) stage_tile(base + kTile, b ^ 1u);
+      const bool ok = mbar_wait(pipe->bars + b, (pipe->parity >> b) & 1u, 1u << 16);
+      // the same outcome in every thread (and the barrier that publishes the plain stores)
+      if (!__syncthreads_and(ok ? 1 : 0)) {
+        // record it, give the copies in flight one more bounded chance to land so that nothing still
+        // writes this CTA's shared memory when it leaves, and stop
+        if (t == 0) dev_fail(err, DEV_ERR_WAIT, v, base, 13);
+        if (!ok) mbar_wait(pipe->bars + b, (pipe->parity >> b) & 1u, 1u << 16);
+        if (base + kTile < n) mbar_wait(pipe->bars + (b ^ 1u), (pipe->parity >> (b ^ 1u)) & 1u, 1u << 16);
+        pipe->failed = true;
+        return;
+      }
+      pipe->parity ^= 1u << b;
+      tw = pipe->buf + b * (kTile + 8) + head;
+    }
     u64 m[EPT];
     u64 Qex = 0;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
       m[k] = 0;
-      if ((u32)k < ept && p0 + k < n) m[k] = quantise_bits(weight(p0 + k), sh);
+      if ((u32)k < ept && p0 + k < n)
+        m[k] = quantise_bits(BULK ? sane_weight(tw[p0 + k - base]) : weight(p0 + k), sh);
       Qex += m[k];
     }
     u64 tq;
@@ -932,6 +994,11 @@ __global__ void __launch_bounds__(NT) build_cta_packed_kernel(const u32* __restr
   }
 }
 
+// Dynamic shared memory of the scratch class: the merge windows (WIN keys and positions, NT + 1
+// window boundaries), rounded up to 16 bytes, then two weight tiles of NT * 8 + 8 floats.
+__host__ __device__ constexpr int win_smem_bytes(int nt, int win) { return (win * 12 + (nt + 1) * 4 + 15) & ~15; }
+__host__ __device__ constexpr int tile_pipe_bytes(int nt) { return 2 * (nt * 8 + 8) * 4; }
+
 // One CTA of NT threads per vertex of degree <= cap.  WIN == 0: lists in dynamic shared memory.
 // WIN > 0: lists in this CTA's slab of global scratch (cap entries of 12 bytes), merged through
 // windows of WIN outputs staged in dynamic shared memory.
@@ -946,11 +1013,19 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
                                                              u64 cap, u32* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ u64 s_tmp[2 * (NT / 32 + 1)];
+  __shared__ __align__(8) u64 s_bars[2];
   unsigned char* store = WIN ? scratch + (u64)blockIdx.x * cap * 12ull : smem;
   u64* A = reinterpret_cast<u64*>(store);
   u32* P = reinterpret_cast<u32*>(A + cap);
   const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
   __shared__ u32 s_it;
+  // WIN > 0: behind the merge windows, two buffers for the weight tiles the bulk-copy engine brings in
+  TilePipe pipe{reinterpret_cast<float*>(smem + win_smem_bytes(NT, WIN)), s_bars, 0u, false};
+  if (WIN && threadIdx.x == 0) {
+    mbar_init(&s_bars[0], 1);
+    mbar_init(&s_bars[1], 1);
+  }
+  __syncthreads();
   for (;;) {  // next vertex from the class's atomic cursor (degrees, hence costs, vary widely)
     if (threadIdx.x == 0) s_it = atomicAdd(cls + 3 * K_CLASSES + k, 1u);
     __syncthreads();
@@ -963,7 +1038,9 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
       if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)cap);
       continue;
     }
-    build_vertex_merge<NT, 8, WIN, false>(threadIdx.x, v, off, n, wgt + off, slots, valid, A, P, s_tmp, smem, err);
+    build_vertex_merge<NT, 8, WIN, false, (WIN > 0)>(threadIdx.x, v, off, n, wgt + off, slots, valid, A, P, s_tmp,
+                                                      smem, err, &pipe);
+    if (pipe.failed) break;  // the same in every thread
     __syncthreads();
   }
 }
@@ -1223,7 +1300,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   constexpr int kCtaStagedSmem = kLargeMax * 8 + (kLargeMax + 8) * 4;
   constexpr int kW1KSmem = 8 * kWarpMax * 8;
   constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
-  constexpr int kWinSmem = kWin * 12 + (1024 + 1) * 4;
+  constexpr int kWinSmem = win_smem_bytes(1024, kWin) + tile_pipe_bytes(1024);
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
     SKW_CUDA(ctx, cudaFuncSetAttribute(build_cta_merge_kernel<1024, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWinSmem));
