@@ -160,12 +160,12 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, u32 by
                "l"(src), "r"(bytes), "r"(smem_addr(bar))
                : "memory");
 }
-// Poll (without blocking) for the phase with the given parity, at most `limit` times with a short
-// sleep in between: a few milliseconds in total.  Returns false if the copy did not complete.
 // One arrival without bytes to wait for (a phase that no bulk copy feeds).
 __device__ __forceinline__ void mbar_arrive(u64* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// Poll (without blocking) for the phase with the given parity, at most `limit` times with a short
+// sleep in between: a few milliseconds in total.  Returns false if the copy did not complete.
 __device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 limit) {
   for (u32 i = 0; i < limit; ++i) {
     u32 done;
