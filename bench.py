@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the alias-method sampling / random-walk path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c2|c1|c3|c4|dw26|c5s]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c2|c1|c3|c4|c4off|dw26|dw22|c5s]
                     [--impl ours|reference]
 
 One "step" is one pass of the hot path over one batch: all walkers of the workload (walks) or one
@@ -41,6 +41,11 @@ WORKLOADS = {
                fanout=[25, 10],
                desc="benchmark configuration 4: online biased 2-hop sampling, fan-out 25 then 10 with replacement, "
                     "R-MAT-like directed graph 4.85M vertices / ~69M edges, batches of 65,536 random seeds"),
+    "c4off": dict(graph="rmat", scale=23, V=4850000, raw_edges=72000000, kind="khop", mode="offline", units=65536,
+                  fanout=[25, 10], khop_flags=1,
+                  desc="offline biased 2-hop sampling by the rule of the reference's offline sampler (fan-out 25 then "
+                       "10 with replacement, every neighbour once where a vertex has no more than the fan-out), graph "
+                       "and seeds of benchmark configuration 4; the reference's own kernel runs beside it"),
     "c5": dict(graph="rmat", scale=26, edge_factor=28, kind="walk", mode="offline", units=8000000, length=100,
                app="ppr", tp=0.15,
                desc="benchmark configuration 5: biased offline PPR tp=0.15 max length 100, R-MAT scale 26 "
@@ -219,7 +224,8 @@ def cpu_leg(host, wl, threads, want_seconds=12.0, steps=1, warmup=0, build_weigh
 
     def run(n):
         if wl["kind"] == "khop":
-            _, sl = O.khop(xadj, adjncy, wgt, table, starts[:n], wl["fanout"], online=online, seed=WALK_SEED,
+            _, sl = O.khop(xadj, adjncy, wgt, table, starts[:n], wl["fanout"], online=online,
+                           flags=wl.get("khop_flags", 0), seed=WALK_SEED,
                            threads=threads)
             return int(sl.sum())
         _, l = O.walk(xadj, adjncy, wgt, table, starts[:n], wl["length"] + 1, app=app_id(wl), online=online,
@@ -257,9 +263,28 @@ def reference_cuda_leg(host, wl, hop, device):
     if not R.available():
         return {"unavailable": "oracle/_ref/libskw_ref.so was not built (no reference tree on the build machine)"}
     V, E = len(host["xadj"]) - 1, int(host["xadj"][-1])
+    if (wl["kind"] == "khop" and wl["mode"] == "offline" and len(wl["fanout"]) == 2 and wl.get("khop_flags", 0) == 1
+            and E <= (1 << 28)):
+        # the reference's own offline 2-hop sampler (sample_kernel through OfflineSample) on the same seeds
+        n, (f1, f2) = wl["units"], wl["fanout"]
+        seeds = O.gen_starts(n, V, START_SEED)
+        data, sl, sec, edges = R.offline_sample(host["xadj"], host["adjncy"], host["table"], seeds, f1, f2,
+                                                device=device, repeats=3)
+        deg = np.diff(host["xadj"].astype(np.int64))
+        have = np.arange(f1)[None, :] < sl[:, :1]
+        parents = data[:, 1:1 + f1][have].astype(np.int64)
+        due = deg[parents] > 0
+        dropped = int((due & (sl[:, 1:][have] == 0)).sum())
+        return {"kernel": "sample_kernel via OfflineSample (src/offline_sample.cu:72-141, 443-513)",
+                "value": edges / sec, "unit": "sampled edges/s", "seconds": sec, "sampled_edges": int(edges),
+                "seeds": n, "hop2_jobs_dropped": dropped, "hop2_jobs_due": int(due.sum()),
+                "note": "best of 3 runs, the reference's own wall-clock timer around its launch and its own count of "
+                        "sampled edges; table built by this library.  The reference's kernel publishes a slot of its "
+                        "hop-2 job queue before writing it and drops jobs it reads too early (hop2_jobs_dropped of "
+                        "hop2_jobs_due), so it samples somewhat fewer edges than the rule asks for"}
     if wl["kind"] != "walk" or wl["mode"] != "offline" or wl.get("app") != "deepwalk" or E > (1 << 28):
-        return {"unavailable": "the reference's static offline kernel covers offline DeepWalk only (no stop rule, no "
-                               "node2vec); run --workload c1, c2 or dw22"}
+        return {"unavailable": "the reference's static offline kernels cover offline DeepWalk (no stop rule, no "
+                               "node2vec) and offline 2-hop sampling; run --workload c1, c2, dw22 or c4off"}
     n = wl["units"]
     starts = O.gen_starts(n, V, START_SEED)
     paths, lens, sec = R.offline_walk(host["xadj"], host["adjncy"], host["table"], starts, hop, device=device, repeats=3)
@@ -292,16 +317,19 @@ def parity_sample(ctx, wl, host, lo, n_local, d_starts, d_result, d_lengths, mod
     h_starts = O.gen_starts(K, V, START_SEED, id_base=lo)
     ok = bool(np.array_equal(d_starts[:K].cpu().numpy().view(np.uint32), h_starts))
     if khop:
-        ctx.sample_khop(d_starts, wl["fanout"], mode=mode, seed=WALK_SEED, instance_base=lo, data=d_result,
+        ctx.sample_khop(d_starts, wl["fanout"], mode=mode, flags=wl.get("khop_flags", 0), seed=WALK_SEED,
+                        instance_base=lo, data=d_result,
                         sample_lengths=d_lengths, n=n_local)
         cells, lens_per = ctx.khop_layout(wl["fanout"])
         got_d = d_result[:K * cells].cpu().numpy().view(np.uint32).reshape(K, cells)
         got_l = d_lengths[:K * lens_per].cpu().numpy().view(np.uint32).reshape(K, lens_per)
         want_d, want_l = O.khop(host["xadj"], host["adjncy"], host["wgt"], host["table"], h_starts, wl["fanout"],
-                                online=online, seed=WALK_SEED, instance_base=lo, threads=threads)
+                                online=online, flags=wl.get("khop_flags", 0), seed=WALK_SEED, instance_base=lo,
+                                threads=threads)
         ok = ok and bool(np.array_equal(got_d, want_d)) and bool(np.array_equal(got_l, want_l))
         # the packed host entry point on the same seeds
-        packed, pl, pcells, _, _ = ctx.sample_khop_packed(h_starts, wl["fanout"], mode=mode, seed=WALK_SEED,
+        packed, pl, pcells, _, _ = ctx.sample_khop_packed(h_starts, wl["fanout"], mode=mode,
+                                                          flags=wl.get("khop_flags", 0), seed=WALK_SEED,
                                                           instance_base=lo)
         want_p = want_d[want_d != 0xFFFFFFFF]
         ok = ok and pcells == len(want_p) and bool(np.array_equal(packed[:pcells], want_p))
@@ -505,7 +533,8 @@ def main():
         if khop:
             if s is starts:
                 ctx.generate_starts(n_local, START_SEED + i, starts, id_base=lo)
-            return ctx.sample_khop(s, wl["fanout"], mode=mode, seed=WALK_SEED + i, instance_base=lo, data=r,
+            return ctx.sample_khop(s, wl["fanout"], mode=mode, flags=wl.get("khop_flags", 0), seed=WALK_SEED + i,
+                                   instance_base=lo, data=r,
                                    sample_lengths=l, n=n_local)
         return ctx.walk(s, hop, app=app_id(wl), mode=mode, tp=wl.get("tp", 0.0), p=wl.get("p", 2.0),
                         q=wl.get("q", 0.5), seed=WALK_SEED + i, walker_base=lo, paths=r, lengths=l, n=n_local,
@@ -634,8 +663,9 @@ def main():
             flat_r = np_r.reshape(-1)
 
             def packed_tree_call(i):
-                out = ctx.sample_khop_packed(np_s, wl["fanout"], mode=mode, seed=WALK_SEED + i, instance_base=lo,
-                                             packed=flat_r, sample_lengths=np_l, n=n_local)
+                out = ctx.sample_khop_packed(np_s, wl["fanout"], mode=mode, flags=wl.get("khop_flags", 0),
+                                             seed=WALK_SEED + i, instance_base=lo, packed=flat_r,
+                                             sample_lengths=np_l, n=n_local)
                 packed_tree_call.cells = out[2]
                 return out[4]
             p_ms, p_edges, p_calls = timed_host_calls(packed_tree_call)

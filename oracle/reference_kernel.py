@@ -46,6 +46,10 @@ def lib():
         L.skwref_offline_walk.argtypes = [C.c_int, C.c_uint32, C.c_uint64, u32p, u32p, f32p, u32p, u8p, u32p,
                                           C.c_uint32, C.c_uint32, C.c_int, u32p, u32p, C.POINTER(C.c_double)]
         L.skwref_offline_walk.restype = C.c_int
+        L.skwref_offline_sample.argtypes = [C.c_int, C.c_uint32, C.c_uint64, u32p, u32p, f32p, u32p, u8p, u32p,
+                                            C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_int, u32p, u32p,
+                                            C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]
+        L.skwref_offline_sample.restype = C.c_int
         _LIB = L
     return _LIB
 
@@ -69,3 +73,30 @@ def offline_walk(xadj, adjncy, table, starts, hop_num, device=0, repeats=1):
         raise RuntimeError("reference offline walk failed with code %d (-1 argument check, -2 CUDA call, "
                            "-3 kernel)" % rc)
     return paths, lengths, sec.value
+
+
+def offline_sample(xadj, adjncy, table, seeds, f1, f2, device=0, repeats=1, blocks_per_sm=0):
+    """Run the reference's offline 2-hop sampler (OfflineSample -> sample_kernel, fan-outs f1 then f2)
+    over `seeds` with the given alias table.  Returns (data[n, 1 + f1 + f1 * f2], sample_lengths[n, 1 + f1],
+    seconds, sampled_edges): the reference's Jobs_result<NS> arrays, its own best wall time of `repeats`
+    runs and its own count of sampled edges.  A vertex with fewer than f neighbours hands over all of them
+    (src/offline_sample.cu:120-128); cells without a sample keep the reference's initial value.
+    blocks_per_sm: the reference's --m (thread blocks per SM, 4 when 0).  The reference's kernel drops
+    hop-2 jobs that it reads from its queue before they are written, so hop-2 counts can be 0 under a
+    sampled vertex that has neighbours; hop 1 is complete."""
+    prob, alias, valid = table
+    xadj = np.ascontiguousarray(xadj, np.uint32)
+    adjncy = np.ascontiguousarray(adjncy, np.uint32)
+    seeds = np.ascontiguousarray(seeds, np.uint32)
+    n, V, E = len(seeds), len(xadj) - 1, len(adjncy)
+    data = np.zeros((n, 1 + f1 + f1 * f2), np.uint32)
+    sl = np.zeros((n, 1 + f1), np.uint32)
+    sec, edges = C.c_double(), C.c_ulonglong()
+    rc = lib().skwref_offline_sample(device, V, E, xadj, adjncy, np.ascontiguousarray(prob, np.float32),
+                                     np.ascontiguousarray(alias, np.uint32), np.ascontiguousarray(valid, np.uint8),
+                                     seeds, n, f1, f2, blocks_per_sm, repeats, data.reshape(-1), sl.reshape(-1), C.byref(sec),
+                                     C.byref(edges))
+    if rc:
+        raise RuntimeError("reference offline sample failed with code %d (-1 argument check, -2 CUDA call, "
+                           "-3 kernel, -4 layout)" % rc)
+    return data, sl, sec.value, edges.value

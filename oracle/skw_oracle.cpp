@@ -14,11 +14,12 @@
 //     (exact mass conservation in integers, reconstruction of w_i / sum(w) to 1e-6) and against
 //     the hand-checkable vectors the reference's smoke programs use (test/tmp.cu:31-42);
 //   * the draw / walk / k-hop rules against the reference kernels they restate, cited below;
-//   * statistically, against the reference's OWN offline walk kernel run on the GPU
-//     (oracle/ref_cuda builds OfflineWalk / sample_kernel_static from the reference sources):
-//     fed with tables of this construction its transitions follow the edge weights, and its
-//     walks have the same length and visit statistics as the walks defined here
-//     (tests/test_reference_kernel.py).
+//   * statistically, against the reference's OWN offline walk kernel and offline 2-hop sampler
+//     run on the GPU (oracle/ref_cuda builds OfflineWalk / sample_kernel_static and
+//     OfflineSample / sample_kernel from the reference sources): fed with tables of this
+//     construction their draws follow the edge weights, the walks have the same length and visit
+//     statistics as the walks defined here, and the hop-1 sample counts and sampled vertices of
+//     the sampler match the take-all rule defined here (tests/test_reference_kernel.py).
 //
 // Each function cites the reference code it follows (paths inside the reference tree).
 // Everything here is deliberately sequential and naive: it is the definition the GPU kernels

@@ -1,5 +1,6 @@
 """The reference's own offline walk kernel (sample_kernel_static, src/offline_walk.cu:75-124 of
-wpybtw/Skywalker, driven through its OfflineWalk entry function) beside this library.
+wpybtw/Skywalker, driven through its OfflineWalk entry function) and its own offline 2-hop sampler
+(sample_kernel, src/offline_sample.cu:72-141, through OfflineSample) beside this library.
 
 The reference has no golden vectors and its random stream (XORWOW seeded by thread id) cannot be
 reproduced, so the comparison is statistical: fed with the alias table THIS library builds (exported
@@ -101,3 +102,87 @@ def test_reference_walks_and_ours_have_the_same_statistics(ctx, oracle, ref, rma
     tb = np.append(vb[top], vb.sum() - vb[top].sum())
     _, p_vis, _, _ = stats.chi2_contingency(np.vstack([ta, tb]))
     assert p_vis > 0.01, p_vis
+
+
+def test_reference_sampler_follows_the_weights_of_our_table(ctx, ref):
+    """The reference's offline sampler draws f1 = 25 neighbours with replacement from a vertex of more
+    than 25 neighbours through the alias table it is handed (src/offline_sample.cu:103-118): from the
+    centre of a star, with the table this library built, its hop-1 samples must follow the edge weights
+    (chi-square).  One thread block per SM and 400,000 instances of the same seed, so that a thread
+    draws for about ten of them: with the reference's default launch (four blocks per SM, one XORWOW
+    generator per thread seeded with the thread id) 120,000 instances meant fewer than one per thread, i.e.
+    only the first outputs of neighbouring seeds, and failed with p = 2e-17 -- the same property of that
+    seeding as in the walk test above."""
+    from scipy import stats
+    rng = np.random.default_rng(8)
+    for n in (33, 300):
+        w = rng.uniform(1, 10, n).astype(np.float32)
+        xadj = np.asarray([0, n] + [n] * n, np.uint32)         # leaves have no out-edges
+        adj = np.arange(1, n + 1, dtype=np.uint32)
+        ctx.upload(xadj, adj, w)
+        ctx.alias_build_offline()
+        table = ctx.alias_export()
+        N, f1, f2 = 400000, 25, 2
+        data, sl, sec, edges = ref.offline_sample(xadj, adj, table, np.zeros(N, np.uint32), f1, f2, blocks_per_sm=1)
+        assert sec > 0 and (data[:, 0] == 0).all()
+        assert (sl[:, 0] == f1).all() and (sl[:, 1:] == 0).all() and edges == N * f1
+        leaves = data[:, 1:1 + f1].astype(np.int64).reshape(-1) - 1
+        assert leaves.min() >= 0 and leaves.max() < n
+        wf = w.astype(np.float64)
+        chi, pval = stats.chisquare(np.bincount(leaves, minlength=n), f_exp=wf / wf.sum() * len(leaves))
+        assert pval > 0.001, (n, pval)
+
+
+def test_reference_samples_and_ours_have_the_same_statistics(ctx, oracle, ref, rmat12):
+    """Same graph, same table, same 100,000 seeds, fan-outs 5 then 3: the reference hands over every
+    neighbour of a vertex that has no more than the fan-out and draws with replacement otherwise, which is
+    this library's SKW_KHOP_TAKE_ALL rule, so the hop-1 sample counts must be equal cell by cell, every
+    sample must be a neighbour of its parent, and the distribution of the sampled vertices must agree
+    (two-sample chi-square).  Hop 2 of the reference is incomplete by construction: its kernel fills the
+    queue of hop-2 jobs while other thread blocks already drain it, publishes a queue slot before writing
+    it (include/frontier.cuh:236-246) and drops what it reads too early; where it did sample, the count
+    and the samples must be right."""
+    from scipy import stats
+    from skywalker_b200 import KHOP_TAKE_ALL
+    g = rmat12
+    ctx.upload(g.xadj, g.adjncy, g.adjwgt)
+    ctx.alias_build_offline()
+    table = ctx.alias_export()
+    N, f1, f2 = 100000, 5, 3
+    seeds = oracle.gen_starts(N, g.V, 55)
+    rdata, rsl, sec, redges = ref.offline_sample(g.xadj, g.adjncy, table, seeds, f1, f2)
+    odata, osl, _, oedges = ctx.sample_khop(seeds, [f1, f2], flags=KHOP_TAKE_ALL, seed=6)
+    assert sec > 0 and (rdata[:, 0] == seeds).all()
+    deg = np.diff(g.xadj.astype(np.int64))
+    assert np.array_equal(rsl[:, 0], np.minimum(deg[seeds], f1)) and np.array_equal(osl[:, 0], rsl[:, 0])
+    # hop 1: every sample is a neighbour of its seed
+    for i in range(2000):
+        k = rsl[i, 0]
+        nb = g.adjncy[g.xadj[seeds[i]]:g.xadj[seeds[i] + 1]]
+        assert np.isin(rdata[i, 1:1 + k], nb).all()
+    # hop 2: under a hop-1 sample either nothing (a dropped job, or a vertex without neighbours) or
+    # min(its degree, f2) samples, each of them its neighbour
+    done = expected = 0
+    for i in range(2000):
+        for j in range(rsl[i, 0]):
+            p = int(rdata[i, 1 + j])
+            k = int(rsl[i, 1 + j])
+            expected += deg[p] > 0
+            if k:
+                done += 1
+                assert k == min(deg[p], f2)
+                kids = rdata[i, 1 + f1 + j * f2:1 + f1 + j * f2 + k]
+                assert np.isin(kids, g.adjncy[g.xadj[p]:g.xadj[p + 1]]).all()
+    assert 0 < done <= expected
+    assert redges == int(rsl.sum()) and redges <= oedges
+    # sampled vertices of hop 1 where a draw happens (degree above the fan-out): 40 most frequent + the rest
+    drawn = deg[seeds] > f1
+    ra = np.bincount(rdata[drawn, 1:1 + f1].astype(np.int64).reshape(-1), minlength=g.V)
+    oa = np.bincount(odata[drawn, 1:1 + f1].astype(np.int64).reshape(-1), minlength=g.V)
+    top = np.argsort(-(ra + oa))[:40]
+    ta = np.append(ra[top], ra.sum() - ra[top].sum())
+    tb = np.append(oa[top], oa.sum() - oa[top].sum())
+    _, p_vis, _, _ = stats.chi2_contingency(np.vstack([ta, tb]))
+    assert p_vis > 0.001, p_vis
+    print("reference hop 2: %d of %d jobs of the first 2000 seeds sampled; sampled edges %d (ours %d)"
+          % (done, expected, redges, oedges))
