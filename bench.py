@@ -253,7 +253,7 @@ def cpu_leg(host, wl, threads, want_seconds=12.0, steps=1, warmup=0, build_weigh
             "alias_build_edges_per_s": build_eps, "seconds": t_run, "edges": edges}
 
 
-def reference_cuda_leg(host, wl, hop, device):
+def reference_cuda_leg(host, wl, hop, device, ctx=None, d_buffers=None, records=False):
     """The reference's OWN offline walk kernel (sample_kernel_static through OfflineWalk) on this
     workload's graph, start vertices and GPU-built table: throughput by the reference's own timer.  Only
     for offline DeepWalk on graphs small enough to hand over through host arrays; its walks come from
@@ -282,9 +282,35 @@ def reference_cuda_leg(host, wl, hop, device):
                         "sampled edges; table built by this library.  The reference's kernel publishes a slot of its "
                         "hop-2 job queue before writing it and drops jobs it reads too early (hop2_jobs_dropped of "
                         "hop2_jobs_due), so it samples somewhat fewer edges than the rule asks for"}
+    if wl["kind"] == "walk" and wl["mode"] == "offline" and wl.get("app") == "ppr" and ctx is not None:
+        # The reference's offline biased kernel has no stop rule, its unbiased walk has: the same graph, start
+        # vertices and termination probability through UnbiasedWalkKernelStatic (uniform neighbour, no table),
+        # and this library's walk of the same kind (SKW_WALK_UNBIASED) beside it, like for like.
+        from skywalker_b200 import APP_PPR, WALK_UNBIASED
+        n = wl["units"]
+        starts = O.gen_starts(n, V, START_SEED)
+        _, lens, sec = R.unbiased_walk(host["xadj"], host["adjncy"], starts, hop, tp=wl["tp"], device=device,
+                                       repeats=3, want_paths=False)
+        edges = int(lens.sum())
+        d_starts, d_result, d_lengths = d_buffers
+        ctx.generate_starts(n, START_SEED, d_starts)
+        best, our_edges = None, 0
+        for r in range(3):
+            _, _, ms, our_edges = ctx.walk(d_starts, hop, app=APP_PPR, tp=wl["tp"], flags=WALK_UNBIASED,
+                                           seed=WALK_SEED + r, paths=d_result, lengths=d_lengths, n=n)
+            best = ms if best is None else min(best, ms)
+        return {"kernel": "UnbiasedWalkKernelStatic via UnbiasedWalk (src/unbiased_walk.cu:104-130, 194-278)",
+                "value": edges / sec, "unit": "sampled edges/s", "seconds": sec, "sampled_edges": edges, "walkers": n,
+                "ours_same_kind": {"kernel": "SKW_WALK_UNBIASED over the walk records (walk_records_ppr_kernel)"
+                                             if records else "SKW_WALK_UNBIASED (walk_offline_kernel)",
+                                   "value": our_edges / (best * 1e-3),
+                                   "unit": "sampled edges/s", "ms": best, "sampled_edges": int(our_edges)},
+                "note": "UNBIASED walks with the workload's stop rule (the reference's biased offline kernel has none): "
+                        "uniform neighbour, no alias table.  Best of 3 runs, the reference's own wall-clock timer "
+                        "around its launch (cuRAND XORWOW set-up per thread included); ours by CUDA events"}
     if wl["kind"] != "walk" or wl["mode"] != "offline" or wl.get("app") != "deepwalk" or E > (1 << 28):
-        return {"unavailable": "the reference's static offline kernels cover offline DeepWalk (no stop rule, no "
-                               "node2vec) and offline 2-hop sampling; run --workload c1, c2, dw22 or c4off"}
+        return {"unavailable": "the reference's bounded kernels cover offline DeepWalk (biased), unbiased walks with "
+                               "a stop rule and offline 2-hop sampling; run --workload c1, c2, dw22, c5, c5s or c4off"}
     n = wl["units"]
     starts = O.gen_starts(n, V, START_SEED)
     paths, lens, sec = R.offline_walk(host["xadj"], host["adjncy"], host["table"], starts, hop, device=device, repeats=3)
@@ -761,7 +787,8 @@ def main():
                     cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample", "alias_build_edges_per_s")}
                 if rank == 0 and world == 1 and not args.no_reference_cuda:
                     try:
-                        ref_cuda = reference_cuda_leg(host, wl, hop, local_rank)
+                        ref_cuda = reference_cuda_leg(host, wl, hop, local_rank, ctx, (starts, result, lengths),
+                                                      records=use_records)
                     except Exception as e:      # never lose the bench line to the comparison arm
                         ref_cuda = {"unavailable": "failed: %s" % e}
                 del host

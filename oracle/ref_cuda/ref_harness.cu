@@ -1,11 +1,12 @@
 // Harness around the reference's OWN offline walk (wpybtw/Skywalker, src/offline_walk.cu:181-230:
 // OfflineWalk -> sample_kernel_static, lines 75-124) and its OWN offline 2-hop sampler
-// (src/offline_sample.cu:443-513: OfflineSample -> sample_kernel, lines 72-141), compiled from the
-// reference sources where they lie.  TEST / MEASUREMENT INFRASTRUCTURE ONLY: nothing in the shipped
+// (src/offline_sample.cu:443-513: OfflineSample -> sample_kernel, lines 72-141) and its OWN unbiased
+// walk (src/unbiased_walk.cu:194-278: UnbiasedWalk -> UnbiasedWalkKernelStatic, lines 104-130),
+// compiled from the reference sources where they lie.  TEST / MEASUREMENT INFRASTRUCTURE ONLY: nothing in the shipped
 // library links this.
 //
-// Only these two entry functions of the reference are driven, because their kernels are bounded:
-// the walk is a per-thread loop of hop_num - 1 iterations, the sampler drains job queues whose
+// Only these three entry functions of the reference are driven, because their kernels are bounded:
+// the walks are per-thread loops of hop_num - 1 iterations, the sampler drains job queues whose
 // sizes are fixed by the seed count and the fan-outs (every pop is one atomic, there is no wait on
 // another thread), and every index is derived from xadj / the table.  The
 // reference's table constructors (include/alias_table_new.cuh:637-708 spins in `while (alive)`) and
@@ -283,5 +284,94 @@ extern "C" int skwref_offline_sample(int device, uint32_t V, uint64_t E, const u
   }
   if (best_seconds) *best_seconds = best;
   if (sampled_edges) *sampled_edges = edges;
+  return 0;
+}
+
+
+// The reference's unbiased walk with its stop rule (every step ends the walk with probability tp, or
+// at a vertex without out-edges; the neighbour is floor(curand_uniform * degree), no table), one
+// thread per walker.  lengths has n entries; h_paths (n x hop_num) may be null when only the lengths
+// are wanted.  Returns 0, or a negative value when an argument or a CUDA call fails.
+extern "C" int skwref_unbiased_walk(int device, uint32_t V, uint64_t E, const uint32_t* h_xadj,
+                                    const uint32_t* h_adjncy, const uint32_t* h_starts, uint32_t n,
+                                    uint32_t hop_num, double tp, int repeats, uint32_t* h_paths,
+                                    uint32_t* h_lengths, double* best_seconds) {
+  if (!h_xadj || !h_adjncy || !h_starts || !h_lengths || !n || hop_num < 2 || E > 0xFFFFFF00ull || tp < 0.0 ||
+      tp >= 1.0)
+    return -1;
+  if (h_xadj[0] != 0 || h_xadj[V] != E) return -1;
+  for (uint32_t v = 0; v < V; ++v)
+    if (h_xadj[v] > h_xadj[v + 1]) return -1;
+  for (uint64_t e = 0; e < E; ++e)
+    if (h_adjncy[e] >= V) return -1;
+  for (uint32_t i = 0; i < n; ++i)
+    if (h_starts[i] >= V) return -1;
+  if (cudaSetDevice(device) != cudaSuccess) return -2;
+  FLAGS_static = true;  // UnbiasedWalkKernelStatic: a bounded loop per thread
+  FLAGS_buffer = false;
+  FLAGS_peritr = false;
+  FLAGS_node2vec = false;
+  FLAGS_tp = tp;
+  Dev dx, da, dd, dal, dlen, dst;
+  uint32_t* xadj = dx.alloc<uint32_t>((size_t)V + 1 + kSpare);
+  uint32_t* adjncy = da.alloc<uint32_t>(E + kSpare);  // the column can equal the degree: one entry past a list
+  uint32_t* data = dd.alloc<uint32_t>((size_t)n * hop_num);
+  char* alive = dal.alloc<char>(n);
+  uint32_t* length = dlen.alloc<uint32_t>(n);
+  uint32_t* starts = dst.alloc<uint32_t>(n);
+  if (!xadj || !adjncy || !data || !alive || !length || !starts) return -2;
+  bool ok = cudaMemcpy(xadj, h_xadj, sizeof(uint32_t) * ((size_t)V + 1), cudaMemcpyHostToDevice) == cudaSuccess &&
+            cudaMemcpy(adjncy, h_adjncy, sizeof(uint32_t) * E, cudaMemcpyHostToDevice) == cudaSuccess &&
+            cudaMemset(adjncy + E, 0, sizeof(uint32_t) * kSpare) == cudaSuccess &&
+            cudaMemcpy(starts, h_starts, sizeof(uint32_t) * n, cudaMemcpyHostToDevice) == cudaSuccess;
+  if (!ok) return -2;
+  gpu_graph g;
+  g.adjncy = adjncy;
+  g.adjwgt = nullptr;
+  g.xadj = xadj;
+  g.degree_list = nullptr;
+  g.outDegree = nullptr;
+  g.prob_array = nullptr;
+  g.alias_array = nullptr;
+  g.valid = nullptr;
+  g.vtx_num = V;
+  g.edge_num = (edge_t)E;
+  g.avg_degree = V ? (edge_t)(E / V) : 0;
+  g.MaxDegree = 0;
+  g.device_id = device;
+  g.result = nullptr;
+  g.local_vtx_offset = 0;
+  g.local_edge_offset = 0;
+  g.local_vtx_num = V;
+  g.local_edge_num = (uint)E;
+  Walker walker(g, device);
+  walker.num_seed = n;
+  walker.prob_array = nullptr;
+  walker.alias_array = nullptr;
+  walker.valid = nullptr;
+  std::memset(&walker.result, 0, sizeof(walker.result));
+  walker.result.size = n;
+  walker.result.hop_num = hop_num;
+  walker.result.data = data;
+  walker.result.alive = alive;
+  walker.result.length = length;
+  walker.result.device_id = device;
+  double best = 1e30;
+  for (int r = 0; r < (repeats > 0 ? repeats : 1); ++r) {
+    // rows of 0xFFFFFFFF with the start vertex in column 0 (a strided copy of the start array)
+    if (cudaMemset(data, 0xFF, sizeof(uint32_t) * (size_t)n * hop_num) != cudaSuccess ||
+        cudaMemcpy2D(data, sizeof(uint32_t) * hop_num, starts, sizeof(uint32_t), sizeof(uint32_t), n,
+                     cudaMemcpyDeviceToDevice) != cudaSuccess ||
+        cudaMemset(alive, 1, n) != cudaSuccess || cudaMemset(length, 0, sizeof(uint32_t) * n) != cudaSuccess)
+      return -2;
+    const double t = UnbiasedWalk(walker);
+    if (cudaDeviceSynchronize() != cudaSuccess) return -3;
+    if (t < best) best = t;
+  }
+  if ((h_paths && cudaMemcpy(h_paths, data, sizeof(uint32_t) * (size_t)n * hop_num, cudaMemcpyDeviceToHost) !=
+                      cudaSuccess) ||
+      cudaMemcpy(h_lengths, length, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost) != cudaSuccess)
+    return -2;
+  if (best_seconds) *best_seconds = best;
   return 0;
 }

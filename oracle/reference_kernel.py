@@ -50,6 +50,9 @@ def lib():
                                             C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_int, u32p, u32p,
                                             C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]
         L.skwref_offline_sample.restype = C.c_int
+        L.skwref_unbiased_walk.argtypes = [C.c_int, C.c_uint32, C.c_uint64, u32p, u32p, u32p, C.c_uint32, C.c_uint32,
+                                           C.c_double, C.c_int, C.c_void_p, u32p, C.POINTER(C.c_double)]
+        L.skwref_unbiased_walk.restype = C.c_int
         _LIB = L
     return _LIB
 
@@ -100,3 +103,22 @@ def offline_sample(xadj, adjncy, table, seeds, f1, f2, device=0, repeats=1, bloc
         raise RuntimeError("reference offline sample failed with code %d (-1 argument check, -2 CUDA call, "
                            "-3 kernel, -4 layout)" % rc)
     return data, sl, sec.value, edges.value
+
+
+def unbiased_walk(xadj, adjncy, starts, hop_num, tp=0.0, device=0, repeats=1, want_paths=True):
+    """Run the reference's unbiased walk (UnbiasedWalk -> UnbiasedWalkKernelStatic: uniform neighbour, every
+    step ends the walk with probability tp) over `starts`.  Returns (paths[n, hop_num] or None, lengths[n],
+    seconds) with the reference's own best wall time of `repeats` runs."""
+    xadj = np.ascontiguousarray(xadj, np.uint32)
+    adjncy = np.ascontiguousarray(adjncy, np.uint32)
+    starts = np.ascontiguousarray(starts, np.uint32)
+    n, V, E = len(starts), len(xadj) - 1, len(adjncy)
+    paths = np.zeros((n, hop_num), np.uint32) if want_paths else None
+    lengths = np.zeros(n, np.uint32)
+    sec = C.c_double()
+    rc = lib().skwref_unbiased_walk(device, V, E, xadj, adjncy, starts, n, hop_num, float(tp), repeats,
+                                    paths.ctypes.data if want_paths else None, lengths, C.byref(sec))
+    if rc:
+        raise RuntimeError("reference unbiased walk failed with code %d (-1 argument check, -2 CUDA call, "
+                           "-3 kernel)" % rc)
+    return paths, lengths, sec.value

@@ -61,6 +61,7 @@ struct skw_ctx {
   void* vinfo = nullptr;
   void* vbits = nullptr;  // one bit per vertex: usable degree != 0
   bool records_ready = false;  // set once records, vinfo and vbits were all written
+  bool records_all_usable = false;  // ... and no vertex with out-edges lacks a usable table
 
   // device error word (4 x u32) and its pinned host mirror
   uint32_t* d_err = nullptr;

@@ -199,7 +199,8 @@ __device__ __forceinline__ void load_record(const WalkRecord* p, u32 (&w)[8]) {
 // end (most uniformly random starts of a directed R-MAT graph) never touches DRAM for it.
 __global__ void __launch_bounds__(256) vertex_info_kernel(const u32* __restrict__ xadj,
                                                           const Slot* __restrict__ slots, u32 V,
-                                                          uint2* __restrict__ vinfo, u32* __restrict__ vbits) {
+                                                          uint2* __restrict__ vinfo, u32* __restrict__ vbits,
+                                                          u32* __restrict__ unusable) {
   const u64 T = (u64)gridDim.x * blockDim.x;
   const u64 rounds = ((u64)V + T - 1) / T;
   for (u64 it = 0; it < rounds; ++it) {  // whole warps stay in the loop: the ballot needs them
@@ -208,7 +209,10 @@ __global__ void __launch_bounds__(256) vertex_info_kernel(const u32* __restrict_
     if (v < V) {
       const u32 off = xadj[v], deg = xadj[v + 1] - off;
       eff = deg;
-      if (deg && load_slot(slots + off).prob < 0.0f) eff = 0;
+      if (deg && load_slot(slots + off).prob < 0.0f) {
+        eff = 0;
+        atomicAdd(unusable, 1u);  // has out-edges but no table (all weights unusable, or not built yet): rare
+      }
       vinfo[v] = make_uint2(off, eff);
     }
     const u32 word = __ballot_sync(0xFFFFFFFFu, eff != 0);
@@ -314,6 +318,7 @@ struct RecordWalkArgs {
   u32 V;
   u32 hop_num;
   float tp;
+  u32 unbiased;  // uniform neighbour: the column's own neighbour is always kept (SKW_WALK_UNBIASED)
 };
 
 // Same lane-owns-a-stride loop as walk_offline_kernel; a step is one record load.
@@ -355,7 +360,7 @@ __global__ void __launch_bounds__(256) walk_records_walk_kernel(const RecordWalk
       // the next step's random words do not depend on the record: computing them here overlaps the
       // load's latency (what a walk is made of when few walkers are in flight)
       const Rand4 rn = philox_tagged(a.seed, TAG_WALK, a.walker_base + w * a.walker_stride, step + 1, 0);
-      const bool keep = u01(r.y) < __uint_as_float(rw[0]);
+      const bool keep = a.unbiased || u01(r.y) < __uint_as_float(rw[0]);
       ++step;
       row[step] = keep ? rw[1] : rw[4];
       off = keep ? rw[2] : rw[5];
@@ -471,7 +476,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2048 / (WARPS * 32)) walk_records_
         // load's latency, which is what the end of a pass is made of
         const u32 ry = r.y;
         r = philox_tagged(a.seed, TAG_WALK, a.walker_base + (w_begin + local) * a.walker_stride, step + 1, 0);
-        const bool keep = u01(ry) < __uint_as_float(rw[0]);
+        const bool keep = a.unbiased || u01(ry) < __uint_as_float(rw[0]);
         ++step;
         const u32 nv = keep ? rw[1] : rw[4];
         if (step < (u32)STAGE) buf[local * kPitch + step] = nv;
@@ -621,9 +626,12 @@ int skw_walk_records_build(skw_ctx* ctx, float* ms) {
     cudaStream_t st = ctx->stream;
     SKW_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
     if (ctx->V) {
+      SKW_CUDA(ctx, cudaMemsetAsync(ctx->d_sum + 3, 0, sizeof(uint64_t), st));
       vertex_info_kernel<<<ctx->sm_count * 16, 256, 0, st>>>(ctx->xadj, ctx->slots, ctx->V,
-                                                              static_cast<uint2*>(ctx->vinfo), static_cast<u32*>(ctx->vbits));
+                                                              static_cast<uint2*>(ctx->vinfo), static_cast<u32*>(ctx->vbits),
+                                                              reinterpret_cast<u32*>(ctx->d_sum + 3));
       SKW_LAUNCHED(ctx);
+      SKW_CUDA(ctx, cudaMemcpyAsync(ctx->h_sum + 3, ctx->d_sum + 3, sizeof(uint64_t), cudaMemcpyDeviceToHost, st));
     }
     if (ctx->E && ctx->V) {
       const u64 tiles = (ctx->E + kRecTile - 1) / kRecTile;
@@ -647,6 +655,9 @@ int skw_walk_records_build(skw_ctx* ctx, float* ms) {
     return rc;
   }
   ctx->records_ready = true;
+  // every vertex with out-edges has a usable table: the records' offsets and degrees are then those of
+  // the graph itself, and unbiased walks may follow them too
+  ctx->records_all_usable = ctx->V == 0 || (ctx->h_sum[3] & 0xFFFFFFFFull) == 0;
   return SKW_OK;
 }
 
@@ -765,8 +776,12 @@ static int walk_launch(skw_ctx* ctx, const skw_walk_params* prm, const uint32_t*
   a.inv_q = prm->app == SKW_APP_NODE2VEC ? 1.0f / prm->q : 1.0f;
   a.fmax = fmaxf(1.0f, fmaxf(a.inv_p, a.inv_q));
   cudaStream_t st = ctx->stream;
-  if (!online && !unbiased && ctx->records_ready && prm->app != SKW_APP_NODE2VEC) {
+  // Walk records serve unbiased walks as well (the record of column c names the c-th neighbour with its
+  // offset and degree: one access per step instead of two), as long as every vertex with out-edges has
+  // a usable table, i.e. the degrees in the records are the graph's own.
+  if (!online && ctx->records_ready && prm->app != SKW_APP_NODE2VEC && (!unbiased || ctx->records_all_usable)) {
     RecordWalkArgs ra;
+    ra.unbiased = unbiased ? 1u : 0u;
     ra.rec = static_cast<const WalkRecord*>(ctx->records);
     ra.vinfo = static_cast<const uint2*>(ctx->vinfo);
     ra.vbits = static_cast<const u32*>(ctx->vbits);

@@ -619,6 +619,16 @@ def test_unbiased_walks_bit_exact(ctx, oracle, plaw, app, kw):
     paths2, lens2, _, _ = ctx.walk(starts, hop, app=app, mode=MODE_ONLINE, seed=5, walker_base=17,
                                    flags=WALK_UNBIASED, **kw)
     assert np.array_equal(lens2, lens) and np.array_equal(paths2, paths)
+    # (DeepWalk and PPR then follow the walk records: one access per step.)  Not when a vertex with
+    # out-edges has no usable table -- its record would say "no way on", which holds for a biased walk only
+    w = g.adjwgt.copy()
+    hub = int(np.argmax(np.diff(g.xadj.astype(np.int64))))
+    w[g.xadj[hub]:g.xadj[hub + 1]] = 0.0
+    ctx.upload(g.xadj, g.adjncy, w)
+    ctx.alias_build_offline()
+    ctx.walk_records_build()
+    paths3, lens3, _, _ = ctx.walk(starts, hop, app=app, seed=5, walker_base=17, flags=WALK_UNBIASED, **kw)
+    assert np.array_equal(lens3, lens) and np.array_equal(paths3, paths)
 
 
 @pytest.mark.parametrize("flags", [0, KHOP_TAKE_ALL])

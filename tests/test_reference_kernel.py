@@ -186,3 +186,34 @@ def test_reference_samples_and_ours_have_the_same_statistics(ctx, oracle, ref, r
     assert p_vis > 0.001, p_vis
     print("reference hop 2: %d of %d jobs of the first 2000 seeds sampled; sampled edges %d (ours %d)"
           % (done, expected, redges, oedges))
+
+
+def test_reference_unbiased_walks_and_ours_have_the_same_statistics(ctx, oracle, ref, rmat12):
+    """The reference's unbiased walk with its stop rule (UnbiasedWalkKernelStatic, src/unbiased_walk.cu:104-130)
+    beside SKW_WALK_UNBIASED on the same graph and start vertices, tp = 0.15: every step follows an edge, and
+    the walk-length histogram and the visit counts after two steps agree (two-sample chi-square)."""
+    from scipy import stats
+    from skywalker_b200 import APP_PPR, WALK_UNBIASED
+    g = rmat12
+    ctx.upload(g.xadj, g.adjncy, g.adjwgt)
+    N, hop = 300000, 41
+    starts = oracle.gen_starts(N, g.V, 91)
+    ref_p, ref_l, sec = ref.unbiased_walk(g.xadj, g.adjncy, starts, hop, tp=0.15)
+    ours_p, ours_l, _, _ = ctx.walk(starts, hop, app=APP_PPR, tp=0.15, flags=WALK_UNBIASED, seed=4)
+    assert sec > 0 and (ref_p[:, 0] == starts).all()
+    for s_ in range(2):
+        alive = ref_l > s_
+        src, dst = ref_p[alive, s_].astype(np.int64)[:2000], ref_p[alive, s_ + 1][:2000]
+        assert all(d in g.adjncy[g.xadj[a]:g.xadj[a + 1]] for a, d in zip(src, dst))
+    ha, hb = np.bincount(ours_l, minlength=hop), np.bincount(ref_l, minlength=hop)
+    keep = (ha + hb) >= 20
+    _, p_len, _, _ = stats.chi2_contingency(np.vstack([ha[keep], hb[keep]]))
+    assert p_len > 0.001, p_len
+    def visits(paths, lens):
+        return np.bincount(paths[lens >= 2, 2].astype(np.int64), minlength=g.V)
+    va, vb = visits(ours_p, ours_l), visits(ref_p, ref_l)
+    top = np.argsort(-(va + vb))[:40]
+    ta = np.append(va[top], va.sum() - va[top].sum())
+    tb = np.append(vb[top], vb.sum() - vb[top].sum())
+    _, p_vis, _, _ = stats.chi2_contingency(np.vstack([ta, tb]))
+    assert p_vis > 0.001, p_vis
