@@ -14,9 +14,9 @@
 //     (exact mass conservation in integers, reconstruction of w_i / sum(w) to 1e-6) and against
 //     the hand-checkable vectors the reference's smoke programs use (test/tmp.cu:31-42);
 //   * the draw / walk / k-hop rules against the reference kernels they restate, cited below;
-//   * statistically, against the reference's OWN offline walk kernel and offline 2-hop sampler
-//     run on the GPU (oracle/ref_cuda builds OfflineWalk / sample_kernel_static and
-//     OfflineSample / sample_kernel from the reference sources): fed with tables of this
+//   * statistically, against the reference's OWN offline walk kernel, offline 2-hop sampler and
+//     unbiased walk run on the GPU (oracle/ref_cuda builds OfflineWalk / sample_kernel_static,
+//     OfflineSample / sample_kernel and UnbiasedWalk from the reference sources): fed with tables of this
 //     construction their draws follow the edge weights, the walks have the same length and visit
 //     statistics as the walks defined here, and the hop-1 sample counts and sampled vertices of
 //     the sampler match the take-all rule defined here (tests/test_reference_kernel.py).

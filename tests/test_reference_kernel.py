@@ -1,6 +1,7 @@
 """The reference's own offline walk kernel (sample_kernel_static, src/offline_walk.cu:75-124 of
 wpybtw/Skywalker, driven through its OfflineWalk entry function) and its own offline 2-hop sampler
-(sample_kernel, src/offline_sample.cu:72-141, through OfflineSample) beside this library.
+(sample_kernel, src/offline_sample.cu:72-141, through OfflineSample) and its unbiased walk
+(UnbiasedWalkKernelStatic, src/unbiased_walk.cu:104-130, through UnbiasedWalk) beside this library.
 
 The reference has no golden vectors and its random stream (XORWOW seeded by thread id) cannot be
 reproduced, so the comparison is statistical: fed with the alias table THIS library builds (exported
