@@ -255,9 +255,10 @@ def cpu_leg(host, wl, threads, want_seconds=12.0, steps=1, warmup=0, build_weigh
 
 def reference_cuda_leg(host, wl, hop, device, ctx=None, d_buffers=None, records=False):
     """The reference's OWN offline walk kernel (sample_kernel_static through OfflineWalk) on this
-    workload's graph, start vertices and GPU-built table: throughput by the reference's own timer.  Only
-    for offline DeepWalk on graphs small enough to hand over through host arrays; its walks come from
-    another random stream, so only the rate is comparable."""
+    workload's graph, start vertices and GPU-built table: throughput by the reference's own timer.  For
+    offline DeepWalk (graph and table are handed over through host arrays; its walks come from another
+    random stream, so only the rate is comparable); PPR and offline 2-hop workloads run the reference's
+    unbiased walk and offline sampler instead."""
     from oracle import oracle as O
     from oracle import reference_kernel as R
     if not R.available():
@@ -308,7 +309,7 @@ def reference_cuda_leg(host, wl, hop, device, ctx=None, d_buffers=None, records=
                 "note": "UNBIASED walks with the workload's stop rule (the reference's biased offline kernel has none): "
                         "uniform neighbour, no alias table.  Best of 3 runs, the reference's own wall-clock timer "
                         "around its launch (cuRAND XORWOW set-up per thread included); ours by CUDA events"}
-    if wl["kind"] != "walk" or wl["mode"] != "offline" or wl.get("app") != "deepwalk" or E > (1 << 28):
+    if wl["kind"] != "walk" or wl["mode"] != "offline" or wl.get("app") != "deepwalk" or E > 0xFFFFFF00:
         return {"unavailable": "the reference's bounded kernels cover offline DeepWalk (biased), unbiased walks with "
                                "a stop rule and offline 2-hop sampling; run --workload c1, c2, dw22, c5, c5s or c4off"}
     n = wl["units"]
