@@ -659,9 +659,7 @@ def main():
         e_steps = max(1, min(args.steps, 20))
 
         def timed_host_calls(call):
-            # warm calls: staging buffers reach their steady size, and with several ranks on one box the
-            # per-call time keeps falling over the first ten or so short calls (8 GPUs: 1.97 -> 1.07 ms)
-            for i in range(3 if world == 1 else 12):
+            for i in range(3):      # warm calls: staging buffers reach their steady size
                 call(50 + i)
             barrier()
             t0 = time.perf_counter()
