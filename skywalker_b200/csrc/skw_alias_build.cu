@@ -396,7 +396,9 @@ __device__ __forceinline__ void merge_window(u32 t, u32 nl, u32 Sl, const u64* s
 
 // WIN == 0: the lists A / P are in shared memory and are merged in place.  WIN > 0: they are in
 // global scratch and win_smem holds WIN * 12 + (NT + 1) * 4 bytes of shared memory for staging.
-// BULK: the tiles of the weight list come through `pipe` (see TilePipe) instead of global loads.
+// NBUF > 0: the tiles of the weight list come through `pipe` (see TilePipe) instead of global loads, with
+// two buffers one tile ahead of the one being worked on, with one buffer refilled as soon as a tile's
+// weights are quantised.
 // STAGED: w points at a copy of the weight list in shared memory, else at the list in global memory.
 // Weight tiles of the scratch class brought into shared memory by the bulk-copy engine, one tile
 // ahead of the one being worked on: two buffers of tile + 8 floats and one mbarrier each.  The parity
@@ -408,7 +410,7 @@ struct TilePipe {
   bool failed;  // a copy did not report completion in time: the CTA stops taking vertices
 };
 
-template <int NT, int EPT, int WIN, bool STAGED, bool BULK = false>
+template <int NT, int EPT, int WIN, bool STAGED, int NBUF = 0>
 __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
                                    Slot* __restrict__ slots, uint8_t* __restrict__ valid, u64* A,
                                    u32* P, u64* s_tmp, unsigned char* win_smem, u32* err,
@@ -441,6 +443,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
   u64 cQ = 0, cD = 0;  // carries between tiles (the same value in every thread)
   u32 cL = 0;
   constexpr u32 kTile = NT * EPT;
+  constexpr bool BULK = NBUF > 0;
   // BULK: element i of a tile sits at buffer[head + i]; the list starts `head` floats after a 16-byte
   // boundary and tiles are whole multiples of 16 bytes, so every tile has the same head.  The copy
   // engine brings the 16-byte groups that lie inside the tile, up to three floats at either end come
@@ -472,9 +475,9 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
     const u32 p0 = base + t * ept;
     const float* tw = nullptr;  // BULK: this tile's weights in shared memory, tw[i] = weight base + i
     if constexpr (BULK) {
-      const u32 b = (base / kTile) & 1u;
-      // the other buffer was last read in the tile before this one, which ended with a barrier
-      if (base + kTile < n) stage_tile(base + kTile, b ^ 1u);
+      const u32 b = NBUF == 2 ? (base / kTile) & 1u : 0u;
+      // two buffers: the other one was last read in the tile before this one, which ended with a barrier
+      if (NBUF == 2 && base + kTile < n) stage_tile(base + kTile, b ^ 1u);
       const bool ok = mbar_wait(pipe->bars + b, (pipe->parity >> b) & 1u, 1u << 16);
       // the same outcome in every thread (and the barrier that publishes the plain stores)
       if (!__syncthreads_and(ok ? 1 : 0)) {
@@ -482,7 +485,7 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
         // writes this CTA's shared memory when it leaves, and stop
         if (t == 0) dev_fail(err, DEV_ERR_WAIT, v, base, 13);
         if (!ok) mbar_wait(pipe->bars + b, (pipe->parity >> b) & 1u, 1u << 16);
-        if (base + kTile < n) mbar_wait(pipe->bars + (b ^ 1u), (pipe->parity >> (b ^ 1u)) & 1u, 1u << 16);
+        if (NBUF == 2 && base + kTile < n) mbar_wait(pipe->bars + (b ^ 1u), (pipe->parity >> (b ^ 1u)) & 1u, 1u << 16);
         pipe->failed = true;
         return;
       }
@@ -500,6 +503,9 @@ __device__ void build_vertex_merge(u32 t, u32 v, u32 off, u32 n, const float* w,
     }
     u64 tq;
     coop_scan_u64<NT>(Qex, tq, s_tmp);
+    // one buffer: every thread has passed the scan's barriers, so nobody reads this tile's weights any
+    // more and the next tile can come in under the rest of this one's work
+    if (NBUF == 1 && base + kTile < n) stage_tile(base + kTile, 0);
     Qex += cQ;
     cQ += tq;
     const u64 gex = cum_mass(Qex, W, nC, K);
@@ -1019,9 +1025,11 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
   u32* P = reinterpret_cast<u32*>(A + cap);
   const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
   __shared__ u32 s_it;
-  // WIN > 0: behind the merge windows, two buffers for the weight tiles the bulk-copy engine brings in
-  TilePipe pipe{reinterpret_cast<float*>(smem + win_smem_bytes(NT, WIN)), s_bars, 0u, false};
-  if (WIN && threadIdx.x == 0) {
+  // Weight tiles brought in by the bulk-copy engine: two buffers behind the merge windows (WIN > 0), one
+  // buffer behind the lists of the 1024-thread shared-memory class, whose one CTA per SM has the room
+  constexpr int NBUF = WIN > 0 ? 2 : (NT == 1024 ? 1 : 0);
+  TilePipe pipe{reinterpret_cast<float*>(WIN ? smem + win_smem_bytes(NT, WIN) : smem + cap * 12ull), s_bars, 0u, false};
+  if (NBUF && threadIdx.x == 0) {
     mbar_init(&s_bars[0], 1);
     mbar_init(&s_bars[1], 1);
   }
@@ -1038,7 +1046,7 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
       if (threadIdx.x == 0) dev_fail(err, DEV_ERR_CAPACITY, v, n, (u32)cap);
       continue;
     }
-    build_vertex_merge<NT, 8, WIN, false, (WIN > 0)>(threadIdx.x, v, off, n, wgt + off, slots, valid, A, P, s_tmp,
+    build_vertex_merge<NT, 8, WIN, false, NBUF>(threadIdx.x, v, off, n, wgt + off, slots, valid, A, P, s_tmp,
                                                       smem, err, &pipe);
     if (pipe.failed) break;  // the same in every thread
     __syncthreads();
@@ -1295,7 +1303,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   cudaStream_t st = ctx->stream;
   static_assert(kLargeMax <= kPackedMax, "the 1025+ CTA class uses packed list entries");
   constexpr int kCtaSmem = kLargeMax * 8;
-  constexpr int kCta2Smem = kHugeSmemMax * 12;
+  constexpr int kCta2Smem = kHugeSmemMax * 12 + tile_pipe_bytes(1024) / 2;  // lists + one weight tile
   constexpr int kCta2aSmem = kMidSmemMax * 12;
   constexpr int kCtaStagedSmem = kLargeMax * 8 + (kLargeMax + 8) * 4;
   constexpr int kW1KSmem = 8 * kWarpMax * 8;
