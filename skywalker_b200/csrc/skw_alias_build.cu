@@ -1026,8 +1026,9 @@ __global__ void __launch_bounds__(NT) build_cta_merge_kernel(const u32* __restri
   const u32 count = cls[k], base = cls[2 * K_CLASSES + k];
   __shared__ u32 s_it;
   // Weight tiles brought in by the bulk-copy engine: two buffers behind the merge windows (WIN > 0), one
-  // buffer behind the lists of the 1024-thread shared-memory class, whose one CTA per SM has the room
-  constexpr int NBUF = WIN > 0 ? 2 : (NT == 1024 ? 1 : 0);
+  // buffer behind the lists of the shared-memory classes (two 512-thread CTAs with 96 KB of lists and a
+  // 16 KB tile each still share an SM)
+  constexpr int NBUF = WIN > 0 ? 2 : 1;
   TilePipe pipe{reinterpret_cast<float*>(WIN ? smem + win_smem_bytes(NT, WIN) : smem + cap * 12ull), s_bars, 0u, false};
   if (NBUF && threadIdx.x == 0) {
     mbar_init(&s_bars[0], 1);
@@ -1304,7 +1305,7 @@ static int launch_builders(skw_ctx* ctx, const u32* worklist, u32* cls) {
   static_assert(kLargeMax <= kPackedMax, "the 1025+ CTA class uses packed list entries");
   constexpr int kCtaSmem = kLargeMax * 8;
   constexpr int kCta2Smem = kHugeSmemMax * 12 + tile_pipe_bytes(1024) / 2;  // lists + one weight tile
-  constexpr int kCta2aSmem = kMidSmemMax * 12;
+  constexpr int kCta2aSmem = kMidSmemMax * 12 + tile_pipe_bytes(512) / 2;  // lists + one weight tile
   constexpr int kCtaStagedSmem = kLargeMax * 8 + (kLargeMax + 8) * 4;
   constexpr int kW1KSmem = 8 * kWarpMax * 8;
   constexpr int kWin = 8192;                        // merged outputs per window of the scratch class
