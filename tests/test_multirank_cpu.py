@@ -102,3 +102,36 @@ def test_edge_chunk_ranges_cover_every_chunk(oracle):
         assert covered.all()
     S, r = edge_chunk_ranges(np.zeros(5, np.uint32), 3)
     assert r[0][0] == 0 and r[-1][1] == 4 and all(b <= e for b, e in r)
+
+
+def test_pipelined_table_assembly_covers_the_table(oracle):
+    """The multi-GPU table build of bench.py and the command-line driver: the slot array in N * P equal
+    chunks, rank r builds chunks r, N + r, 2N + r ..., piece k (chunks k*N .. k*N + N - 1) is all-gathered in
+    place while piece k + 1 is built.  Simulated on the CPU with the oracle as builder: the pieces tile the
+    slot array without a gap, every rank's chunk sits where the in-place all-gather expects it, and the
+    assembled table equals the table built in one go."""
+    sys.path.insert(0, ROOT)
+    from skywalker_b200.api import edge_chunk_ranges
+    x, a = oracle.gen_rmat(11, 12 << 11, seed=5)
+    w = oracle.gen_weights(len(a), 3)
+    E, V = int(x[-1]), len(x) - 1
+    prob, alias, valid = oracle.alias_build(x, w)
+    for world, pieces in ((2, 4), (4, 4), (8, 4), (3, 2)):
+        S, ranges = edge_chunk_ranges(x, world * pieces)
+        assert world * pieces * S >= E > (world * pieces - 1) * S - S
+        got_p = np.full(world * pieces * S, np.nan, np.float32)
+        got_a = np.zeros(world * pieces * S, np.uint32)
+        got_v = np.zeros(V, np.uint8)
+        for k in range(pieces):
+            piece = slice(k * world * S, (k + 1) * world * S)          # the all-gather's receive buffer
+            for rank in range(world):
+                c = k * world + rank
+                assert piece.start + rank * S == c * S                 # in place: send buffer inside it
+                vb, ve = ranges[c]
+                p_r, a_r, v_r = oracle.alias_build(x, w, vb, ve)       # this rank's build of its vertices
+                lo, hi = min(c * S, E), min((c + 1) * S, E)
+                got_p[lo:hi] = p_r[lo:hi]                              # what the gather takes from this rank
+                got_a[lo:hi] = a_r[lo:hi]
+                got_v[vb:ve] = np.maximum(got_v[vb:ve], v_r[vb:ve])    # flags: all-reduce (max)
+        assert np.array_equal(got_p[:E].view(np.uint32), prob.view(np.uint32))
+        assert np.array_equal(got_a[:E], alias) and np.array_equal(got_v, valid)
